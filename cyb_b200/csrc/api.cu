@@ -1,0 +1,72 @@
+// Context and error plumbing of libqeng.
+#include <stdarg.h>
+
+#include "qeng_internal.h"
+
+int32_t qeng_fail(qeng_ctx* ctx, int32_t code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (ctx) ctx->err = buf;
+  return code;
+}
+
+extern "C" {
+
+int32_t qeng_version(void) { return 100; }
+
+int32_t qeng_create(int32_t device, qeng_ctx** out) {
+  if (!out) return QENG_ERR_ARG;
+  *out = nullptr;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) return QENG_ERR_CUDA;  // no CPU fallback
+  if (device < 0 || device >= count) return QENG_ERR_ARG;
+  qeng_ctx* ctx = new qeng_ctx();
+  ctx->device = device;
+  cudaDeviceProp prop;
+  if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
+    delete ctx;
+    return QENG_ERR_CUDA;
+  }
+  if (prop.major != 10) {  // the kernels are built for sm_100a only
+    delete ctx;
+    return QENG_ERR_CUDA;
+  }
+  ctx->sm_count = prop.multiProcessorCount;
+  if (cudaMalloc(&ctx->status, 64) != cudaSuccess || cudaMemset(ctx->status, 0, 64) != cudaSuccess) {
+    delete ctx;
+    return QENG_ERR_CUDA;
+  }
+  *out = ctx;
+  return QENG_OK;
+}
+
+int32_t qeng_destroy(qeng_ctx* ctx) {
+  if (!ctx) return QENG_ERR_ARG;
+  cudaSetDevice(ctx->device);
+  if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);
+  if (ctx->status) cudaFree(ctx->status);
+  delete ctx;
+  return QENG_OK;
+}
+
+const char* qeng_last_error(const qeng_ctx* ctx) { return ctx ? ctx->err.c_str() : "null context"; }
+
+int32_t qeng_device_status(qeng_ctx* ctx) {
+  if (!ctx) return QENG_ERR_ARG;
+  QENG_CUDA(ctx, cudaSetDevice(ctx->device));
+  QENG_CUDA(ctx, cudaDeviceSynchronize());
+  int32_t status = 0;
+  QENG_CUDA(ctx, cudaMemcpy(&status, ctx->status, 4, cudaMemcpyDeviceToHost));
+  if (status == 0) return QENG_OK;
+  QENG_CUDA(ctx, cudaMemset(ctx->status, 0, 4));
+  return qeng_fail(ctx, QENG_ERR_DEVICE_STATUS,
+                   "a kernel reported status %d (1 = page id outside the pool, 2 = position outside the cache, "
+                   "3 = token id outside the vocabulary)", status);
+}
+
+int32_t qeng_sm_count(const qeng_ctx* ctx) { return ctx ? ctx->sm_count : 0; }
+
+}  // extern "C"

@@ -1,0 +1,348 @@
+// Decode attention (GQA) over a paged f16 KV cache, split over the KV length.
+//
+// Pool layout: f16 [page][kv head][K|V][16 tokens][128], so the K tile and the
+// V tile of one (page, kv head) are 4 KB contiguous each.  One CTA serves one
+// (sequence, kv head, split): its warps take pages round-robin, load the K and
+// V tiles straight into MMA fragments with 128-bit loads (the contraction
+// index of an MMA may be permuted freely as long as both operands agree, which
+// lets every lane load contiguous 16-byte pieces), and keep an online softmax
+// (max, sum, out) per query head of the group.  Warps are merged in shared
+// memory, splits through a scratch buffer and a second small kernel.
+//
+// HBM-bound: algorithmic bytes = sum_b len_b * kv_heads * 2 * 128 * 2.
+#include <math.h>
+
+#include "qeng_internal.h"
+
+namespace {
+
+constexpr int kAW = 4;  // warps per CTA
+constexpr int kHD = 128;
+
+struct AttnParams {
+  const __half* pool;
+  const __half* q;
+  const int32_t* table;
+  const int32_t* lens;
+  float* part_o;   // [B][Hq][S][128]
+  float* part_ml;  // [B][Hq][S][2]
+  float* out;      // [B][Hq][128]
+  int32_t* status;
+  int pages, Hkv, Hq, grp, max_pages, pps, S;
+  float scale_log2;
+};
+
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg_nc(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnParams p) {
+  const int s = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int len = p.lens[b];
+  const int npages = min((len + 15) >> 4, p.max_pages);
+  const int p0 = s * p.pps;
+  if (p0 >= npages) return;
+  const int p1 = min(npages, p0 + p.pps);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+
+  __shared__ float sm_o[kAW][8][kHD];
+  __shared__ float sm_m[kAW][8], sm_l[kAW][8];
+
+  // Q fragments: row g of the A operand = query head h*grp+g (rows >= grp are zero)
+  uint4 qa[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) qa[i] = make_uint4(0u, 0u, 0u, 0u);
+  if (g < p.grp) {
+    const uint4* qp = reinterpret_cast<const uint4*>(p.q + ((size_t)b * p.Hq + (size_t)h * p.grp + g) * kHD);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) qa[i] = qp[i * 4 + t];
+  }
+
+  float m_run = -INFINITY, l_run = 0.f;
+  float o[16][4];
+#pragma unroll
+  for (int j = 0; j < 16; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
+
+  for (int pg = p0 + warp; pg < p1; pg += kAW) {
+    const int pid = p.table[(size_t)b * p.max_pages + pg];
+    if ((unsigned)pid >= (unsigned)p.pages) {  // malformed page table: record and skip
+      if (lane == 0) atomicExch(p.status, 1);
+      continue;
+    }
+    const uint4* kt = reinterpret_cast<const uint4*>(p.pool + ((size_t)pid * p.Hkv + h) * (2 * 16 * kHD));
+    const uint4* vt = kt + 16 * kHD / 8;
+    // K rows of tokens g and g+8: the 16 bytes at d = 32i + 8t .. +7
+    uint4 kq[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) kq[nt][i] = ldg_nc(kt + (nt * 8 + g) * 16 + i * 4 + t);
+    // V rows of tokens 2t, 2t+1, 2t+8, 2t+9: d = 8g..8g+7 and 64+8g..64+8g+7
+    uint4 vv[4][2];
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      const int tk = 2 * t + (x & 1) + ((x >> 1) << 3);
+#pragma unroll
+      for (int r = 0; r < 2; ++r) vv[x][r] = ldg_nc(vt + tk * 16 + r * 8 + g);
+    }
+
+    // S = Q K^T for 16 tokens: two n-tiles of 8 tokens
+    float sacc[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        mma16816(sacc[nt], qa[i].x, 0u, qa[i].y, 0u, kq[nt][i].x, kq[nt][i].y);
+        mma16816(sacc[nt], qa[i].z, 0u, qa[i].w, 0u, kq[nt][i].z, kq[nt][i].w);
+      }
+    }
+    // scale (log2 domain), mask the tail of the last page
+    const int tok0 = pg * 16;
+    float sv[4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int tok = tok0 + nt * 8 + 2 * t + c;
+        sv[nt * 2 + c] = tok < len ? sacc[nt][c] * p.scale_log2 : -INFINITY;
+      }
+    float tmax = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+    const float m_new = fmaxf(m_run, tmax);  // finite: token tok0 of a listed page is valid
+    const float alpha = exp2f(m_run - m_new);
+    float pr[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pr[i] = exp2f(sv[i] - m_new);
+    l_run = l_run * alpha + (pr[0] + pr[1] + pr[2] + pr[3]);
+    m_run = m_new;
+    if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        o[j][0] *= alpha;
+        o[j][1] *= alpha;
+      }
+    }
+    // P as A operand, split into two f16 terms so no probability precision is lost
+    const uint32_t ph0 = pack_h2(pr[0], pr[1]), ph1 = pack_h2(pr[2], pr[3]);
+    const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&ph0));
+    const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&ph1));
+    const uint32_t pl0 = pack_h2(pr[0] - f0.x, pr[1] - f0.y), pl1 = pack_h2(pr[2] - f1.x, pr[3] - f1.y);
+    // zero V rows beyond the sequence (their probability is 0, but 0 * garbage may be NaN)
+    if (tok0 + 16 > len) {
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const int tok = tok0 + 2 * t + (x & 1) + ((x >> 1) << 3);
+        if (tok >= len) vv[x][0] = vv[x][1] = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    // O += P V : n-tile j covers d = 8n + (j&7) + 64*(j>>3), n = column of the tile
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int r = j >> 3, jj = j & 7;
+      const uint32_t* va = reinterpret_cast<const uint32_t*>(&vv[0][r]);
+      const uint32_t* vb = reinterpret_cast<const uint32_t*>(&vv[1][r]);
+      const uint32_t* vc = reinterpret_cast<const uint32_t*>(&vv[2][r]);
+      const uint32_t* vd = reinterpret_cast<const uint32_t*>(&vv[3][r]);
+      const uint32_t sel = (jj & 1) ? 0x7632u : 0x5410u;
+      const uint32_t b0 = __byte_perm(va[jj >> 1], vb[jj >> 1], sel);
+      const uint32_t b1 = __byte_perm(vc[jj >> 1], vd[jj >> 1], sel);
+      mma16816(o[j], ph0, 0u, ph1, 0u, b0, b1);
+      mma16816(o[j], pl0, 0u, pl1, 0u, b0, b1);
+    }
+  }
+
+  // ---- merge the warps of this CTA ------------------------------------------
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  if (g < p.grp) {
+    if (t == 0) {
+      sm_m[warp][g] = m_run;
+      sm_l[warp][g] = l_run;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int dbase = (j & 7) + 64 * (j >> 3);
+      sm_o[warp][g][8 * (2 * t) + dbase] = o[j][0];
+      sm_o[warp][g][8 * (2 * t + 1) + dbase] = o[j][1];
+    }
+  }
+  __syncthreads();
+  for (int hh = 0; hh < p.grp; ++hh) {
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kAW; ++w) M = fmaxf(M, sm_m[w][hh]);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAW; ++w) {
+      const float f = exp2f(sm_m[w][hh] - M);
+      L += sm_l[w][hh] * f;
+      O += sm_o[w][hh][tid] * f;
+    }
+    const size_t row = ((size_t)b * p.Hq + (size_t)h * p.grp + hh) * p.S + s;
+    p.part_o[row * kHD + tid] = O;
+    if (tid == 0) {
+      p.part_ml[row * 2] = M;
+      p.part_ml[row * 2 + 1] = L;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kHD) attn_combine_kernel(const AttnParams p) {
+  const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  const int len = p.lens[b];
+  const int npages = min((len + 15) >> 4, p.max_pages);
+  const int ns = (npages + p.pps - 1) / p.pps;
+  const size_t row0 = ((size_t)b * p.Hq + head) * p.S;
+  float M = -INFINITY;
+  for (int s = 0; s < ns; ++s) M = fmaxf(M, p.part_ml[(row0 + s) * 2]);
+  float L = 0.f, O = 0.f;
+  for (int s = 0; s < ns; ++s) {
+    const float f = exp2f(p.part_ml[(row0 + s) * 2] - M);
+    L += p.part_ml[(row0 + s) * 2 + 1] * f;
+    O += p.part_o[(row0 + s) * kHD + d] * f;
+  }
+  p.out[((size_t)b * p.Hq + head) * kHD + d] = ns > 0 ? O / L : 0.f;
+}
+
+__global__ void kv_append_kernel(__half* pool, const float* k, const float* v, const int32_t* table,
+                                 const int32_t* pos, int B, int Hkv, int pages, int max_pages, int32_t* status) {
+  const int b = blockIdx.y, h = blockIdx.x, d = threadIdx.x;
+  const int ps = pos[b];
+  const int pg = ps >> 4;
+  if (pg >= max_pages) {
+    if (d == 0) atomicExch(status, 2);
+    return;
+  }
+  const int pid = table[(size_t)b * max_pages + pg];
+  if ((unsigned)pid >= (unsigned)pages) {
+    if (d == 0) atomicExch(status, 1);
+    return;
+  }
+  __half* base = pool + ((size_t)pid * Hkv + h) * (2 * 16 * kHD) + (ps & 15) * kHD + d;
+  base[0] = __float2half_rn(k[((size_t)b * Hkv + h) * kHD + d]);
+  base[16 * kHD] = __float2half_rn(v[((size_t)b * Hkv + h) * kHD + d]);
+}
+
+}  // namespace
+
+// Splits: enough CTAs to fill the machine several times over, at least one page per warp.
+static int pages_per_split(const qeng_ctx* ctx, int64_t B, int64_t Hkv, int64_t max_pages) {
+  int64_t target = (int64_t)ctx->sm_count * 8;
+  int64_t pps = (B * Hkv * max_pages + target - 1) / target;
+  pps = (pps + kAW - 1) / kAW * kAW;
+  if (pps < kAW) pps = kAW;
+  if (pps > 64) pps = 64;
+  return (int)pps;
+}
+
+// Grow the split scratch of the context to what a call of this shape needs.
+// The steady state never allocates; a growing call drains the device first.
+int32_t qeng_attn_reserve(qeng_ctx* ctx, int64_t B, int64_t Hq, int64_t Hkv, int64_t max_pages) {
+  const int pps = pages_per_split(ctx, B, Hkv, max_pages);
+  const int64_t S = (max_pages + pps - 1) / pps;
+  size_t need = (size_t)B * Hq * S * (kHD + 2) * sizeof(float);
+  if (need <= ctx->attn_scratch_bytes) return QENG_OK;
+  QENG_CUDA(ctx, cudaSetDevice(ctx->device));
+  QENG_CUDA(ctx, cudaDeviceSynchronize());
+  if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);
+  ctx->attn_scratch = nullptr;
+  ctx->attn_scratch_bytes = 0;
+  QENG_CUDA(ctx, cudaMalloc(&ctx->attn_scratch, need));
+  ctx->attn_scratch_bytes = need;
+  return QENG_OK;
+}
+
+extern "C" {
+
+int32_t qeng_kv_pool_create(qeng_ctx* ctx, int64_t pages, int64_t kv_heads, int64_t hd, qeng_kv_pool** out) {
+  if (!ctx || !out) return qeng_fail(ctx, QENG_ERR_ARG, "kv_pool_create: null argument");
+  *out = nullptr;
+  if (hd != kHD) return qeng_fail(ctx, QENG_ERR_SHAPE, "kv_pool_create: head_dim must be 128 (got %lld)", (long long)hd);
+  if (pages <= 0 || kv_heads <= 0) return qeng_fail(ctx, QENG_ERR_ARG, "kv_pool_create: pages and kv_heads must be positive");
+  QENG_CUDA(ctx, cudaSetDevice(ctx->device));
+  qeng_kv_pool* p = new qeng_kv_pool();
+  p->pages = pages; p->kv_heads = kv_heads; p->hd = hd; p->data = nullptr;
+  size_t bytes = (size_t)pages * kv_heads * 2 * 16 * hd * sizeof(__half);
+  cudaError_t e = cudaMalloc(&p->data, bytes);
+  if (e == cudaSuccess) e = cudaMemset(p->data, 0, bytes);
+  if (e != cudaSuccess) {
+    if (p->data) cudaFree(p->data);
+    delete p;
+    return qeng_fail(ctx, QENG_ERR_CUDA, "kv_pool_create: %s", cudaGetErrorString(e));
+  }
+  *out = p;
+  return QENG_OK;
+}
+
+int32_t qeng_kv_pool_free(qeng_ctx* ctx, qeng_kv_pool* pool) {
+  if (!pool) return QENG_OK;
+  if (ctx) cudaSetDevice(ctx->device);
+  if (pool->data) cudaFree(pool->data);
+  delete pool;
+  return QENG_OK;
+}
+
+void* qeng_kv_pool_data(const qeng_kv_pool* pool) { return pool ? pool->data : nullptr; }
+int64_t qeng_kv_pool_pages(const qeng_kv_pool* pool) { return pool ? pool->pages : 0; }
+
+int32_t qeng_kv_append(qeng_ctx* ctx, qeng_kv_pool* pool, const float* k, const float* v, const int32_t* page_table,
+                       int64_t max_pages, const int32_t* pos, int64_t B, void* stream) {
+  if (!ctx || !pool || !k || !v || !page_table || !pos) return qeng_fail(ctx, QENG_ERR_ARG, "kv_append: null argument");
+  if (B <= 0 || max_pages <= 0) return qeng_fail(ctx, QENG_ERR_ARG, "kv_append: B and max_pages must be positive");
+  dim3 grid((unsigned)pool->kv_heads, (unsigned)B);
+  kv_append_kernel<<<grid, kHD, 0, (cudaStream_t)stream>>>(pool->data, k, v, page_table, pos, (int)B,
+                                                           (int)pool->kv_heads, (int)pool->pages, (int)max_pages,
+                                                           ctx->status);
+  QENG_LAUNCH_CHECK(ctx);
+  return QENG_OK;
+}
+
+int32_t qeng_attn_decode(qeng_ctx* ctx, const qeng_kv_pool* pool, const uint16_t* q_f16, const int32_t* page_table,
+                         int64_t max_pages, const int32_t* lens, int64_t B, int64_t Hq, float scale, float* out,
+                         void* stream) {
+  if (!ctx || !pool || !q_f16 || !page_table || !lens || !out) return qeng_fail(ctx, QENG_ERR_ARG, "attn_decode: null argument");
+  if (B <= 0 || max_pages <= 0 || Hq <= 0) return qeng_fail(ctx, QENG_ERR_ARG, "attn_decode: B, Hq, max_pages must be positive");
+  if (Hq % pool->kv_heads != 0 || Hq / pool->kv_heads > 8)
+    return qeng_fail(ctx, QENG_ERR_SHAPE, "attn_decode: query heads per kv head must divide evenly and be <= 8");
+  if ((reinterpret_cast<uintptr_t>(q_f16) & 15) != 0) return qeng_fail(ctx, QENG_ERR_ALIGN, "attn_decode: q must be 16-byte aligned");
+  AttnParams p;
+  p.pool = pool->data; p.q = reinterpret_cast<const __half*>(q_f16);
+  p.table = page_table; p.lens = lens; p.out = out; p.status = ctx->status;
+  p.pages = (int)pool->pages; p.Hkv = (int)pool->kv_heads; p.Hq = (int)Hq; p.grp = (int)(Hq / pool->kv_heads);
+  p.max_pages = (int)max_pages;
+  p.pps = pages_per_split(ctx, B, pool->kv_heads, max_pages);
+  p.S = (int)((max_pages + p.pps - 1) / p.pps);
+  p.scale_log2 = scale * 1.4426950408889634f;
+  int32_t rc = qeng_attn_reserve(ctx, B, Hq, pool->kv_heads, max_pages);
+  if (rc != QENG_OK) return rc;
+  p.part_o = ctx->attn_scratch;
+  p.part_ml = ctx->attn_scratch + (size_t)B * Hq * p.S * kHD;
+  dim3 grid((unsigned)p.S, (unsigned)p.Hkv, (unsigned)B);
+  attn_decode_kernel<<<grid, kAW * 32, 0, (cudaStream_t)stream>>>(p);
+  QENG_LAUNCH_CHECK(ctx);
+  dim3 grid2((unsigned)Hq, (unsigned)B);
+  attn_combine_kernel<<<grid2, kHD, 0, (cudaStream_t)stream>>>(p);
+  QENG_LAUNCH_CHECK(ctx);
+  return QENG_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,575 @@
+// The layer executor: runs the decode loop
+//   embed -> per layer: norm, QKV, RoPE, KV append, attention, O proj (+residual),
+//            norm, gate/up (+SwiGLU), down (+residual) -> norm -> LM head -> greedy sample
+// over the kernels of this library.  One decode step is captured once into a
+// CUDA graph and replayed; positions, lengths and the sampled tokens live on the
+// device so that no host work sits between two steps.
+//
+// Fusions: RMSNorm into the activation staging of the following matmul, the
+// residual add and SwiGLU into the matmul epilogues, RoPE + f16 rounding + KV
+// append + q conversion into one small kernel.
+#include <math.h>
+#include <string.h>
+
+#include <vector>
+
+#include "qeng_internal.h"
+
+namespace {
+
+constexpr int kHD = 128;
+constexpr int kPage = 16;
+
+struct HostMat {
+  std::vector<uint8_t> q;
+  std::vector<uint16_t> s;
+  int64_t N = 0, K = 0;
+};
+
+struct Layer {
+  qeng_weight* wqkv = nullptr;
+  qeng_weight* wo = nullptr;
+  qeng_weight* wgu = nullptr;  // gate/up rows interleaved 8/8 per 16-row tile
+  qeng_weight* wdown = nullptr;
+  float* norm1 = nullptr;
+  float* norm2 = nullptr;
+  HostMat pend[7];  // host shards waiting for their fusion partners
+};
+
+// rows of q|k|v (f32, straight from the QKV matmul) -> rotated q as f16, rotated k and v
+// as f16 into the page pool at token index pos[row].
+__global__ void __launch_bounds__(256) rope_append_kernel(const float* __restrict__ qkv, const float* __restrict__ cs,
+                                                          const int32_t* __restrict__ pos,
+                                                          const int32_t* __restrict__ table, int max_pages, int pages,
+                                                          int Hq, int Hkv, int max_seq, __half* __restrict__ q16,
+                                                          __half* __restrict__ pool, int32_t* status) {
+  const int row = blockIdx.x;
+  const int ps = pos[row];
+  if (ps < 0 || ps >= max_seq || (ps >> 4) >= max_pages) {
+    if (threadIdx.x == 0) atomicExch(status, 2);
+    return;
+  }
+  const int pid = table[(size_t)row * max_pages + (ps >> 4)];
+  if ((unsigned)pid >= (unsigned)pages) {
+    if (threadIdx.x == 0) atomicExch(status, 1);
+    return;
+  }
+  const int nq = Hq * kHD, nkv = Hkv * kHD;
+  const float* src = qkv + (size_t)row * (nq + 2 * nkv);
+  const float* cosr = cs + (size_t)ps * kHD;  // [64 cos | 64 sin]
+  // rotated heads: Hq query heads then Hkv key heads, 64 pairs each
+  for (int idx = threadIdx.x; idx < (Hq + Hkv) * 64; idx += blockDim.x) {
+    const int h = idx >> 6, i = idx & 63;
+    const float c = cosr[i], s = cosr[64 + i];
+    const float a = src[h * kHD + i], b = src[h * kHD + i + 64];
+    const __half lo = __float2half_rn(a * c - b * s), hi = __float2half_rn(b * c + a * s);
+    if (h < Hq) {
+      q16[(size_t)row * nq + h * kHD + i] = lo;
+      q16[(size_t)row * nq + h * kHD + i + 64] = hi;
+    } else {
+      __half* kd = pool + ((size_t)pid * Hkv + (h - Hq)) * (2 * kPage * kHD) + (ps & 15) * kHD;
+      kd[i] = lo;
+      kd[i + 64] = hi;
+    }
+  }
+  for (int idx = threadIdx.x; idx < nkv; idx += blockDim.x) {
+    const int h = idx >> 7, i = idx & 127;
+    pool[((size_t)pid * Hkv + h) * (2 * kPage * kHD) + kPage * kHD + (ps & 15) * kHD + i] =
+        __float2half_rn(src[nq + nkv + idx]);
+  }
+}
+
+// End of a decode step: record the sampled tokens, move every sequence one token on.
+__global__ void advance_kernel(const int32_t* __restrict__ next, int32_t* pos, int32_t* lens, int32_t* out_tokens,
+                               int32_t* step, int B) {
+  const int b = threadIdx.x;
+  const int st = *step;
+  __syncthreads();
+  if (b < B) {
+    out_tokens[(size_t)st * B + b] = next[b];
+    pos[b] += 1;
+    lens[b] += 1;
+  }
+  if (b == 0) *step = st + 1;
+}
+
+}  // namespace
+
+struct qeng_decoder {
+  qeng_model_cfg cfg;
+  int Hq = 0, Hkv = 0, F = 0;  // local (per rank) head counts and FFN width
+  int nqkv = 0;
+  int max_pages = 0;           // pages per sequence
+  int64_t pages = 0;           // pages per layer pool
+  std::vector<Layer> layers;
+  uint16_t* emb = nullptr;
+  uint16_t* lm_head = nullptr;
+  float* final_norm = nullptr;
+  float* rope_cs = nullptr;    // [max_seq][64 cos | 64 sin]
+  __half* pool = nullptr;      // [layers][pages][Hkv][2][16][128]
+  qeng_kv_pool view;           // per-layer view handed to the attention entry point
+  // activations (rows = batch in decode, batch*T in prefill)
+  int64_t rows_cap = 0;
+  float *x = nullptr, *qkv = nullptr, *att = nullptr, *act = nullptr;
+  __half* q16 = nullptr;
+  int32_t *pos = nullptr, *lens = nullptr, *table = nullptr;  // per row
+  // decode state
+  float *xn = nullptr, *xlast = nullptr, *logits = nullptr;
+  int32_t *next = nullptr, *out_tokens = nullptr, *step = nullptr, *dec_table = nullptr;
+  int max_steps = 0;
+  int batch = 0;
+  std::vector<int32_t> len;  // host copy of sequence lengths
+  bool have_logits = false;
+  cudaStream_t stream = nullptr;
+  cudaStream_t own_stream = nullptr;
+  cudaGraphExec_t graph = nullptr;
+  int graph_batch = 0;
+  int launches = 0;
+};
+
+namespace {
+
+int32_t ensure_rows(qeng_ctx* ctx, qeng_decoder* d, int64_t rows) {
+  if (rows <= d->rows_cap) return QENG_OK;
+  QENG_CUDA(ctx, cudaDeviceSynchronize());
+  float** fb[] = {&d->x, &d->qkv, &d->att, &d->act};
+  for (auto p : fb)
+    if (*p) { cudaFree(*p); *p = nullptr; }
+  if (d->q16) { cudaFree(d->q16); d->q16 = nullptr; }
+  int32_t** ib[] = {&d->pos, &d->lens, &d->table};
+  for (auto p : ib)
+    if (*p) { cudaFree(*p); *p = nullptr; }
+  d->rows_cap = 0;
+  const int64_t dm = d->cfg.d_model;
+  QENG_CUDA(ctx, cudaMalloc(&d->x, rows * dm * 4));
+  QENG_CUDA(ctx, cudaMalloc(&d->qkv, rows * d->nqkv * 4));
+  QENG_CUDA(ctx, cudaMalloc(&d->att, rows * d->Hq * kHD * 4));
+  QENG_CUDA(ctx, cudaMalloc(&d->act, rows * d->F * 4));
+  QENG_CUDA(ctx, cudaMalloc(&d->q16, rows * d->Hq * kHD * 2));
+  QENG_CUDA(ctx, cudaMalloc(&d->pos, rows * 4));
+  QENG_CUDA(ctx, cudaMalloc(&d->lens, rows * 4));
+  QENG_CUDA(ctx, cudaMalloc(&d->table, rows * d->max_pages * 4));
+  d->rows_cap = rows;
+  return qeng_attn_reserve(ctx, rows, d->Hq, d->Hkv, d->max_pages);
+}
+
+// matmul over `rows` activation rows in chunks the decode kernel accepts
+int32_t mm(qeng_ctx* ctx, qeng_decoder* d, const qeng_weight* w, const float* x, int64_t ldx, int64_t rows, float* y,
+           int64_t ldy, const qeng_gemm_fuse& fuse, cudaStream_t st) {
+  for (int64_t m0 = 0; m0 < rows; m0 += 16) {
+    const int64_t mm_ = rows - m0 < 16 ? rows - m0 : 16;
+    qeng_gemm_fuse f = fuse;
+    if (f.resid) f.resid = fuse.resid + m0 * ldy;
+    int32_t rc = qeng_gemm_q4_decode(ctx, w, x + m0 * ldx, QENG_F32, mm_, ldx, y + m0 * ldy, ldy, true, f, st);
+    if (rc != QENG_OK) return rc;
+    d->launches++;
+  }
+  return QENG_OK;
+}
+
+// One layer over `rows` rows whose positions / lengths / page-table rows are on the device.
+int32_t run_layer(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, const int32_t* table, cudaStream_t st) {
+  Layer& L = d->layers[l];
+  if (!L.wqkv || !L.wo || !L.wgu || !L.wdown || !L.norm1 || !L.norm2)
+    return qeng_fail(ctx, QENG_ERR_STATE, "decoder: layer %d is not fully loaded", l);
+  const int64_t dm = d->cfg.d_model;
+  qeng_gemm_fuse f;
+  f.norm_gamma = L.norm1; f.norm_eps = d->cfg.rms_eps; f.epilogue = QENG_EPI_STORE;
+  int32_t rc = mm(ctx, d, L.wqkv, d->x, dm, rows, d->qkv, d->nqkv, f, st);
+  if (rc != QENG_OK) return rc;
+  __half* pool = d->pool + (size_t)l * d->pages * d->Hkv * 2 * kPage * kHD;
+  rope_append_kernel<<<(unsigned)rows, 256, 0, st>>>(d->qkv, d->rope_cs, d->pos, table, d->max_pages, (int)d->pages,
+                                                     d->Hq, d->Hkv, d->cfg.max_seq, d->q16, pool, ctx->status);
+  QENG_LAUNCH_CHECK(ctx);
+  d->launches++;
+  d->view.pages = d->pages; d->view.kv_heads = d->Hkv; d->view.hd = kHD; d->view.data = pool;
+  rc = qeng_attn_decode(ctx, &d->view, reinterpret_cast<const uint16_t*>(d->q16), table, d->max_pages, d->lens, rows,
+                        d->Hq, 1.0f / sqrtf((float)kHD), d->att, st);
+  if (rc != QENG_OK) return rc;
+  d->launches += 2;
+  qeng_gemm_fuse fo;
+  fo.epilogue = QENG_EPI_ACCUM;
+  rc = mm(ctx, d, L.wo, d->att, (int64_t)d->Hq * kHD, rows, d->x, dm, fo, st);
+  if (rc != QENG_OK) return rc;
+  qeng_gemm_fuse fg;
+  fg.norm_gamma = L.norm2; fg.norm_eps = d->cfg.rms_eps; fg.epilogue = QENG_EPI_SWIGLU;
+  rc = mm(ctx, d, L.wgu, d->x, dm, rows, d->act, d->F, fg, st);
+  if (rc != QENG_OK) return rc;
+  rc = mm(ctx, d, L.wdown, d->act, d->F, rows, d->x, dm, fo, st);
+  return rc;
+}
+
+int32_t tail(qeng_ctx* ctx, qeng_decoder* d, const float* x_last, int B, cudaStream_t st) {
+  int32_t rc = qeng_rmsnorm(ctx, x_last, d->final_norm, B, d->cfg.d_model, d->cfg.rms_eps, d->xn, st);
+  if (rc != QENG_OK) return rc;
+  rc = qeng_lm_head(ctx, d->lm_head, d->xn, B, d->cfg.d_model, d->cfg.vocab, d->logits, st);
+  if (rc != QENG_OK) return rc;
+  d->launches += 1 + (B + 3) / 4;
+  return QENG_OK;
+}
+
+// one decode step, all state on the device
+int32_t decode_step(qeng_ctx* ctx, qeng_decoder* d, cudaStream_t st) {
+  const int B = d->batch;
+  int32_t rc = qeng_argmax(ctx, d->logits, B, d->cfg.vocab, d->next, st);
+  if (rc != QENG_OK) return rc;
+  rc = qeng_embed(ctx, d->emb, d->next, B, d->cfg.d_model, d->cfg.vocab, d->x, st);
+  if (rc != QENG_OK) return rc;
+  d->launches += 2;
+  for (int l = 0; l < d->cfg.layers; ++l) {
+    rc = run_layer(ctx, d, l, B, d->dec_table, st);
+    if (rc != QENG_OK) return rc;
+  }
+  rc = tail(ctx, d, d->x, B, st);
+  if (rc != QENG_OK) return rc;
+  advance_kernel<<<1, 32 * ((B + 31) / 32), 0, st>>>(d->next, d->pos, d->lens, d->out_tokens, d->step, B);
+  QENG_LAUNCH_CHECK(ctx);
+  d->launches++;
+  return QENG_OK;
+}
+
+// shard of a full host matrix: rows [r0,r1) x columns [k0,k1)
+void take_shard(const uint8_t* q, const uint16_t* s, int64_t K, int64_t r0, int64_t r1, int64_t k0, int64_t k1,
+                HostMat& out) {
+  out.N = r1 - r0; out.K = k1 - k0;
+  out.q.resize((size_t)out.N * out.K);
+  out.s.resize((size_t)out.N * out.K / 32);
+  for (int64_t r = r0; r < r1; ++r) {
+    memcpy(&out.q[(size_t)(r - r0) * out.K], q + r * K + k0, (size_t)out.K);
+    memcpy(&out.s[(size_t)(r - r0) * (out.K / 32)], s + r * (K / 32) + k0 / 32, (size_t)(out.K / 32) * 2);
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t qeng_decoder_create(qeng_ctx* ctx, const qeng_model_cfg* cfg, qeng_decoder** out) {
+  if (!ctx || !cfg || !out) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_create: null argument");
+  *out = nullptr;
+  const int t = cfg->tp_world;
+  if (t < 1 || cfg->tp_rank < 0 || cfg->tp_rank >= t) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_create: bad tp rank/world");
+  if (cfg->head_dim != kHD) return qeng_fail(ctx, QENG_ERR_SHAPE, "decoder_create: head_dim must be 128");
+  if (cfg->layers < 1 || cfg->heads < 1 || cfg->kv_heads < 1 || cfg->heads % cfg->kv_heads != 0 ||
+      cfg->heads / cfg->kv_heads > 8)
+    return qeng_fail(ctx, QENG_ERR_SHAPE, "decoder_create: bad head counts");
+  if (cfg->kv_heads % t != 0 || cfg->ffn % (16 * t) != 0 || cfg->d_model % 32 != 0 || (cfg->ffn / t) % 32 != 0 ||
+      (cfg->heads * kHD / t) % 32 != 0)
+    return qeng_fail(ctx, QENG_ERR_SHAPE, "decoder_create: shapes do not shard evenly over %d ranks", t);
+  if (cfg->max_batch < 1 || cfg->max_batch > 16 || cfg->max_seq < 1)
+    return qeng_fail(ctx, QENG_ERR_SHAPE, "decoder_create: max_batch must be 1..16 and max_seq positive");
+  QENG_CUDA(ctx, cudaSetDevice(ctx->device));
+  qeng_decoder* d = new qeng_decoder();
+  d->cfg = *cfg;
+  d->Hq = cfg->heads / t; d->Hkv = cfg->kv_heads / t; d->F = cfg->ffn / t;
+  d->nqkv = (d->Hq + 2 * d->Hkv) * kHD;
+  d->max_pages = (cfg->max_seq + kPage - 1) / kPage;
+  d->pages = (int64_t)d->max_pages * cfg->max_batch;
+  d->layers.resize(cfg->layers);
+  d->max_steps = cfg->max_seq;
+  const int64_t dm = cfg->d_model;
+  const size_t pool_bytes = (size_t)cfg->layers * d->pages * d->Hkv * 2 * kPage * kHD * 2;
+  cudaError_t e = cudaMalloc(&d->pool, pool_bytes);
+  if (e == cudaSuccess) e = cudaMemset(d->pool, 0, pool_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&d->rope_cs, (size_t)cfg->max_seq * kHD * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&d->xn, (size_t)cfg->max_batch * dm * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&d->xlast, (size_t)cfg->max_batch * dm * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&d->logits, (size_t)cfg->max_batch * cfg->vocab * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&d->next, 64 * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&d->step, 4);
+  if (e == cudaSuccess) e = cudaMalloc(&d->out_tokens, (size_t)d->max_steps * cfg->max_batch * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&d->dec_table, (size_t)cfg->max_batch * d->max_pages * 4);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&d->own_stream, cudaStreamNonBlocking);
+  d->stream = d->own_stream;
+  if (e != cudaSuccess) {
+    qeng_decoder_free(ctx, d);
+    return qeng_fail(ctx, QENG_ERR_CUDA, "decoder_create: %s", cudaGetErrorString(e));
+  }
+  // rotary table in double, stored as f32: [pos][cos 0..63 | sin 0..63]
+  std::vector<float> cs((size_t)cfg->max_seq * kHD);
+  for (int p = 0; p < cfg->max_seq; ++p)
+    for (int i = 0; i < 64; ++i) {
+      const double ang = (double)p * pow((double)cfg->rope_base, -2.0 * i / (double)kHD);
+      cs[(size_t)p * kHD + i] = (float)cos(ang);
+      cs[(size_t)p * kHD + 64 + i] = (float)sin(ang);
+    }
+  e = cudaMemcpy(d->rope_cs, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice);
+  // page table: sequence b owns pages p*max_batch + b (interleaved, so the
+  // indirection is exercised)
+  std::vector<int32_t> tb((size_t)cfg->max_batch * d->max_pages);
+  for (int b = 0; b < cfg->max_batch; ++b)
+    for (int p = 0; p < d->max_pages; ++p) tb[(size_t)b * d->max_pages + p] = p * cfg->max_batch + b;
+  if (e == cudaSuccess) e = cudaMemcpy(d->dec_table, tb.data(), tb.size() * 4, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    qeng_decoder_free(ctx, d);
+    return qeng_fail(ctx, QENG_ERR_CUDA, "decoder_create: %s", cudaGetErrorString(e));
+  }
+  int32_t rc = ensure_rows(ctx, d, cfg->max_batch);
+  if (rc != QENG_OK) {
+    qeng_decoder_free(ctx, d);
+    return rc;
+  }
+  *out = d;
+  return QENG_OK;
+}
+
+int32_t qeng_decoder_free(qeng_ctx* ctx, qeng_decoder* d) {
+  if (!d) return QENG_OK;
+  if (ctx) cudaSetDevice(ctx->device);
+  cudaDeviceSynchronize();
+  if (d->graph) cudaGraphExecDestroy(d->graph);
+  for (auto& L : d->layers) {
+    qeng_weight_free(ctx, L.wqkv); qeng_weight_free(ctx, L.wo); qeng_weight_free(ctx, L.wgu); qeng_weight_free(ctx, L.wdown);
+    if (L.norm1) cudaFree(L.norm1);
+    if (L.norm2) cudaFree(L.norm2);
+  }
+  void* bufs[] = {d->emb, d->lm_head, d->final_norm, d->rope_cs, d->pool, d->x, d->qkv, d->att, d->act, d->q16,
+                  d->pos, d->lens, d->table, d->xn, d->xlast, d->logits, d->next, d->out_tokens, d->step, d->dec_table};
+  for (void* p : bufs)
+    if (p) cudaFree(p);
+  if (d->own_stream) cudaStreamDestroy(d->own_stream);
+  delete d;
+  return QENG_OK;
+}
+
+int32_t qeng_decoder_load_matrix(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, int32_t which, const uint8_t* q,
+                                 const uint16_t* s, int64_t N, int64_t K) {
+  if (!ctx || !d || !q || !s) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_load_matrix: null argument");
+  if (layer < 0 || layer >= d->cfg.layers || which < 0 || which > QENG_W_DOWN)
+    return qeng_fail(ctx, QENG_ERR_ARG, "decoder_load_matrix: bad layer/which");
+  const qeng_model_cfg& c = d->cfg;
+  const int t = c.tp_world, r = c.tp_rank;
+  const int64_t dm = c.d_model, nq = (int64_t)c.heads * kHD, nkv = (int64_t)c.kv_heads * kHD;
+  int64_t eN = 0, eK = 0;
+  switch (which) {
+    case QENG_W_Q: eN = nq; eK = dm; break;
+    case QENG_W_K: case QENG_W_V: eN = nkv; eK = dm; break;
+    case QENG_W_O: eN = dm; eK = nq; break;
+    case QENG_W_GATE: case QENG_W_UP: eN = c.ffn; eK = dm; break;
+    default: eN = dm; eK = c.ffn; break;
+  }
+  if (N != eN || K != eK)
+    return qeng_fail(ctx, QENG_ERR_SHAPE, "decoder_load_matrix: matrix %d must be [%lld,%lld], got [%lld,%lld]", which,
+                     (long long)eN, (long long)eK, (long long)N, (long long)K);
+  Layer& L = d->layers[layer];
+  HostMat& hm = L.pend[which];
+  const bool row_split = which == QENG_W_O || which == QENG_W_DOWN;  // split along K, partial sums
+  if (row_split) take_shard(q, s, K, 0, N, K / t * r, K / t * (r + 1), hm);
+  else take_shard(q, s, K, N / t * r, N / t * (r + 1), 0, K, hm);
+  int32_t rc = QENG_OK;
+  if (row_split) {
+    qeng_weight** dst = which == QENG_W_O ? &L.wo : &L.wdown;
+    qeng_weight_free(ctx, *dst); *dst = nullptr;
+    rc = qeng_weight_pack_q4(ctx, hm.q.data(), hm.s.data(), hm.N, hm.K, dst);
+    hm = HostMat();
+  } else if (which <= QENG_W_V) {
+    if (L.pend[QENG_W_Q].N && L.pend[QENG_W_K].N && L.pend[QENG_W_V].N) {
+      HostMat f;
+      f.K = dm;
+      for (int i = QENG_W_Q; i <= QENG_W_V; ++i) {
+        f.q.insert(f.q.end(), L.pend[i].q.begin(), L.pend[i].q.end());
+        f.s.insert(f.s.end(), L.pend[i].s.begin(), L.pend[i].s.end());
+        f.N += L.pend[i].N;
+        L.pend[i] = HostMat();
+      }
+      qeng_weight_free(ctx, L.wqkv); L.wqkv = nullptr;
+      rc = qeng_weight_pack_q4(ctx, f.q.data(), f.s.data(), f.N, f.K, &L.wqkv);
+    }
+  } else {
+    if (L.pend[QENG_W_GATE].N && L.pend[QENG_W_UP].N) {
+      // interleave: fused row 16*j + r = gate row 8*j + r (r < 8), up row 8*j + r - 8 (r >= 8)
+      const HostMat& G = L.pend[QENG_W_GATE];
+      const HostMat& U = L.pend[QENG_W_UP];
+      HostMat f;
+      f.N = 2 * G.N; f.K = dm;
+      f.q.resize((size_t)f.N * f.K);
+      f.s.resize((size_t)f.N * f.K / 32);
+      for (int64_t i = 0; i < G.N; ++i) {
+        const int64_t rg = (i / 8) * 16 + i % 8, ru = rg + 8;
+        memcpy(&f.q[(size_t)rg * dm], &G.q[(size_t)i * dm], (size_t)dm);
+        memcpy(&f.q[(size_t)ru * dm], &U.q[(size_t)i * dm], (size_t)dm);
+        memcpy(&f.s[(size_t)rg * (dm / 32)], &G.s[(size_t)i * (dm / 32)], (size_t)(dm / 32) * 2);
+        memcpy(&f.s[(size_t)ru * (dm / 32)], &U.s[(size_t)i * (dm / 32)], (size_t)(dm / 32) * 2);
+      }
+      L.pend[QENG_W_GATE] = HostMat();
+      L.pend[QENG_W_UP] = HostMat();
+      qeng_weight_free(ctx, L.wgu); L.wgu = nullptr;
+      rc = qeng_weight_pack_q4(ctx, f.q.data(), f.s.data(), f.N, f.K, &L.wgu);
+    }
+  }
+  if (d->graph) { cudaGraphExecDestroy(d->graph); d->graph = nullptr; }
+  return rc;
+}
+
+int32_t qeng_decoder_load_norm(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, int32_t which, const float* gamma) {
+  if (!ctx || !d || !gamma) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_load_norm: null argument");
+  if (layer < 0 || layer >= d->cfg.layers || which < 0 || which > 1) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_load_norm: bad layer/which");
+  float** dst = which == 0 ? &d->layers[layer].norm1 : &d->layers[layer].norm2;
+  if (!*dst) QENG_CUDA(ctx, cudaMalloc(dst, (size_t)d->cfg.d_model * 4));
+  QENG_CUDA(ctx, cudaMemcpy(*dst, gamma, (size_t)d->cfg.d_model * 4, cudaMemcpyHostToDevice));
+  return QENG_OK;
+}
+
+int32_t qeng_decoder_load_head(qeng_ctx* ctx, qeng_decoder* d, const uint16_t* emb, const uint16_t* lm_head,
+                               const float* final_gamma) {
+  if (!ctx || !d || !emb || !lm_head || !final_gamma) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_load_head: null argument");
+  const size_t n = (size_t)d->cfg.vocab * d->cfg.d_model;
+  if (!d->emb) QENG_CUDA(ctx, cudaMalloc(&d->emb, n * 2));
+  if (!d->lm_head) QENG_CUDA(ctx, cudaMalloc(&d->lm_head, n * 2));
+  if (!d->final_norm) QENG_CUDA(ctx, cudaMalloc(&d->final_norm, (size_t)d->cfg.d_model * 4));
+  QENG_CUDA(ctx, cudaMemcpy(d->emb, emb, n * 2, cudaMemcpyHostToDevice));
+  QENG_CUDA(ctx, cudaMemcpy(d->lm_head, lm_head, n * 2, cudaMemcpyHostToDevice));
+  QENG_CUDA(ctx, cudaMemcpy(d->final_norm, final_gamma, (size_t)d->cfg.d_model * 4, cudaMemcpyHostToDevice));
+  return QENG_OK;
+}
+
+int32_t qeng_decoder_reset(qeng_ctx* ctx, qeng_decoder* d, int32_t batch) {
+  if (!ctx || !d) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_reset: null argument");
+  if (batch < 1 || batch > d->cfg.max_batch) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_reset: batch outside 1..max_batch");
+  d->batch = batch;
+  d->len.assign(batch, 0);
+  d->have_logits = false;
+  return QENG_OK;
+}
+
+int32_t qeng_decoder_prefill(qeng_ctx* ctx, qeng_decoder* d, const int32_t* tokens, int32_t batch, int32_t T) {
+  if (!ctx || !d || !tokens) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_prefill: null argument");
+  if (batch != d->batch) return qeng_fail(ctx, QENG_ERR_STATE, "decoder_prefill: batch differs from the last reset");
+  if (T < 1) return qeng_fail(ctx, QENG_ERR_SHAPE, "decoder_prefill: empty prompt");
+  for (int b = 0; b < batch; ++b)
+    if (d->len[b] + T > d->cfg.max_seq) return qeng_fail(ctx, QENG_ERR_SHAPE, "decoder_prefill: prompt exceeds max_seq");
+  if (!d->emb) return qeng_fail(ctx, QENG_ERR_STATE, "decoder_prefill: embeddings not loaded");
+  QENG_CUDA(ctx, cudaSetDevice(ctx->device));
+  const int64_t rows = (int64_t)batch * T;
+  int32_t rc = ensure_rows(ctx, d, rows);
+  if (rc != QENG_OK) return rc;
+  cudaStream_t st = d->stream;
+  std::vector<int32_t> pos(rows), lens(rows), table((size_t)rows * d->max_pages);
+  for (int b = 0; b < batch; ++b)
+    for (int tt = 0; tt < T; ++tt) {
+      const int64_t r = (int64_t)b * T + tt;
+      pos[r] = d->len[b] + tt;
+      lens[r] = pos[r] + 1;
+      for (int p = 0; p < d->max_pages; ++p) table[(size_t)r * d->max_pages + p] = p * d->cfg.max_batch + b;
+    }
+  int32_t* dtok = nullptr;
+  QENG_CUDA(ctx, cudaMalloc(&dtok, rows * 4));
+  cudaMemcpyAsync(dtok, tokens, rows * 4, cudaMemcpyHostToDevice, st);
+  cudaMemcpyAsync(d->pos, pos.data(), rows * 4, cudaMemcpyHostToDevice, st);
+  cudaMemcpyAsync(d->lens, lens.data(), rows * 4, cudaMemcpyHostToDevice, st);
+  cudaMemcpyAsync(d->table, table.data(), table.size() * 4, cudaMemcpyHostToDevice, st);
+  rc = qeng_embed(ctx, d->emb, dtok, rows, d->cfg.d_model, d->cfg.vocab, d->x, st);
+  for (int l = 0; rc == QENG_OK && l < d->cfg.layers; ++l) rc = run_layer(ctx, d, l, rows, d->table, st);
+  if (rc == QENG_OK) {
+    // hidden state of the last prompt position of every sequence, gathered for the LM head
+    for (int b = 0; b < batch; ++b)
+      cudaMemcpyAsync(d->xlast + (size_t)b * d->cfg.d_model, d->x + ((size_t)b * T + T - 1) * d->cfg.d_model,
+                      (size_t)d->cfg.d_model * 4, cudaMemcpyDeviceToDevice, st);
+    rc = tail(ctx, d, d->xlast, batch, st);
+  }
+  cudaError_t e = cudaStreamSynchronize(st);
+  cudaFree(dtok);
+  if (rc != QENG_OK) return rc;
+  if (e != cudaSuccess) return qeng_fail(ctx, QENG_ERR_CUDA, "decoder_prefill: %s", cudaGetErrorString(e));
+  for (int b = 0; b < batch; ++b) d->len[b] += T;
+  d->have_logits = true;
+  return QENG_OK;
+}
+
+int32_t qeng_decoder_decode(qeng_ctx* ctx, qeng_decoder* d, int32_t steps, int32_t* out_tokens) {
+  if (!ctx || !d || !out_tokens) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_decode: null argument");
+  if (!d->have_logits) return qeng_fail(ctx, QENG_ERR_STATE, "decoder_decode: no logits yet (prefill first)");
+  if (steps < 1 || steps > d->max_steps) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_decode: bad step count");
+  const int B = d->batch;
+  for (int b = 0; b < B; ++b)
+    if (d->len[b] + steps > d->cfg.max_seq) return qeng_fail(ctx, QENG_ERR_SHAPE, "decoder_decode: would exceed max_seq");
+  QENG_CUDA(ctx, cudaSetDevice(ctx->device));
+  cudaStream_t st = d->stream;
+  {
+    int32_t rc = qeng_attn_reserve(ctx, B, d->Hq, d->Hkv, d->max_pages);  // never allocate inside the capture
+    if (rc != QENG_OK) return rc;
+  }
+  std::vector<int32_t> pos(B), lens(B);
+  for (int b = 0; b < B; ++b) { pos[b] = d->len[b]; lens[b] = d->len[b] + 1; }
+  QENG_CUDA(ctx, cudaMemcpyAsync(d->pos, pos.data(), B * 4, cudaMemcpyHostToDevice, st));
+  QENG_CUDA(ctx, cudaMemcpyAsync(d->lens, lens.data(), B * 4, cudaMemcpyHostToDevice, st));
+  QENG_CUDA(ctx, cudaMemsetAsync(d->step, 0, 4, st));
+  QENG_CUDA(ctx, cudaStreamSynchronize(st));
+  if (!d->graph || d->graph_batch != B) {
+    if (d->graph) { cudaGraphExecDestroy(d->graph); d->graph = nullptr; }
+    cudaGraph_t g = nullptr;
+    QENG_CUDA(ctx, cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+    d->launches = 0;
+    int32_t rc = decode_step(ctx, d, st);
+    cudaError_t e = cudaStreamEndCapture(st, &g);
+    if (rc != QENG_OK) { if (g) cudaGraphDestroy(g); return rc; }
+    if (e != cudaSuccess) return qeng_fail(ctx, QENG_ERR_CUDA, "decoder_decode: capture failed: %s", cudaGetErrorString(e));
+    e = cudaGraphInstantiate(&d->graph, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return qeng_fail(ctx, QENG_ERR_CUDA, "decoder_decode: instantiate failed: %s", cudaGetErrorString(e));
+    d->graph_batch = B;
+  }
+  for (int s = 0; s < steps; ++s) QENG_CUDA(ctx, cudaGraphLaunch(d->graph, st));
+  QENG_CUDA(ctx, cudaMemcpyAsync(out_tokens, d->out_tokens, (size_t)steps * B * 4, cudaMemcpyDeviceToHost, st));
+  int32_t status = 0;
+  QENG_CUDA(ctx, cudaMemcpyAsync(&status, ctx->status, 4, cudaMemcpyDeviceToHost, st));
+  QENG_CUDA(ctx, cudaStreamSynchronize(st));
+  for (int b = 0; b < B; ++b) d->len[b] += steps;
+  if (status != 0) {
+    cudaMemset(ctx->status, 0, 4);
+    return qeng_fail(ctx, QENG_ERR_DEVICE_STATUS, "decoder_decode: a kernel reported status %d (1 = page id outside the pool, 2 = position outside the cache, 3 = token id outside the vocabulary)", status);
+  }
+  // device order is [step][batch]; the caller gets [batch][steps]
+  std::vector<int32_t> tmp(out_tokens, out_tokens + (size_t)steps * B);
+  for (int s = 0; s < steps; ++s)
+    for (int b = 0; b < B; ++b) out_tokens[(size_t)b * steps + s] = tmp[(size_t)s * B + b];
+  return QENG_OK;
+}
+
+int32_t qeng_decoder_logits(qeng_ctx* ctx, qeng_decoder* d, float* out) {
+  if (!ctx || !d || !out) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_logits: null argument");
+  if (!d->have_logits) return qeng_fail(ctx, QENG_ERR_STATE, "decoder_logits: no logits yet");
+  QENG_CUDA(ctx, cudaSetDevice(ctx->device));
+  QENG_CUDA(ctx, cudaStreamSynchronize(d->stream));
+  QENG_CUDA(ctx, cudaMemcpy(out, d->logits, (size_t)d->batch * d->cfg.vocab * 4, cudaMemcpyDeviceToHost));
+  return QENG_OK;
+}
+
+int32_t qeng_decoder_layer(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, const float* x_in, const int32_t* pos,
+                           int32_t rows, float* x_out, void* stream) {
+  if (!ctx || !d || !x_in || !pos || !x_out) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_layer: null argument");
+  if (layer < 0 || layer >= d->cfg.layers) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_layer: bad layer");
+  if (rows < 1 || rows > d->cfg.max_seq) return qeng_fail(ctx, QENG_ERR_SHAPE, "decoder_layer: bad row count");
+  QENG_CUDA(ctx, cudaSetDevice(ctx->device));
+  int32_t rc = ensure_rows(ctx, d, rows);
+  if (rc != QENG_OK) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  // all rows belong to sequence 0 (a prompt chunk or a single step)
+  std::vector<int32_t> lens(rows), table((size_t)rows * d->max_pages);
+  for (int r = 0; r < rows; ++r) {
+    if (pos[r] < 0 || pos[r] >= d->cfg.max_seq) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_layer: position outside the cache");
+    lens[r] = pos[r] + 1;
+    for (int p = 0; p < d->max_pages; ++p) table[(size_t)r * d->max_pages + p] = p * d->cfg.max_batch;
+  }
+  QENG_CUDA(ctx, cudaMemcpyAsync(d->pos, pos, rows * 4, cudaMemcpyHostToDevice, st));
+  QENG_CUDA(ctx, cudaMemcpyAsync(d->lens, lens.data(), rows * 4, cudaMemcpyHostToDevice, st));
+  QENG_CUDA(ctx, cudaMemcpyAsync(d->table, table.data(), table.size() * 4, cudaMemcpyHostToDevice, st));
+  QENG_CUDA(ctx, cudaMemcpyAsync(d->x, x_in, (size_t)rows * d->cfg.d_model * 4, cudaMemcpyDeviceToDevice, st));
+  rc = run_layer(ctx, d, layer, rows, d->table, st);
+  if (rc != QENG_OK) return rc;
+  QENG_CUDA(ctx, cudaMemcpyAsync(x_out, d->x, (size_t)rows * d->cfg.d_model * 4, cudaMemcpyDeviceToDevice, st));
+  QENG_CUDA(ctx, cudaStreamSynchronize(st));  // host staging buffers go out of scope
+  return QENG_OK;
+}
+
+int32_t qeng_decoder_set_stream(qeng_ctx* ctx, qeng_decoder* d, void* stream) {
+  if (!ctx || !d) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_set_stream: null argument");
+  QENG_CUDA(ctx, cudaSetDevice(ctx->device));
+  QENG_CUDA(ctx, cudaStreamSynchronize(d->stream));
+  d->stream = stream ? (cudaStream_t)stream : d->own_stream;
+  return QENG_OK;
+}
+
+int32_t qeng_decoder_launches_per_step(const qeng_decoder* d) { return d ? d->launches : 0; }
+
+}  // extern "C"

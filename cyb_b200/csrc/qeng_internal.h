@@ -1,0 +1,83 @@
+// Internal declarations shared by the translation units of libqeng.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <string>
+
+#include "../../include/qeng.h"
+
+// Device layout of a 4-bit block weight W[N,K] ("tile16"):
+//  * rows are grouped in tiles of 16, K in chunks of 64 (two 32-blocks);
+//    Kp = K rounded up to 64, the padding block has code 0 and scale 0;
+//  * nibble plane: [tile][chunk][lane 0..31] one uint4 per lane; with
+//    g = lane/4, t = lane%4 the four words are
+//       .x = row g   , block 2c      .y = row g+8 , block 2c
+//       .z = row g   , block 2c+1    .w = row g+8 , block 2c+1
+//    and each word holds the codes of k = 32*block + 8*t + j in nibble j
+//    (bits 4j..4j+3).  One warp-wide 128-bit load therefore fetches 512
+//    contiguous bytes and every lane receives exactly the A-fragment words of
+//    an m16n8k16 MMA over that chunk;
+//  * scale plane: [tile][chunk][g 0..7] one uint2 = four f16:
+//       (row g, blk 2c), (row g+8, blk 2c), (row g, blk 2c+1), (row g+8, blk 2c+1).
+struct qeng_weight {
+  int64_t N, K;        // logical shape
+  int64_t ntiles;      // N / 16
+  int64_t nchunks;     // Kp / 64
+  uint4* qs;           // nibble plane, ntiles*nchunks*32 uint4
+  uint2* sc;           // scale plane,  ntiles*nchunks*8 uint2
+  int64_t bytes;       // device bytes held
+};
+
+struct qeng_kv_pool {
+  int64_t pages, kv_heads, hd;
+  __half* data;        // [pages][kv_heads][2][16][hd]
+};
+
+struct qeng_ctx {
+  int device = 0;
+  int sm_count = 0;
+  std::string err;
+  // scratch for split-KV attention partials and device status words
+  float* attn_scratch = nullptr;
+  size_t attn_scratch_bytes = 0;
+  int32_t* status = nullptr;  // device status word (0 = ok)
+};
+
+int32_t qeng_fail(qeng_ctx* ctx, int32_t code, const char* fmt, ...);
+
+#define QENG_CUDA(ctx, expr)                                                              \
+  do {                                                                                    \
+    cudaError_t e__ = (expr);                                                             \
+    if (e__ != cudaSuccess)                                                               \
+      return qeng_fail(ctx, QENG_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                \
+                       cudaGetErrorString(e__), __FILE__, __LINE__);                      \
+  } while (0)
+
+#define QENG_LAUNCH_CHECK(ctx)                                                            \
+  do {                                                                                    \
+    cudaError_t e__ = cudaGetLastError();                                                 \
+    if (e__ != cudaSuccess)                                                               \
+      return qeng_fail(ctx, QENG_ERR_CUDA, "kernel launch failed: %s (%s:%d)",            \
+                       cudaGetErrorString(e__), __FILE__, __LINE__);                      \
+  } while (0)
+
+// ---- fused entry used by the executor (gemv_q4.cu) -------------------------
+struct qeng_gemm_fuse {
+  const float* norm_gamma = nullptr;  // if set: x is RMS-normalised (gain gamma) while it is staged
+  float norm_eps = 0.f;
+  int epilogue = 0;                   // see QENG_EPI_*
+  const float* resid = nullptr;       // QENG_EPI_RESID: y = resid + x.W^T
+};
+// SWIGLU: rows g (gate) and g+8 (up) of every 16-row tile are combined into one
+// output y[8*tile + g] = silu(gate) * up, so y has N/2 columns.
+enum { QENG_EPI_STORE = 0, QENG_EPI_ACCUM = 1, QENG_EPI_RESID = 2, QENG_EPI_SWIGLU = 3 };
+
+int32_t qeng_gemm_q4_decode(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t x_dtype,
+                            int64_t M, int64_t ldx, float* y, int64_t ldy, bool split_f32,
+                            const qeng_gemm_fuse& fuse, cudaStream_t stream);
+
+// attn_decode.cu: size the context's split scratch for a shape (may allocate; never call while capturing)
+int32_t qeng_attn_reserve(qeng_ctx* ctx, int64_t B, int64_t Hq, int64_t Hkv, int64_t max_pages);

@@ -1,0 +1,404 @@
+"""ctypes binding of libqeng (include/qeng.h) — the same entry points a Rust
+host would bind with ``extern "C"``.  PyTorch is used only to own device memory
+and streams; every computation goes through the C ABI into the CUDA library.
+
+There is no CPU fallback: if the library is missing, importing this module
+raises; if no B200 is visible, ``Context()`` raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import re
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "_lib", "libqeng.so")
+HEADER_PATH = os.path.join(_HERE, "..", "include", "qeng.h")
+
+F32, F16, BF16 = 0, 1, 2
+GEMM_ACCUMULATE, GEMM_FAST_F16 = 1, 2
+W_Q, W_K, W_V, W_O, W_GATE, W_UP, W_DOWN = range(7)
+
+ERRORS = {0: "OK", -1: "ERR_ARG", -2: "ERR_SHAPE", -3: "ERR_ALIGN", -4: "ERR_CUDA", -5: "ERR_NCCL",
+          -6: "ERR_TIMEOUT", -7: "ERR_DEVICE_STATUS", -8: "ERR_STATE"}
+
+
+class QengError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__("qeng %s (%d): %s" % (ERRORS.get(code, "?"), code, msg))
+        self.code = code
+
+
+def declared_symbols(header=HEADER_PATH):
+    """Names of all functions include/qeng.h declares."""
+    text = open(header).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(qeng_[a-z0-9_]+)\s*\(", text)))
+
+
+def load_library(path=LIB_PATH):
+    if not os.path.exists(path):
+        raise ImportError("libqeng.so is not built (%s): run `python -m cyb_b200.build`; there is no CPU fallback" % path)
+    return C.CDLL(path)
+
+
+_lib = load_library()
+
+_vp, _i32, _i64, _f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float
+
+
+class ModelCfg(C.Structure):
+    _fields_ = [("layers", _i32), ("d_model", _i32), ("ffn", _i32), ("heads", _i32), ("kv_heads", _i32),
+                ("head_dim", _i32), ("vocab", _i32), ("rms_eps", _f32), ("rope_base", _f32),
+                ("max_batch", _i32), ("max_seq", _i32), ("tp_rank", _i32), ("tp_world", _i32)]
+
+
+def _sig(name, res, *args):
+    f = getattr(_lib, name)
+    f.restype = res
+    f.argtypes = list(args)
+    return f
+
+
+_sig("qeng_version", _i32)
+_sig("qeng_create", _i32, _i32, C.POINTER(_vp))
+_sig("qeng_destroy", _i32, _vp)
+_sig("qeng_last_error", C.c_char_p, _vp)
+_sig("qeng_device_status", _i32, _vp)
+_sig("qeng_sm_count", _i32, _vp)
+_sig("qeng_weight_pack_q4", _i32, _vp, _vp, _vp, _i64, _i64, C.POINTER(_vp))
+_sig("qeng_weight_unpack_q4", _i32, _vp, _vp, _vp, _vp)
+_sig("qeng_weight_dequant_f32", _i32, _vp, _vp, _vp, _vp)
+_sig("qeng_weight_free", _i32, _vp, _vp)
+_sig("qeng_weight_rows", _i64, _vp)
+_sig("qeng_weight_cols", _i64, _vp)
+_sig("qeng_weight_device_bytes", _i64, _vp)
+_sig("qeng_gemm_q4", _i32, _vp, _vp, _vp, _i32, _i64, _i64, _vp, _i64, _i32, _vp)
+_sig("qeng_gemv_q4", _i32, _vp, _vp, _vp, _vp, _vp)
+_sig("qeng_rmsnorm", _i32, _vp, _vp, _vp, _i64, _i64, _f32, _vp, _vp)
+_sig("qeng_rope", _i32, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _vp)
+_sig("qeng_swiglu", _i32, _vp, _vp, _vp, _i64, _vp, _vp)
+_sig("qeng_add", _i32, _vp, _vp, _vp, _i64, _vp, _vp)
+_sig("qeng_embed", _i32, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp)
+_sig("qeng_lm_head", _i32, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp)
+_sig("qeng_argmax", _i32, _vp, _vp, _i64, _i64, _vp, _vp)
+_sig("qeng_kv_pool_create", _i32, _vp, _i64, _i64, _i64, C.POINTER(_vp))
+_sig("qeng_kv_pool_free", _i32, _vp, _vp)
+_sig("qeng_kv_pool_data", _vp, _vp)
+_sig("qeng_kv_pool_pages", _i64, _vp)
+_sig("qeng_kv_append", _i32, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp)
+_sig("qeng_attn_decode", _i32, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _f32, _vp, _vp)
+_sig("qeng_decoder_create", _i32, _vp, C.POINTER(ModelCfg), C.POINTER(_vp))
+_sig("qeng_decoder_free", _i32, _vp, _vp)
+_sig("qeng_decoder_load_matrix", _i32, _vp, _vp, _i32, _i32, _vp, _vp, _i64, _i64)
+_sig("qeng_decoder_load_norm", _i32, _vp, _vp, _i32, _i32, _vp)
+_sig("qeng_decoder_load_head", _i32, _vp, _vp, _vp, _vp, _vp)
+_sig("qeng_decoder_reset", _i32, _vp, _vp, _i32)
+_sig("qeng_decoder_prefill", _i32, _vp, _vp, _vp, _i32, _i32)
+_sig("qeng_decoder_decode", _i32, _vp, _vp, _i32, _vp)
+_sig("qeng_decoder_logits", _i32, _vp, _vp, _vp)
+_sig("qeng_decoder_layer", _i32, _vp, _vp, _i32, _vp, _vp, _i32, _vp, _vp)
+_sig("qeng_decoder_set_stream", _i32, _vp, _vp, _vp)
+_sig("qeng_decoder_launches_per_step", _i32, _vp)
+
+
+def _np_ptr(a):
+    return a.ctypes.data_as(_vp)
+
+
+def _dev_ptr(t):
+    return _vp(t.data_ptr())
+
+
+def _cur_stream():
+    import torch
+    return _vp(torch.cuda.current_stream().cuda_stream)
+
+
+class Context:
+    """One engine context on one CUDA device."""
+
+    def __init__(self, device=0):
+        h = _vp()
+        rc = _lib.qeng_create(device, C.byref(h))
+        if rc != 0:
+            raise QengError(rc, "qeng_create failed (no B200 visible, or device index out of range)")
+        self.h = h
+        self.device = device
+
+    def close(self):
+        if self.h:
+            _lib.qeng_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def check(self, rc):
+        if rc != 0:
+            raise QengError(rc, _lib.qeng_last_error(self.h).decode())
+
+    @property
+    def sm_count(self):
+        return _lib.qeng_sm_count(self.h)
+
+    def device_status(self):
+        self.check(_lib.qeng_device_status(self.h))
+
+    # ---- weights ----------------------------------------------------------
+    def pack_q4(self, q, s):
+        """q uint8 [N,K] codes 0..15, s float16 [N,K/32] (host numpy)."""
+        q = np.ascontiguousarray(q, dtype=np.uint8)
+        s = np.ascontiguousarray(s, dtype=np.float16)
+        n, k = q.shape
+        if s.shape != (n, k // 32):
+            raise QengError(-2, "scale shape %s does not match codes %s" % (s.shape, q.shape))
+        h = _vp()
+        self.check(_lib.qeng_weight_pack_q4(self.h, _np_ptr(q), _np_ptr(s), n, k, C.byref(h)))
+        return Weight(self, h)
+
+    # ---- ops (torch CUDA tensors in, torch CUDA tensors out) ---------------
+    def gemm_q4(self, w, x, out=None, flags=0):
+        import torch
+        dt = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}[x.dtype]
+        assert x.is_cuda and x.dim() == 2 and x.stride(1) == 1
+        m = x.shape[0]
+        if out is None:
+            out = torch.empty((m, w.rows), dtype=torch.float32, device=x.device)
+        self.check(_lib.qeng_gemm_q4(self.h, w.h, _dev_ptr(x), dt, m, x.stride(0), _dev_ptr(out), out.stride(0), flags,
+                                     _cur_stream()))
+        return out
+
+    def gemv_q4(self, w, x, out=None):
+        import torch
+        assert x.is_cuda and x.dtype == torch.float32 and x.is_contiguous()
+        if out is None:
+            out = torch.empty((w.rows,), dtype=torch.float32, device=x.device)
+        self.check(_lib.qeng_gemv_q4(self.h, w.h, _dev_ptr(x), _dev_ptr(out), _cur_stream()))
+        return out
+
+    def rmsnorm(self, x, gamma, eps):
+        import torch
+        y = torch.empty_like(x)
+        self.check(_lib.qeng_rmsnorm(self.h, _dev_ptr(x), _dev_ptr(gamma), x.shape[0], x.shape[1], eps, _dev_ptr(y),
+                                     _cur_stream()))
+        return y
+
+    def rope_(self, x, pos, base):
+        m, h, hd = x.shape
+        self.check(_lib.qeng_rope(self.h, _dev_ptr(x), _dev_ptr(pos), m, h, hd, base, _cur_stream()))
+        return x
+
+    def swiglu(self, gate, up):
+        import torch
+        y = torch.empty_like(gate)
+        self.check(_lib.qeng_swiglu(self.h, _dev_ptr(gate), _dev_ptr(up), gate.numel(), _dev_ptr(y), _cur_stream()))
+        return y
+
+    def add(self, a, b):
+        import torch
+        y = torch.empty_like(a)
+        self.check(_lib.qeng_add(self.h, _dev_ptr(a), _dev_ptr(b), a.numel(), _dev_ptr(y), _cur_stream()))
+        return y
+
+    def embed(self, table_bf16, tokens):
+        import torch
+        v, d = table_bf16.shape
+        x = torch.empty((tokens.numel(), d), dtype=torch.float32, device=tokens.device)
+        self.check(_lib.qeng_embed(self.h, _dev_ptr(table_bf16), _dev_ptr(tokens), tokens.numel(), d, v, _dev_ptr(x),
+                                   _cur_stream()))
+        return x
+
+    def lm_head(self, table_bf16, x):
+        import torch
+        v, d = table_bf16.shape
+        out = torch.empty((x.shape[0], v), dtype=torch.float32, device=x.device)
+        self.check(_lib.qeng_lm_head(self.h, _dev_ptr(table_bf16), _dev_ptr(x), x.shape[0], d, v, _dev_ptr(out),
+                                     _cur_stream()))
+        return out
+
+    def argmax(self, logits):
+        import torch
+        idx = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+        self.check(_lib.qeng_argmax(self.h, _dev_ptr(logits), logits.shape[0], logits.shape[1], _dev_ptr(idx),
+                                    _cur_stream()))
+        return idx
+
+    # ---- KV cache ----------------------------------------------------------
+    def kv_pool(self, pages, kv_heads, hd=128):
+        h = _vp()
+        self.check(_lib.qeng_kv_pool_create(self.h, pages, kv_heads, hd, C.byref(h)))
+        return KVPool(self, h, pages, kv_heads, hd)
+
+    def kv_append(self, pool, k, v, table, pos):
+        self.check(_lib.qeng_kv_append(self.h, pool.h, _dev_ptr(k), _dev_ptr(v), _dev_ptr(table), table.shape[1],
+                                       _dev_ptr(pos), pos.numel(), _cur_stream()))
+
+    def attn_decode(self, pool, q, table, lens, scale=None):
+        import torch
+        b, hq, hd = q.shape
+        assert q.dtype == torch.float16 and q.is_contiguous()
+        out = torch.empty((b, hq, hd), dtype=torch.float32, device=q.device)
+        scale = float(hd) ** -0.5 if scale is None else scale
+        self.check(_lib.qeng_attn_decode(self.h, pool.h, _dev_ptr(q), _dev_ptr(table), table.shape[1], _dev_ptr(lens),
+                                         b, hq, scale, _dev_ptr(out), _cur_stream()))
+        return out
+
+    def decoder(self, **kw):
+        return Decoder(self, **kw)
+
+
+class Weight:
+    def __init__(self, ctx, h):
+        self.ctx, self.h = ctx, h
+        self.rows = _lib.qeng_weight_rows(h)
+        self.cols = _lib.qeng_weight_cols(h)
+        self.device_bytes = _lib.qeng_weight_device_bytes(h)
+
+    def unpack(self):
+        q = np.empty((self.rows, self.cols), np.uint8)
+        s = np.empty((self.rows, self.cols // 32), np.float16)
+        self.ctx.check(_lib.qeng_weight_unpack_q4(self.ctx.h, self.h, _np_ptr(q), _np_ptr(s)))
+        return q, s
+
+    def dequant(self):
+        import torch
+        out = torch.empty((self.rows, self.cols), dtype=torch.float32, device="cuda:%d" % self.ctx.device)
+        self.ctx.check(_lib.qeng_weight_dequant_f32(self.ctx.h, self.h, _dev_ptr(out), _cur_stream()))
+        return out
+
+    def free(self):
+        if self.h:
+            _lib.qeng_weight_free(self.ctx.h, self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            if self.ctx.h:
+                self.free()
+        except Exception:
+            pass
+
+
+class KVPool:
+    def __init__(self, ctx, h, pages, kv_heads, hd):
+        self.ctx, self.h, self.pages, self.kv_heads, self.hd = ctx, h, pages, kv_heads, hd
+
+    def tensor(self):
+        """The pool's storage as a torch f16 view [pages, kv_heads, 2, 16, hd]."""
+        import torch
+        n = self.pages * self.kv_heads * 2 * 16 * self.hd
+        ptr = _lib.qeng_kv_pool_data(self.h)
+        iface = {"shape": (n,), "typestr": "<f2", "data": (ptr, False), "version": 2}
+
+        class _Holder:
+            __cuda_array_interface__ = iface
+        return torch.as_tensor(_Holder(), device="cuda:%d" % self.ctx.device).view(self.pages, self.kv_heads, 2, 16, self.hd)
+
+    def free(self):
+        if self.h:
+            _lib.qeng_kv_pool_free(self.ctx.h, self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            if self.ctx.h:
+                self.free()
+        except Exception:
+            pass
+
+
+class Decoder:
+    """The layer executor behind the C ABI (qeng_decoder_*)."""
+
+    def __init__(self, ctx, layers, d_model, ffn, heads, kv_heads, vocab, head_dim=128, rms_eps=1e-5,
+                 rope_base=10000.0, max_batch=1, max_seq=1024, tp_rank=0, tp_world=1):
+        self.ctx = ctx
+        self.cfg = ModelCfg(layers, d_model, ffn, heads, kv_heads, head_dim, vocab, rms_eps, rope_base, max_batch,
+                            max_seq, tp_rank, tp_world)
+        h = _vp()
+        ctx.check(_lib.qeng_decoder_create(ctx.h, C.byref(self.cfg), C.byref(h)))
+        self.h = h
+        self.batch = 0
+
+    def load_matrix(self, layer, which, q, s):
+        q = np.ascontiguousarray(q, dtype=np.uint8)
+        s = np.ascontiguousarray(s, dtype=np.float16)
+        self.ctx.check(_lib.qeng_decoder_load_matrix(self.ctx.h, self.h, layer, which, _np_ptr(q), _np_ptr(s),
+                                                     q.shape[0], q.shape[1]))
+
+    def load_norm(self, layer, which, gamma):
+        g = np.ascontiguousarray(gamma, dtype=np.float32)
+        self.ctx.check(_lib.qeng_decoder_load_norm(self.ctx.h, self.h, layer, which, _np_ptr(g)))
+
+    def load_head(self, emb_bits, lm_bits, final_gamma):
+        e = np.ascontiguousarray(emb_bits, dtype=np.uint16)
+        l = np.ascontiguousarray(lm_bits, dtype=np.uint16)
+        g = np.ascontiguousarray(final_gamma, dtype=np.float32)
+        self.ctx.check(_lib.qeng_decoder_load_head(self.ctx.h, self.h, _np_ptr(e), _np_ptr(l), _np_ptr(g)))
+
+    def reset(self, batch):
+        self.ctx.check(_lib.qeng_decoder_reset(self.ctx.h, self.h, batch))
+        self.batch = batch
+
+    def prefill(self, tokens):
+        t = np.ascontiguousarray(tokens, dtype=np.int32)
+        self.ctx.check(_lib.qeng_decoder_prefill(self.ctx.h, self.h, _np_ptr(t), t.shape[0], t.shape[1]))
+
+    def decode(self, steps):
+        out = np.empty((self.batch, steps), np.int32)
+        self.ctx.check(_lib.qeng_decoder_decode(self.ctx.h, self.h, steps, _np_ptr(out)))
+        return out
+
+    def logits(self):
+        out = np.empty((self.batch, self.cfg.vocab), np.float32)
+        self.ctx.check(_lib.qeng_decoder_logits(self.ctx.h, self.h, _np_ptr(out)))
+        return out
+
+    def layer(self, layer, x, pos):
+        import torch
+        out = torch.empty_like(x)
+        p = np.ascontiguousarray(pos, dtype=np.int32)
+        self.ctx.check(_lib.qeng_decoder_layer(self.ctx.h, self.h, layer, _dev_ptr(x), _np_ptr(p), x.shape[0],
+                                               _dev_ptr(out), _cur_stream()))
+        return out
+
+    def use_current_stream(self):
+        self.ctx.check(_lib.qeng_decoder_set_stream(self.ctx.h, self.h, _cur_stream()))
+
+    @property
+    def launches_per_step(self):
+        return _lib.qeng_decoder_launches_per_step(self.h)
+
+    def free(self):
+        if self.h:
+            _lib.qeng_decoder_free(self.ctx.h, self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            if self.ctx.h:
+                self.free()
+        except Exception:
+            pass
+
+
+def load_decoder_weights(dec, W, cfg):
+    """Feed a weight dict into a Decoder: W["layers"][l][name] = (codes, scales)
+    for name in wq wk wv wo wgate wup wdown, norm1/norm2 gains, and bf16-valued
+    f32 tables W["emb"], W["lm_head"], gain W["final_norm"]."""
+    names = ["wq", "wk", "wv", "wo", "wgate", "wup", "wdown"]
+    for l, lw in enumerate(W["layers"]):
+        for i, nm in enumerate(names):
+            dec.load_matrix(l, i, *lw[nm])
+        dec.load_norm(l, 0, lw["norm1"])
+        dec.load_norm(l, 1, lw["norm2"])
+
+    def bits(x):
+        return (np.ascontiguousarray(x, dtype=np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    dec.load_head(bits(W["emb"]), bits(W["lm_head"]), W["final_norm"])

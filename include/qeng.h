@@ -1,0 +1,194 @@
+/* qeng — C ABI of the B200 (sm_100a) engine for cyb's local-LLM hot path.
+ *
+ * This is the surface a Rust host binds with `extern "C"`.  cyb reaches its
+ * model runtime through soma-kernel -> glia `run` (shell/Cargo.toml:34,
+ * Cargo.lock:8444-8462, 9091-9101); `run`'s per-backend operator set executes
+ * the loop "embed -> per layer: norm, QKV, RoPE, KV cache, attention, O proj,
+ * norm, FFN -> LM head -> sample" (decide/pipeline.md:51).  Each entry point
+ * below replaces one operator of that loop (or the whole loop) on a B200.
+ *
+ * Conventions
+ *  - every call returns an int32 status (QENG_OK = 0, negative = error) and
+ *    never throws or aborts; qeng_last_error() gives the text of the last
+ *    failure on that context;
+ *  - a context is bound to one CUDA device and is used by one host thread at a
+ *    time; one context per GPU for tensor parallelism;
+ *  - activation / output pointers are DEVICE pointers owned by the caller;
+ *    packed weights, KV pools and decoders are opaque handles owned by the
+ *    engine; `stream` is a cudaStream_t passed as void* (NULL = default
+ *    stream); work is asynchronous on that stream unless stated otherwise;
+ *  - there is no CPU fallback: an unsupported shape is an error.
+ */
+#ifndef QENG_H_
+#define QENG_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  QENG_OK = 0,
+  QENG_ERR_ARG = -1,     /* null pointer, bad enum, value out of range */
+  QENG_ERR_SHAPE = -2,   /* shape the kernels do not support */
+  QENG_ERR_ALIGN = -3,   /* pointer or leading dimension not aligned */
+  QENG_ERR_CUDA = -4,    /* a CUDA runtime call failed */
+  QENG_ERR_NCCL = -5,    /* an NCCL call failed */
+  QENG_ERR_TIMEOUT = -6, /* a bounded device-side wait ran out */
+  QENG_ERR_DEVICE_STATUS = -7, /* a kernel reported an error through its status word */
+  QENG_ERR_STATE = -8    /* call not valid in the object's current state */
+};
+
+/* element types of activation buffers */
+enum { QENG_F32 = 0, QENG_F16 = 1, QENG_BF16 = 2 };
+
+/* flags of qeng_gemm_q4 */
+enum {
+  QENG_GEMM_ACCUMULATE = 1, /* y += x.W^T instead of y = x.W^T (fused residual add) */
+  QENG_GEMM_FAST_F16 = 2    /* f32 activations are rounded to f16 once instead of
+                               being split into two f16 terms (halves tensor work,
+                               costs ~2e-4 of the error budget) */
+};
+
+typedef struct qeng_ctx qeng_ctx;
+typedef struct qeng_weight qeng_weight;
+typedef struct qeng_kv_pool qeng_kv_pool;
+typedef struct qeng_decoder qeng_decoder;
+
+/* ---- context (replaces the backend object glia `run` creates per device;
+ *      named "cpu . wgpu . honeycrisp" in decide/model-lifecycle.md:25) ------- */
+int32_t qeng_version(void);
+int32_t qeng_create(int32_t device, qeng_ctx** out);
+int32_t qeng_destroy(qeng_ctx* ctx);
+const char* qeng_last_error(const qeng_ctx* ctx);
+/* Drain the device, read and clear the status word kernels write when they meet a
+ * malformed input (page id outside the pool, position outside the cache, token
+ * outside the vocabulary): QENG_OK or QENG_ERR_DEVICE_STATUS. */
+int32_t qeng_device_status(qeng_ctx* ctx);
+/* SM count of the context's device (grid sizing, reporting). */
+int32_t qeng_sm_count(const qeng_ctx* ctx);
+
+/* ---- 4-bit block weights ("Q4_0 ... for all backends", decide/pipeline.md:38,59;
+ *      "tensor data (Q4/Q8/F16/F32)", decide/pipeline.md:28) --------------------
+ * Import: q[N*K] holds one code 0..15 per byte (row-major, K contiguous),
+ * s[N*K/32] one IEEE f16 bit pattern per 32 consecutive K.  Both are HOST
+ * pointers; the call validates the codes, re-tiles them into the device layout
+ * and uploads (synchronous).  K % 32 == 0, N % 16 == 0. */
+int32_t qeng_weight_pack_q4(qeng_ctx* ctx, const uint8_t* q, const uint16_t* s,
+                            int64_t N, int64_t K, qeng_weight** out);
+/* Inverse, computed ON THE DEVICE from the packed layout (the bit-exactness
+ * check): writes N*K codes and N*K/32 scales to HOST buffers (synchronous). */
+int32_t qeng_weight_unpack_q4(qeng_ctx* ctx, const qeng_weight* w, uint8_t* q, uint16_t* s);
+/* Device-side dequantisation to f32 [N,K] (device pointer), w = (q-8)*s. */
+int32_t qeng_weight_dequant_f32(qeng_ctx* ctx, const qeng_weight* w, float* out, void* stream);
+int32_t qeng_weight_free(qeng_ctx* ctx, qeng_weight* w);
+int64_t qeng_weight_rows(const qeng_weight* w);
+int64_t qeng_weight_cols(const qeng_weight* w);
+int64_t qeng_weight_device_bytes(const qeng_weight* w);
+
+/* ---- quantized matmul (the "QKV / O proj / FFN" steps of decide/pipeline.md:51)
+ * y[M,N] (f32, leading dimension ldy) = x[M,K] (x_dtype, leading dimension ldx)
+ * . dequant(W)^T, f32 accumulation.  M <= 256 runs the decode kernel
+ * (dequantise in registers); larger M the tensor-core prefill kernel. */
+int32_t qeng_gemm_q4(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t x_dtype,
+                     int64_t M, int64_t ldx, float* y, int64_t ldy, int32_t flags, void* stream);
+/* M = 1, f32 activations: the decode GEMV. */
+int32_t qeng_gemv_q4(qeng_ctx* ctx, const qeng_weight* w, const float* x, float* y, void* stream);
+
+/* ---- small operators of the loop ------------------------------------------- */
+/* y = x * gamma / sqrt(mean(x^2) + eps), rows of length D
+ * ("norm = rms", decide/compile.md:95). */
+int32_t qeng_rmsnorm(qeng_ctx* ctx, const float* x, const float* gamma, int64_t M, int64_t D,
+                     float eps, float* y, void* stream);
+/* In-place rotary embedding of x[M,H,hd] at integer positions pos[M]; pairs
+ * (i, i+hd/2), angle pos*base^(-2i/hd) ("RoPE", decide/pipeline.md:51). */
+int32_t qeng_rope(qeng_ctx* ctx, float* x, const int32_t* pos, int64_t M, int64_t H, int64_t hd,
+                  float base, void* stream);
+/* y = silu(gate) * up  ("ffn = swiglu", decide/compile.md:97). */
+int32_t qeng_swiglu(qeng_ctx* ctx, const float* gate, const float* up, int64_t n, float* y, void* stream);
+/* y = a + b (residual). */
+int32_t qeng_add(qeng_ctx* ctx, const float* a, const float* b, int64_t n, float* y, void* stream);
+/* x[M,D] f32 = table[tokens[m], :] for a bf16 table [V,D] ("embed"). */
+int32_t qeng_embed(qeng_ctx* ctx, const uint16_t* table_bf16, const int32_t* tokens, int64_t M,
+                   int64_t D, int64_t V, float* x, void* stream);
+/* logits[M,V] f32 = x[M,D] f32 . table[V,D]^T, bf16 table ("LM head"). */
+int32_t qeng_lm_head(qeng_ctx* ctx, const uint16_t* table_bf16, const float* x, int64_t M,
+                     int64_t D, int64_t V, float* logits, void* stream);
+/* idx[m] = lowest index of the maximum of row m ("sample", greedy). */
+int32_t qeng_argmax(qeng_ctx* ctx, const float* logits, int64_t M, int64_t V, int32_t* idx, void* stream);
+
+/* ---- KV cache and decode attention ("KV cache", "attention" of
+ *      decide/pipeline.md:51; f16 KV, decide/runtime.md:35; GQA,
+ *      decide/compile.md:96) ---------------------------------------------------
+ * The pool is f16 [pages][kv_heads][2 (K,V)][16 tokens][hd]; a page table row
+ * lists the pages of one sequence in order. hd must be 128. */
+int32_t qeng_kv_pool_create(qeng_ctx* ctx, int64_t pages, int64_t kv_heads, int64_t hd, qeng_kv_pool** out);
+int32_t qeng_kv_pool_free(qeng_ctx* ctx, qeng_kv_pool* pool);
+/* device pointer of the pool's storage (tests upload prepared caches through it) */
+void* qeng_kv_pool_data(const qeng_kv_pool* pool);
+int64_t qeng_kv_pool_pages(const qeng_kv_pool* pool);
+/* Append one token per sequence: k,v f32 [B,kv_heads,hd] rounded to f16 and
+ * written at token index pos[b] of sequence b. */
+int32_t qeng_kv_append(qeng_ctx* ctx, qeng_kv_pool* pool, const float* k, const float* v,
+                       const int32_t* page_table, int64_t max_pages, const int32_t* pos, int64_t B,
+                       void* stream);
+/* out[B,Hq,hd] f32 = softmax(q K^T * scale) V per sequence over its first
+ * lens[b] cached tokens; q f16 [B,Hq,hd]; split over the KV length with a
+ * merge of the partial (max, sum, out) triples.  Uses scratch owned by ctx. */
+int32_t qeng_attn_decode(qeng_ctx* ctx, const qeng_kv_pool* pool, const uint16_t* q_f16,
+                         const int32_t* page_table, int64_t max_pages, const int32_t* lens,
+                         int64_t B, int64_t Hq, float scale, float* out, void* stream);
+
+/* ---- the layer executor (the whole loop of decide/pipeline.md:51; what
+ *      soma-kernel drives between SomaEvent::Prefill and SomaEvent::Answer,
+ *      shell/src/worlds/soma_bridge.rs:244-277) -------------------------------- */
+typedef struct qeng_model_cfg {
+  int32_t layers, d_model, ffn, heads, kv_heads, head_dim, vocab;
+  float rms_eps, rope_base;
+  int32_t max_batch; /* sequences decoded together */
+  int32_t max_seq;   /* tokens per sequence the KV pool is sized for */
+  int32_t tp_rank, tp_world; /* tensor-parallel position of this context */
+} qeng_model_cfg;
+
+/* matrices of one layer, in the order of the decode loop */
+enum { QENG_W_Q = 0, QENG_W_K = 1, QENG_W_V = 2, QENG_W_O = 3, QENG_W_GATE = 4, QENG_W_UP = 5, QENG_W_DOWN = 6 };
+
+int32_t qeng_decoder_create(qeng_ctx* ctx, const qeng_model_cfg* cfg, qeng_decoder** out);
+int32_t qeng_decoder_free(qeng_ctx* ctx, qeng_decoder* dec);
+/* Load one linear weight of one layer from HOST codes/scales of the FULL
+ * (unsharded) matrix [N,K]; the decoder keeps this rank's shard only. */
+int32_t qeng_decoder_load_matrix(qeng_ctx* ctx, qeng_decoder* dec, int32_t layer, int32_t which,
+                                 const uint8_t* q, const uint16_t* s, int64_t N, int64_t K);
+/* RMSNorm gains of a layer (which = 0: before attention, 1: before FFN), HOST f32[d_model]. */
+int32_t qeng_decoder_load_norm(qeng_ctx* ctx, qeng_decoder* dec, int32_t layer, int32_t which, const float* gamma);
+/* Embedding table, LM head (bf16 bit patterns, HOST, [vocab,d_model]) and final norm gain. */
+int32_t qeng_decoder_load_head(qeng_ctx* ctx, qeng_decoder* dec, const uint16_t* emb, const uint16_t* lm_head,
+                               const float* final_gamma);
+/* Forget all sequences (KV lengths to zero). */
+int32_t qeng_decoder_reset(qeng_ctx* ctx, qeng_decoder* dec, int32_t batch);
+/* Prompt phase: tokens HOST int32 [batch, T]; fills the KV cache and leaves the
+ * logits of the last prompt position.  Synchronous. */
+int32_t qeng_decoder_prefill(qeng_ctx* ctx, qeng_decoder* dec, const int32_t* tokens, int32_t batch, int32_t T);
+/* Greedy decode: runs `steps` steps; each step samples from the current logits,
+ * feeds the sampled token and computes the next logits.  Writes the sampled
+ * tokens to HOST out_tokens [batch, steps].  Synchronous. */
+int32_t qeng_decoder_decode(qeng_ctx* ctx, qeng_decoder* dec, int32_t steps, int32_t* out_tokens);
+/* Copy the current logits [batch, vocab] (f32) to a HOST buffer. */
+int32_t qeng_decoder_logits(qeng_ctx* ctx, qeng_decoder* dec, float* out);
+/* Teacher-forced single layer for parity checks: x_in DEVICE f32 [batch,d_model]
+ * at positions pos (HOST int32[batch]) -> x_out DEVICE f32 [batch,d_model];
+ * appends to the KV cache of that layer. */
+int32_t qeng_decoder_layer(qeng_ctx* ctx, qeng_decoder* dec, int32_t layer, const float* x_in,
+                           const int32_t* pos, int32_t batch, float* x_out, void* stream);
+/* Run prefill/decode on the caller's stream (NULL = the decoder's own stream), so
+ * that the caller's events bracket the work. */
+int32_t qeng_decoder_set_stream(qeng_ctx* ctx, qeng_decoder* dec, void* stream);
+/* Kernel launches issued per decode step (for reporting). */
+int32_t qeng_decoder_launches_per_step(const qeng_decoder* dec);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QENG_H_ */

@@ -1,0 +1,75 @@
+"""The layer executor against the float64 teacher: teacher-forced layers, then
+free-running greedy decode on the tiny golden decoder."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import ref
+
+pytestmark = pytest.mark.gpu
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "golden.npz"))
+CFG = dict(layers=2, d=256, ffn=512, heads=4, kv_heads=2, vocab=320)
+
+
+def _make(ctx, max_batch=2, max_seq=64):
+    from cyb_b200 import qeng
+    cfg = ref.DecoderConfig(**CFG)
+    W = ref.make_decoder_weights(cfg, seed=5)
+    dec = ctx.decoder(layers=cfg.layers, d_model=cfg.d, ffn=cfg.ffn, heads=cfg.heads, kv_heads=cfg.kv_heads,
+                      vocab=cfg.vocab, max_batch=max_batch, max_seq=max_seq)
+    qeng.load_decoder_weights(dec, W, cfg)
+    return cfg, W, dec
+
+
+def test_teacher_forced_layers(ctx):
+    import torch
+    cfg, W, dec = _make(ctx)
+    teacher = ref.Decoder(cfg, W)
+    teacher.reset(1)
+    rng = ref.rng_of(40)
+    T = 19
+    x = rng.standard_normal((1, T, cfg.d), dtype=np.float32) * 3
+    pos = np.arange(T)
+    for l in range(cfg.layers):
+        want = teacher.layer(l, x.astype(np.float64), pos[None])
+        got = dec.layer(l, torch.from_numpy(x[0]).cuda(), pos).cpu().numpy()
+        assert ref.err_inf(got, want[0]) < 2e-3
+        assert ref.err_inf(got, want[0]) < 5e-5
+        # one decode step on top of the cached prompt
+        x1 = rng.standard_normal((1, 1, cfg.d), dtype=np.float32)
+        want1 = teacher.layer(l, x1.astype(np.float64), np.array([[T]]))
+        got1 = dec.layer(l, torch.from_numpy(x1[0]).cuda(), np.array([T])).cpu().numpy()
+        assert ref.err_inf(got1, want1[0]) < 5e-5
+    dec.free()
+
+
+def test_greedy_decode_matches_golden(ctx):
+    g = GOLD
+    cfg, W, dec = _make(ctx)
+    prompt = g["dec_prompt"]
+    steps = g["dec_tokens"].shape[1]
+    dec.reset(prompt.shape[0])
+    dec.prefill(prompt)
+    assert ref.err_inf(dec.logits(), g["dec_logits"][0]) < 2e-3
+    toks = dec.decode(steps)
+    assert np.array_equal(toks, g["dec_tokens"])
+    # a second call continues the same sequences (graph replay path)
+    more = dec.decode(2)
+    teacher = ref.Decoder(cfg, W)
+    want, _ = teacher.generate(prompt, steps + 2)
+    assert np.array_equal(np.concatenate([toks, more], 1), want)
+    dec.free()
+
+
+def test_state_errors(ctx):
+    from cyb_b200 import qeng
+    cfg, W, dec = _make(ctx, max_batch=1, max_seq=32)
+    dec.reset(1)
+    with pytest.raises(qeng.QengError) as e:
+        dec.decode(1)  # no logits yet
+    assert e.value.code == -8
+    with pytest.raises(qeng.QengError) as e:
+        dec.prefill(np.zeros((1, 33), np.int32))  # longer than the cache
+    assert e.value.code == -2
+    dec.free()

@@ -1,0 +1,134 @@
+"""Parity of the CUDA quantized matmul (through the C ABI) with the oracle.
+Gate: unpacked codes/scales bit-exact; outputs max|y-ref|/max|ref| <= 2e-3
+(f64 oracle)."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import ref
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "golden.npz"))
+
+
+def _t(a, dtype=None):
+    import torch
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+@pytest.mark.parametrize("n,k", [(16, 32), (16, 96), (48, 160), (256, 512), (4096, 4096), (1376, 4096), (4096, 1376)])
+def test_pack_unpack_bit_exact(ctx, n, k):
+    q, s = ref.make_q4(ref.rng_of(n * 7 + k), n, k)
+    w = ctx.pack_q4(q, s)
+    q2, s2 = w.unpack()
+    assert np.array_equal(q, q2)
+    assert np.array_equal(s.view(np.uint16), s2.view(np.uint16))
+    assert np.array_equal(w.dequant().cpu().numpy(), ref.dequant(q, s, np.float32))
+    w.free()
+
+
+def test_pack_rejects_bad_input(ctx):
+    from cyb_b200 import qeng
+    q, s = ref.make_q4(ref.rng_of(1), 16, 64)
+    bad = q.copy()
+    bad[3, 5] = 16
+    with pytest.raises(qeng.QengError) as e:
+        ctx.pack_q4(bad, s)
+    assert e.value.code == -1
+    with pytest.raises(qeng.QengError) as e:
+        ctx.pack_q4(q[:8], s[:8])  # N % 16 != 0
+    assert e.value.code == -2
+
+
+def test_config1_gemv(ctx):
+    x, q, s = ref.config1(0)
+    w = ctx.pack_q4(q, s)
+    y = ctx.gemv_q4(w, _t(x[0])).cpu().numpy()
+    yref = ref.gemm_q4_fast(x, q, s)[0]
+    e = ref.err_inf(y, yref)
+    assert e < TOL, e
+    assert e < 2e-6, e  # the split-activation path is f32-accurate
+    w.free()
+
+
+@pytest.mark.parametrize("name", ["gemv_64x96", "gemm_5x48x160", "gemm_16x32x64", "enum"])
+def test_golden_vectors(ctx, name):
+    g = GOLD
+    w = ctx.pack_q4(g[name + "_q"], g[name + "_s"])
+    y = ctx.gemm_q4(w, _t(g[name + "_x"])).cpu().numpy()
+    assert ref.err_inf(y, g[name + "_y"]) < 2e-6
+    w.free()
+
+
+def test_known_answers(ctx):
+    import torch
+    # all codes 8 -> exactly zero
+    q = np.full((16, 64), 8, np.uint8)
+    s = np.full((16, 2), 0.01, np.float16)
+    w = ctx.pack_q4(q, s)
+    x = ref.rng_of(3).standard_normal((3, 64), dtype=np.float32)
+    assert float(ctx.gemm_q4(w, _t(x)).abs().max()) == 0.0
+    w.free()
+    # one-hot activations select a column of dequant(W) exactly
+    q, s = ref.make_q4(ref.rng_of(4), 32, 96)
+    wd = ref.dequant(q, s, np.float32)
+    w = ctx.pack_q4(q, s)
+    for k in (0, 7, 31, 32, 95):
+        x = np.zeros((1, 96), np.float32)
+        x[0, k] = 1.0
+        assert np.array_equal(ctx.gemm_q4(w, _t(x)).cpu().numpy()[0], wd[:, k])
+    # identical rows give identical outputs whatever M is
+    x1 = ref.rng_of(5).standard_normal((1, 96), dtype=np.float32)
+    y1 = ctx.gemm_q4(w, _t(x1)).cpu().numpy()
+    y8 = ctx.gemm_q4(w, _t(np.repeat(x1, 8, 0))).cpu().numpy()
+    assert all(np.array_equal(y8[i], y1[0]) for i in range(8))
+    w.free()
+
+
+@pytest.mark.parametrize("idx,m,n,k", [(i, m, n, k) for i, (n, k) in enumerate([(4096, 4096), (11008, 4096), (4096, 11008)])
+                                       for m in (1, 8, 32)])
+def test_config2_sweep(ctx, idx, m, n, k):
+    import torch
+    x, q, s = ref.config2(idx, m, n, k)
+    w = ctx.pack_q4(q, s)
+    xb = _t(x).to(torch.bfloat16)
+    y = ctx.gemm_q4(w, xb).cpu().numpy()
+    e = ref.err_inf(y, ref.gemm_q4_fast(x, q, s))
+    assert e < TOL, e
+    w.free()
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 7, 16, 17, 40])
+def test_ragged_m_f32_and_accumulate(ctx, m):
+    from cyb_b200 import qeng
+    rng = ref.rng_of(100 + m)
+    x = rng.standard_normal((m, 160), dtype=np.float32)
+    q, s = ref.make_q4(rng, 48, 160)
+    w = ctx.pack_q4(q, s)
+    yref = ref.gemm_q4(x, q, s)
+    y = ctx.gemm_q4(w, _t(x))
+    assert ref.err_inf(y.cpu().numpy(), yref) < 2e-6
+    y2 = ctx.gemm_q4(w, _t(x), out=y.clone(), flags=qeng.GEMM_ACCUMULATE)
+    assert ref.err_inf(y2.cpu().numpy(), 2 * yref) < 2e-6
+    yf = ctx.gemm_q4(w, _t(x), flags=qeng.GEMM_FAST_F16)
+    assert ref.err_inf(yf.cpu().numpy(), yref) < TOL
+    yh = ctx.gemm_q4(w, _t(x).half())
+    assert ref.err_inf(yh.cpu().numpy(), ref.gemm_q4(x.astype(np.float16).astype(np.float32), q, s)) < 2e-6
+    w.free()
+
+
+def test_linearity_at_full_size(ctx):
+    """Size-independent property at a BASELINE shape: W(a x1 + b x2) = a W x1 + b W x2."""
+    rng = ref.rng_of(9)
+    q, s = ref.make_q4(rng, 11008, 4096)
+    w = ctx.pack_q4(q, s)
+    x1 = rng.standard_normal((1, 4096), dtype=np.float32)
+    x2 = rng.standard_normal((1, 4096), dtype=np.float32)
+    y1, y2 = ctx.gemm_q4(w, _t(x1)), ctx.gemm_q4(w, _t(x2))
+    y3 = ctx.gemm_q4(w, _t(2 * x1 - 3 * x2))
+    lin = (2 * y1 - 3 * y2)
+    assert float((y3 - lin).abs().max() / lin.abs().max()) < 1e-5
+    w.free()
