@@ -65,12 +65,13 @@ def test_golden_vectors(ctx, name):
 
 def test_known_answers(ctx):
     import torch
-    # all codes 8 -> exactly zero
+    # all codes 8 -> zero up to the f32 rounding of the two cancelling block sums
+    # (sum x*c and 8*sum x are formed separately, each ~ 8*sum|x| ~ 400 here)
     q = np.full((16, 64), 8, np.uint8)
     s = np.full((16, 2), 0.01, np.float16)
     w = ctx.pack_q4(q, s)
     x = ref.rng_of(3).standard_normal((3, 64), dtype=np.float32)
-    assert float(ctx.gemm_q4(w, _t(x)).abs().max()) == 0.0
+    assert float(ctx.gemm_q4(w, _t(x)).abs().max()) < 0.01 * 8 * np.abs(x).sum(1).max() * 1e-6
     w.free()
     # one-hot activations select a column of dequant(W) exactly
     q, s = ref.make_q4(ref.rng_of(4), 32, 96)
