@@ -570,6 +570,18 @@ int32_t qeng_decoder_set_stream(qeng_ctx* ctx, qeng_decoder* d, void* stream) {
   return QENG_OK;
 }
 
+int32_t qeng_decoder_weight(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, int32_t fused_index,
+                            const qeng_weight** out) {
+  if (!ctx || !d || !out) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_weight: null argument");
+  if (layer < 0 || layer >= d->cfg.layers || fused_index < 0 || fused_index > 3)
+    return qeng_fail(ctx, QENG_ERR_ARG, "decoder_weight: bad layer/index");
+  const Layer& L = d->layers[layer];
+  const qeng_weight* w = fused_index == 0 ? L.wqkv : fused_index == 1 ? L.wo : fused_index == 2 ? L.wgu : L.wdown;
+  if (!w) return qeng_fail(ctx, QENG_ERR_STATE, "decoder_weight: matrix not loaded yet");
+  *out = w;
+  return QENG_OK;
+}
+
 int32_t qeng_decoder_launches_per_step(const qeng_decoder* d) { return d ? d->launches : 0; }
 
 }  // extern "C"

@@ -101,6 +101,7 @@ _sig("qeng_decoder_decode", _i32, _vp, _vp, _i32, _vp)
 _sig("qeng_decoder_logits", _i32, _vp, _vp, _vp)
 _sig("qeng_decoder_layer", _i32, _vp, _vp, _i32, _vp, _vp, _i32, _vp, _vp)
 _sig("qeng_decoder_set_stream", _i32, _vp, _vp, _vp)
+_sig("qeng_decoder_weight", _i32, _vp, _vp, _i32, _i32, C.POINTER(_vp))
 _sig("qeng_decoder_launches_per_step", _i32, _vp)
 
 
@@ -367,6 +368,17 @@ class Decoder:
         self.ctx.check(_lib.qeng_decoder_layer(self.ctx.h, self.h, layer, _dev_ptr(x), _np_ptr(p), x.shape[0],
                                                _dev_ptr(out), _cur_stream()))
         return out
+
+    def weight(self, layer, fused_index):
+        """Borrowed handle of a fused layer weight (0 qkv, 1 o, 2 gate/up, 3 down)."""
+        h = _vp()
+        self.ctx.check(_lib.qeng_decoder_weight(self.ctx.h, self.h, layer, fused_index, C.byref(h)))
+        w = Weight.__new__(Weight)
+        w.ctx, w.h = self.ctx, h
+        w.rows, w.cols = _lib.qeng_weight_rows(h), _lib.qeng_weight_cols(h)
+        w.device_bytes = _lib.qeng_weight_device_bytes(h)
+        w.free = lambda: None  # borrowed
+        return w
 
     def use_current_stream(self):
         self.ctx.check(_lib.qeng_decoder_set_stream(self.ctx.h, self.h, _cur_stream()))

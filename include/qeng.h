@@ -185,6 +185,11 @@ int32_t qeng_decoder_layer(qeng_ctx* ctx, qeng_decoder* dec, int32_t layer, cons
 /* Run prefill/decode on the caller's stream (NULL = the decoder's own stream), so
  * that the caller's events bracket the work. */
 int32_t qeng_decoder_set_stream(qeng_ctx* ctx, qeng_decoder* dec, void* stream);
+/* The packed weights the executor holds for one layer, as fused for the kernels:
+ * 0 = q|k|v rows concatenated, 1 = o, 2 = gate/up interleaved 8/8 per 16 rows,
+ * 3 = down.  Borrowed handle (valid until the matrix is reloaded or the decoder freed). */
+int32_t qeng_decoder_weight(qeng_ctx* ctx, qeng_decoder* dec, int32_t layer, int32_t fused_index,
+                            const qeng_weight** out);
 /* Kernel launches issued per decode step (for reporting). */
 int32_t qeng_decoder_launches_per_step(const qeng_decoder* dec);
 

@@ -50,14 +50,42 @@ void orc_pack_q4(const uint8_t* q, const uint16_t* s, int64_t N, int64_t K, void
     }
 }
 
+#if defined(__AVX2__) && defined(__FMA__)
+#include <immintrin.h>
+/* 32 codes of one block against 32 activations, 8 lanes at a time */
 static inline float block_dot(const orc_block* b, const float* x) {
-  float acc = 0.f;
+  const __m128i raw = _mm_loadu_si128((const __m128i*)b->qs);
+  const __m128i m4 = _mm_set1_epi8(15);
+  const __m128i lo = _mm_and_si128(raw, m4);                      /* codes 0,2,4,.. */
+  const __m128i hi = _mm_and_si128(_mm_srli_epi16(raw, 4), m4);   /* codes 1,3,5,.. */
+  const __m128i c0 = _mm_unpacklo_epi8(lo, hi);                   /* codes 0..15 */
+  const __m128i c1 = _mm_unpackhi_epi8(lo, hi);                   /* codes 16..31 */
+  const __m256i eight = _mm256_set1_epi32(8);
+  __m256 acc = _mm256_setzero_ps();
+  acc = _mm256_fmadd_ps(_mm256_cvtepi32_ps(_mm256_sub_epi32(_mm256_cvtepu8_epi32(c0), eight)), _mm256_loadu_ps(x), acc);
+  acc = _mm256_fmadd_ps(_mm256_cvtepi32_ps(_mm256_sub_epi32(_mm256_cvtepu8_epi32(_mm_srli_si128(c0, 8)), eight)),
+                        _mm256_loadu_ps(x + 8), acc);
+  acc = _mm256_fmadd_ps(_mm256_cvtepi32_ps(_mm256_sub_epi32(_mm256_cvtepu8_epi32(c1), eight)), _mm256_loadu_ps(x + 16), acc);
+  acc = _mm256_fmadd_ps(_mm256_cvtepi32_ps(_mm256_sub_epi32(_mm256_cvtepu8_epi32(_mm_srli_si128(c1, 8)), eight)),
+                        _mm256_loadu_ps(x + 24), acc);
+  __m128 r = _mm_add_ps(_mm256_castps256_ps128(acc), _mm256_extractf128_ps(acc, 1));
+  r = _mm_add_ps(r, _mm_movehl_ps(r, r));
+  r = _mm_add_ss(r, _mm_shuffle_ps(r, r, 1));
+  return _mm_cvtss_f32(r) * (float)b->s;
+}
+#else
+static inline float block_dot(const orc_block* b, const float* x) {
+  float w[32];
   for (int i = 0; i < 16; i++) {
-    acc += x[2 * i] * (float)((int)(b->qs[i] & 15) - 8);
-    acc += x[2 * i + 1] * (float)((int)(b->qs[i] >> 4) - 8);
+    w[2 * i] = (float)((int)(b->qs[i] & 15) - 8);
+    w[2 * i + 1] = (float)((int)(b->qs[i] >> 4) - 8);
   }
+  float acc = 0.f;
+#pragma omp simd reduction(+ : acc)
+  for (int i = 0; i < 32; i++) acc += x[i] * w[i];
   return acc * (float)b->s;
 }
+#endif
 
 /* y[M,N] = x[M,K] . dequant(W)^T ; f32 block sums, f64 across blocks */
 void orc_gemm_q4(const float* x, const void* blocks, int64_t M, int64_t N, int64_t K, float* y) {
