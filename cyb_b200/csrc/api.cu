@@ -64,7 +64,7 @@ int32_t qeng_device_status(qeng_ctx* ctx) {
   QENG_CUDA(ctx, cudaMemset(ctx->status, 0, 4));
   return qeng_fail(ctx, QENG_ERR_DEVICE_STATUS,
                    "a kernel reported status %d (1 = page id outside the pool, 2 = position outside the cache, "
-                   "3 = token id outside the vocabulary)", status);
+                   "3 = token id outside the vocabulary, 4 = a bounded wait on a bulk copy ran out)", status);
 }
 
 int32_t qeng_sm_count(const qeng_ctx* ctx) { return ctx ? ctx->sm_count : 0; }

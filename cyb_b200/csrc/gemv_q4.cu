@@ -299,6 +299,11 @@ int32_t launch(qeng_ctx* ctx, const GemvParams& p, int grid, size_t smem, cudaSt
 int32_t qeng_gemm_q4_decode(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t x_dtype, int64_t M,
                             int64_t ldx, float* y, int64_t ldy, bool split_f32, const qeng_gemm_fuse& fuse,
                             cudaStream_t stream) {
+  {
+    bool handled = false;
+    int32_t rc = qeng_gemm_q4_stream(ctx, w, x, x_dtype, M, ldx, y, ldy, split_f32, fuse, stream, &handled);
+    if (handled || rc != QENG_OK) return rc;
+  }
   const int split = (x_dtype == QENG_F32 && split_f32) ? 1 : 0;
   const int max_m = split ? 16 : 32;
   if (M < 1 || M > max_m) return qeng_fail(ctx, QENG_ERR_SHAPE, "gemm_q4_decode: M=%lld outside 1..%d", (long long)M, max_m);

@@ -1,0 +1,438 @@
+// Streaming decode GEMV/GEMM over 4-bit block weights: the bandwidth kernel.
+//
+// One persistent CTA per SM: a producer warp and 16 consumer warps around a
+// ring of shared-memory stages.  The producer walks this CTA's row tiles
+// (16 rows x K, contiguous in the packed layout) and copies them stage by
+// stage (64 chunks: 32 KB of nibbles + 4 KB of scales) with bulk asynchronous
+// copies (cp.async.bulk, completion counted on an mbarrier), so ~170 KB per SM
+// are in flight without holding registers and independent of what the
+// consumers are doing.  Consumers take the chunks of a stage round-robin, read
+// them with conflict-free 128-bit shared loads, unpack in registers and
+// contract on the tensor pipe (mma.sync.m16n8k16, weights = A, activations = B;
+// arithmetic as in gemv_q4.cu).  At the end of a row tile the 16 partial
+// accumulators meet in shared memory (one named barrier, double-buffered) and
+// one warp applies the fused epilogue.
+//
+// HBM-bound: algorithmic bytes = N*K*0.5625 + activations + outputs.
+#include "qeng_internal.h"
+
+namespace {
+
+constexpr int kSC = 64;                        // chunks (of 64 k) per stage
+constexpr int kStageBytes = kSC * (512 + 64);  // nibbles then scales: 36864
+constexpr int kCW = 16;                        // consumer warps
+constexpr int kCT = kCW * 32;                  // consumer threads
+constexpr int kThreadsS = kCT + 32;            // + producer warp
+constexpr int kMaxStages = 12;
+
+struct StreamParams {
+  const uint4* qs;
+  const uint2* sc;
+  int ntiles, nchunks;
+  int K;
+  const void* x;
+  int x_dtype;
+  long long ldx;
+  int M, cols, split;
+  float* y;
+  long long ldy;
+  const float* gamma;
+  float eps;
+  int epilogue;
+  const float* resid;
+  int nstages;
+  int32_t* status;
+};
+
+// d = a.b + c (m16n8k16, f16 operands, f32 accumulate)
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1, float c0, float c1, float c2, float c3) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};\n"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(c2), "f"(c3));
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+// One attempt: the hardware may park the thread until the phase completes or the hinted time passes.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(100000u)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up (false) after 2^24 attempts, which is seconds; a healthy wait ends in microseconds.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (int i = 0; i < (1 << 24); ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+// 1-D bulk copy global -> shared, completion counted in bytes on the mbarrier
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float2 lds64f(uint32_t addr) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(kCT) : "memory"); }
+
+__device__ __forceinline__ float act_f32(const void* x, int dtype, long long i) {
+  if (dtype == QENG_F32) return reinterpret_cast<const float*>(x)[i];
+  if (dtype == QENG_F16) return __half2float(reinterpret_cast<const __half*>(x)[i]);
+  return __uint_as_float((uint32_t)reinterpret_cast<const uint16_t*>(x)[i] << 16);
+}
+
+__device__ __forceinline__ uint32_t h2bits(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int NT>
+__global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const StreamParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int Kp = p.nchunks * 64;
+  const int CS = Kp + 32;  // halves per staged activation column (64-byte skew)
+  const int nblk = p.nchunks * 2;
+  const int NS = p.nstages;
+  // carve: ring | barriers | activations | block sums | reduction buffers
+  unsigned char* ring = smem;
+  unsigned char* after_ring = smem + (size_t)NS * kStageBytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(after_ring);
+  uint64_t* empty = full + kMaxStages;
+  __half* xs_h = reinterpret_cast<__half*>(after_ring + 2 * kMaxStages * 8 + 64);
+  float* xsum = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(xs_h) + (size_t)p.cols * CS * 2);
+  float* red = xsum + (size_t)nblk * 8 * NT;  // [2][kCW][16 * 8 * NT]
+  __shared__ float warp_part[kCW], warp_max[kCW], oscale[32];
+
+  if (tid == 0) {
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(smem_u32(full + s), 1);
+      mbar_init(smem_u32(empty + s), kCW);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncthreads();
+
+  const int stages_per_tile = (p.nchunks + kSC - 1) / kSC;
+
+  if (warp == kCW) {
+    // ===== producer: stream this CTA's row tiles through the ring ==================
+    if (lane == 0) {
+      bool failed = false;
+      int s = 0;
+      uint32_t ph = 0;
+      for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
+        for (int st = 0; st < stages_per_tile; ++st) {
+          if (!failed && !mbar_wait(smem_u32(empty + s), ph ^ 1u)) failed = true;
+          const int c0 = st * kSC;
+          const int nc = min(kSC, p.nchunks - c0);
+          const uint32_t bar = smem_u32(full + s);
+          const uint32_t dst = smem_u32(ring + (size_t)s * kStageBytes);
+          const size_t chunk = (size_t)tile * p.nchunks + c0;
+          mbar_expect_tx(bar, (uint32_t)nc * 576u);
+          bulk_g2s(dst, p.qs + chunk * 32, (uint32_t)nc * 512u, bar);
+          bulk_g2s(dst + kSC * 512, p.sc + chunk * 8, (uint32_t)nc * 64u, bar);
+          if (++s == NS) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+      if (failed) atomicExch(p.status, 4);
+    }
+    return;
+  }
+
+  // ===== consumers ====================================================================
+  // ---- stage the activations as f16 (hi | lo columns), fused RMSNorm -----------------
+  // Row m is scaled by a power of two 2^sh so that its largest magnitude lands in
+  // [2^14, 2^15): the f16 split hi + lo then never touches the subnormal range for
+  // values that matter, and the slots that meet a code pre-multiplied by 16 (see the
+  // unpacking below) can hold x/16 exactly.  The epilogue multiplies by 2^-sh.
+  // One thread handles groups of 8 consecutive k; the 4 groups of a 32-block sit in one quad.
+  const int ngroups = Kp / 8;
+  for (int m = 0; m < p.M; ++m) {
+    float ss = 0.f, amax = 0.f;
+    for (int k = tid; k < p.K; k += kCT) {
+      float v = act_f32(p.x, p.x_dtype, (long long)m * p.ldx + k);
+      ss += v * v;
+      if (p.gamma != nullptr) v *= p.gamma[k];
+      amax = fmaxf(amax, fabsf(v));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    }
+    if (lane == 0) {
+      warp_part[warp] = ss;
+      warp_max[warp] = amax;
+    }
+    consumer_sync();
+    float tot = 0.f, mx = 0.f;
+#pragma unroll
+    for (int w = 0; w < kCW; ++w) {
+      tot += warp_part[w];
+      mx = fmaxf(mx, warp_max[w]);
+    }
+    consumer_sync();
+    float rs = 1.f;
+    if (p.gamma != nullptr) {
+      rs = rsqrtf(tot / (float)p.K + p.eps);
+      mx *= rs;
+    }
+    int sh = 0;
+    if (mx > 0.f && mx < 3.0e38f) sh = 14 - (((int)(__float_as_uint(mx) >> 23) & 0xff) - 127);
+    sh = max(-100, min(100, sh));
+    const float up = __uint_as_float((uint32_t)(sh + 127) << 23);
+    if (tid == 0) oscale[m] = __uint_as_float((uint32_t)(127 - sh) << 23);
+    const float mul = rs * up;
+    // whole warps iterate together (the block sums use shuffles); ngroups is a multiple of 8,
+    // so a quad is either entirely valid or entirely past the end
+    for (int grp = tid; grp < ((ngroups + 31) & ~31); grp += kCT) {
+      const bool valid = grp < ngroups;
+      const int k0 = grp * 8;
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int k = k0 + j;
+        float a = 0.f;
+        if (valid && k < p.K) {
+          a = act_f32(p.x, p.x_dtype, (long long)m * p.ldx + k) * mul;
+          if (p.gamma != nullptr) a *= p.gamma[k];
+        }
+        v[j] = (j & 1) ? a * 0.0625f : a;  // odd k of the group meet codes pre-multiplied by 16
+      }
+      // order 0,4,1,5,2,6,3,7: one 128-bit shared load yields the B registers of both MMAs of a block
+      uint4 hi;
+      hi.x = h2bits(v[0], v[4]); hi.y = h2bits(v[1], v[5]); hi.z = h2bits(v[2], v[6]); hi.w = h2bits(v[3], v[7]);
+      const __half2* hh = reinterpret_cast<const __half2*>(&hi);
+      const float2 a0 = __half22float2(hh[0]), a1 = __half22float2(hh[1]), a2 = __half22float2(hh[2]),
+                   a3 = __half22float2(hh[3]);
+      // block sums carry the zero point: -8 * 2^-24 * sum of the values the MMA effectively sees
+      float hsum = ((a0.x + a0.y) + (a2.x + a2.y)) + 16.f * ((a1.x + a1.y) + (a3.x + a3.y));
+      float lsum = 0.f;
+      const int colh = p.split ? 2 * m : m;
+      if (valid) *reinterpret_cast<uint4*>(xs_h + (size_t)colh * CS + k0) = hi;
+      if (p.split) {
+        uint4 lo;
+        lo.x = h2bits(v[0] - a0.x, v[4] - a0.y); lo.y = h2bits(v[1] - a1.x, v[5] - a1.y);
+        lo.z = h2bits(v[2] - a2.x, v[6] - a2.y); lo.w = h2bits(v[3] - a3.x, v[7] - a3.y);
+        const __half2* ll = reinterpret_cast<const __half2*>(&lo);
+        const float2 b0 = __half22float2(ll[0]), b1 = __half22float2(ll[1]), b2 = __half22float2(ll[2]),
+                     b3 = __half22float2(ll[3]);
+        lsum = ((b0.x + b0.y) + (b2.x + b2.y)) + 16.f * ((b1.x + b1.y) + (b3.x + b3.y));
+        if (valid) *reinterpret_cast<uint4*>(xs_h + (size_t)(colh + 1) * CS + k0) = lo;
+      }
+      hsum += __shfl_xor_sync(0xffffffffu, hsum, 1);
+      hsum += __shfl_xor_sync(0xffffffffu, hsum, 2);
+      lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
+      lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
+      if (valid && (lane & 3) == 0) {
+        const int blk = grp >> 2;
+        xsum[blk * (8 * NT) + colh] = hsum * (-8.0f * 5.9604644775390625e-08f);
+        if (p.split) xsum[blk * (8 * NT) + colh + 1] = lsum * (-8.0f * 5.9604644775390625e-08f);
+      }
+    }
+  }
+  // unused columns of the block-sum table must be finite (their results are never read)
+  for (int i = tid; i < nblk * 8 * NT; i += kCT)
+    if ((i % (8 * NT)) >= p.cols) xsum[i] = 0.f;
+  consumer_sync();
+
+  // ---- main loop over this CTA's row tiles -------------------------------------------
+  // Lanes whose B column lies beyond the activations read an existing column instead:
+  // every load stays in bounds and unpredicated, and their output columns are ignored.
+  // All addresses are 32-bit shared-space byte addresses advanced by compile-time strides.
+  uint32_t xcol[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+    xcol[nt] = smem_u32(xs_h) + (uint32_t)((min(nt * 8 + g, p.cols - 1) * CS + t * 8) * 2) + (uint32_t)warp * 128u;
+  const uint32_t zcol = smem_u32(xsum) + (uint32_t)t * 8u + (uint32_t)warp * (2u * 32u * NT);
+  const uint32_t ring_w = smem_u32(ring) + (uint32_t)warp * 512u + (uint32_t)lane * 16u;
+  const uint32_t ring_s = smem_u32(ring) + kSC * 512u + (uint32_t)warp * 64u + (uint32_t)g * 8u;
+  const int red_stride = 16 * 8 * NT;  // floats per warp per buffer
+  bool failed = false;
+  int s = 0, buf = 0, tcount = 0;
+  uint32_t ph = 0;
+  for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++tcount) {
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+
+    uint32_t xo = 0, zo = 0;  // byte offsets of the current stage along k
+    for (int st = 0; st < stages_per_tile; ++st) {
+      if (!failed && !mbar_wait(smem_u32(full + s), ph)) failed = true;
+      const int nc = min(kSC, p.nchunks - st * kSC);
+      const uint32_t wb = ring_w + (uint32_t)s * kStageBytes;
+      const uint32_t sb = ring_s + (uint32_t)s * kStageBytes;
+#pragma unroll
+      for (int rep = 0; rep < kSC / kCW; ++rep) {
+        if (warp + rep * kCW < nc) {
+          const uint4 w = lds128(wb + rep * (kCW * 512));
+          const uint2 s2 = lds64(sb + rep * (kCW * 64));
+#pragma unroll
+          for (int b1 = 0; b1 < 2; ++b1) {
+            // A fragments: a 4-bit code c in the low mantissa bits of an f16 is the subnormal
+            // c*2^-24; one nibble higher it is 16c*2^-24 (its activation slot holds x/16).
+            const uint32_t w0 = b1 ? w.z : w.x, w1 = b1 ? w.w : w.y;
+            const uint32_t v0 = w0 >> 8, v1 = w1 >> 8;
+            const uint32_t mlo = 0x000f000fu, mhi = 0x00f000f0u;
+            const uint32_t sbits = b1 ? s2.y : s2.x;
+            const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&sbits));
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+              const uint4 xb = lds128(xcol[nt] + xo + (rep * kCW * 128 + b1 * 64));
+              const float2 z = lds64f(zcol + zo + ((rep * kCW * 2 + b1) * 32 * NT + nt * 32));
+              float d[4];
+              mma16816(d, w0 & mlo, w1 & mlo, w0 & mhi, w1 & mhi, xb.x, xb.y, z.x, z.y, z.x, z.y);
+              mma16816(d, v0 & mlo, v1 & mlo, v0 & mhi, v1 & mhi, xb.z, xb.w, d[0], d[1], d[2], d[3]);
+              acc[nt][0] = fmaf(sf.x, d[0], acc[nt][0]);
+              acc[nt][1] = fmaf(sf.x, d[1], acc[nt][1]);
+              acc[nt][2] = fmaf(sf.y, d[2], acc[nt][2]);
+              acc[nt][3] = fmaf(sf.y, d[3], acc[nt][3]);
+            }
+          }
+        }
+      }
+      xo += kSC * 128;
+      zo += kSC * 2 * 32 * NT;
+      // this warp is done with the stage
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(empty + s));
+      if (++s == NS) {
+        s = 0;
+        ph ^= 1u;
+      }
+    }
+
+    // ---- the 16 partial accumulators meet in shared memory --------------------------
+    // red[buf][warp][act][row16]; the reader of buffer `buf` finishes before it arrives at
+    // the next tile's barrier, and buffer `buf` is written again only after that barrier
+    float* myred = red + ((size_t)buf * kCW + warp) * red_stride;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      if (p.split) {
+        const int a = nt * 4 + t;
+        myred[a * 16 + g] = acc[nt][0] + acc[nt][1];
+        myred[a * 16 + g + 8] = acc[nt][2] + acc[nt][3];
+      } else {
+        const int a = nt * 8 + 2 * t;
+        myred[a * 16 + g] = acc[nt][0];
+        myred[(a + 1) * 16 + g] = acc[nt][1];
+        myred[a * 16 + g + 8] = acc[nt][2];
+        myred[(a + 1) * 16 + g + 8] = acc[nt][3];
+      }
+    }
+    consumer_sync();
+    if (warp == (tcount & (kCW - 1))) {
+      const float* rb = red + (size_t)buf * kCW * red_stride;
+      if (p.epilogue == QENG_EPI_SWIGLU) {
+        for (int e = lane; e < p.M * 8; e += 32) {
+          const int a = e >> 3, r = e & 7;
+          float gate = 0.f, up = 0.f;
+#pragma unroll
+          for (int w = 0; w < kCW; ++w) {
+            gate += rb[w * red_stride + a * 16 + r];
+            up += rb[w * red_stride + a * 16 + r + 8];
+          }
+          const float os = oscale[a];
+          gate = gate * 16777216.0f * os;
+          up = up * 16777216.0f * os;
+          p.y[(size_t)a * p.ldy + (size_t)tile * 8 + r] = gate / (1.0f + __expf(-gate)) * up;
+        }
+      } else {
+        for (int e = lane; e < p.M * 16; e += 32) {
+          const int a = e >> 4, r = e & 15;
+          float v = 0.f;
+#pragma unroll
+          for (int w = 0; w < kCW; ++w) v += rb[w * red_stride + a * 16 + r];
+          v = v * 16777216.0f * oscale[a];
+          const size_t o = (size_t)a * p.ldy + (size_t)tile * 16 + r;
+          if (p.epilogue == QENG_EPI_ACCUM) v += p.y[o];
+          else if (p.epilogue == QENG_EPI_RESID) v += p.resid[o];
+          p.y[o] = v;
+        }
+      }
+    }
+    buf ^= 1;
+  }
+  if (failed && lane == 0) atomicExch(p.status, 4);
+}
+
+template <int NT>
+int32_t launch_stream(qeng_ctx* ctx, const StreamParams& p, size_t smem, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    QENG_CUDA(ctx, cudaFuncSetAttribute(gemv_q4_stream_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    configured = true;
+  }
+  const int grid = p.ntiles < ctx->sm_count ? p.ntiles : ctx->sm_count;
+  gemv_q4_stream_kernel<NT><<<grid, kThreadsS, smem, stream>>>(p);
+  QENG_LAUNCH_CHECK(ctx);
+  return QENG_OK;
+}
+
+}  // namespace
+
+// *handled = false when the shape does not fit this kernel (activations too large to keep
+// resident in shared memory); the caller then uses the register-streaming kernel.
+int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t x_dtype, int64_t M,
+                            int64_t ldx, float* y, int64_t ldy, bool split_f32, const qeng_gemm_fuse& fuse,
+                            cudaStream_t stream, bool* handled) {
+  *handled = false;
+  const int split = (x_dtype == QENG_F32 && split_f32) ? 1 : 0;
+  const int cols = split ? 2 * (int)M : (int)M;
+  if (M < 1 || cols > 32) return QENG_OK;
+  const int NT = cols <= 8 ? 1 : (cols <= 16 ? 2 : 4);
+  const int64_t Kp = w->nchunks * 64;
+  const size_t fixed = (size_t)2 * kMaxStages * 8 + 64                  // barriers
+                       + (size_t)cols * (Kp + 32) * 2                   // staged activations
+                       + (size_t)w->nchunks * 2 * 8 * NT * 4            // block sums
+                       + (size_t)2 * kCW * 16 * 8 * NT * 4;             // reduction buffers
+  const size_t budget = 226 * 1024 - 256;
+  if (fixed + (size_t)3 * kStageBytes > budget) return QENG_OK;
+  int nstages = (int)((budget - fixed) / kStageBytes);
+  if (nstages > kMaxStages) nstages = kMaxStages;
+  StreamParams p;
+  p.qs = w->qs; p.sc = w->sc;
+  p.ntiles = (int)w->ntiles; p.nchunks = (int)w->nchunks; p.K = (int)w->K;
+  p.x = x; p.x_dtype = x_dtype; p.ldx = ldx; p.M = (int)M; p.cols = cols; p.split = split;
+  p.y = y; p.ldy = ldy;
+  p.gamma = fuse.norm_gamma; p.eps = fuse.norm_eps; p.epilogue = fuse.epilogue; p.resid = fuse.resid;
+  p.nstages = nstages; p.status = ctx->status;
+  const size_t smem = (size_t)nstages * kStageBytes + fixed;
+  *handled = true;
+  switch (NT) {
+    case 1: return launch_stream<1>(ctx, p, smem, stream);
+    case 2: return launch_stream<2>(ctx, p, smem, stream);
+    default: return launch_stream<4>(ctx, p, smem, stream);
+  }
+}

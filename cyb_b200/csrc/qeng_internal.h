@@ -81,3 +81,8 @@ int32_t qeng_gemm_q4_decode(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
 
 // attn_decode.cu: size the context's split scratch for a shape (may allocate; never call while capturing)
 int32_t qeng_attn_reserve(qeng_ctx* ctx, int64_t B, int64_t Hq, int64_t Hkv, int64_t max_pages);
+
+// gemv_q4_stream.cu: the persistent bulk-copy kernel; *handled = false when the shape does not fit it
+int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t x_dtype, int64_t M,
+                            int64_t ldx, float* y, int64_t ldy, bool split_f32, const qeng_gemm_fuse& fuse,
+                            cudaStream_t stream, bool* handled);

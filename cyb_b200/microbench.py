@@ -1,0 +1,151 @@
+"""Kernel microbenchmarks over the C ABI (device-resident inputs, CUDA events).
+
+    python -m cyb_b200.microbench gemv --n 4096 --k 4096 [--m 1] [--dtype f32|bf16] [--pool 24] [--iters 20]
+    python -m cyb_b200.microbench attn [--batch 16] [--lo 512] [--hi 4096]
+    python -m cyb_b200.microbench lmhead [--m 1]
+
+`gemv` rotates through a pool of distinct packed weights larger than the 126 MB
+L2, so every launch streams its weights from HBM; the figure printed is
+algorithmic bytes / time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import numpy as np
+
+
+def _events(torch):
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def gemv(args):
+    import torch
+    from cyb_b200 import qeng
+    ctx = qeng.Context(0)
+    n, k, m = args.n, args.k, args.m
+    wbytes = n * k * 0.5625
+    pool = args.pool or max(2, int(160e6 // wbytes) + 1)
+    rng = np.random.Generator(np.random.PCG64(0))
+    q = rng.integers(0, 16, (n, k), dtype=np.uint8)
+    s = rng.uniform(0.002, 0.02, (n, k // 32)).astype(np.float16)
+    ws = [ctx.pack_q4(np.roll(q, i, axis=1), s) for i in range(pool)]
+    dt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[args.dtype]
+    x = torch.randn(m, k, device="cuda").to(dt)
+    y = torch.empty(m, n, device="cuda")
+    algo = wbytes + m * k * x.element_size() + m * n * 4
+    # the launches are replayed from a CUDA graph so that the host launch rate does not bound the figure
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for i in range(2 * pool):
+            ctx.gemm_q4(ws[i % pool], x, out=y, flags=args.flags)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for w in ws:
+            ctx.gemm_q4(w, x, out=y, flags=args.flags)
+    graph.replay()
+    e0, e1 = _events(torch)
+    torch.cuda.synchronize()
+    e0.record()
+    for it in range(args.iters):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (args.iters * pool)
+    ctx.device_status()
+    print(json.dumps({"kernel": "gemm_q4", "n": n, "k": k, "m": m, "dtype": args.dtype, "pool": pool,
+                      "us_per_launch": us, "algo_bytes": algo, "gbs": algo / us / 1e3}))
+
+
+def attn(args):
+    import torch
+    from cyb_b200 import qeng
+    ctx = qeng.Context(0)
+    rng = np.random.Generator(np.random.PCG64(4))
+    B, Hq, Hkv = args.batch, 32, 8
+    lens = rng.integers(args.lo, args.hi + 1, B).astype(np.int32)
+    npages = (lens + 15) // 16
+    total = int(npages.sum())
+    pools = []
+    for _ in range(args.pool):
+        p = ctx.kv_pool(total, Hkv)
+        p.tensor().normal_()
+        pools.append(p)
+    order = rng.permutation(total).astype(np.int32)
+    table = np.zeros((B, int(npages.max())), np.int32)
+    off = 0
+    for b in range(B):
+        table[b, :npages[b]] = order[off:off + npages[b]]
+        off += npages[b]
+    q = torch.randn(B, Hq, 128, device="cuda").half()
+    tb, ln = torch.from_numpy(table).cuda(), torch.from_numpy(lens).cuda()
+    algo = float(lens.sum()) * Hkv * 2 * 128 * 2 + 2 * B * Hq * 128 * 2
+    for i in range(3):
+        ctx.attn_decode(pools[i % args.pool], q, tb, ln)
+    e0, e1 = _events(torch)
+    torch.cuda.synchronize()
+    e0.record()
+    for it in range(args.iters):
+        for p in pools:
+            ctx.attn_decode(p, q, tb, ln)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (args.iters * args.pool)
+    ctx.device_status()
+    print(json.dumps({"kernel": "attn_decode", "batch": B, "tokens": int(lens.sum()), "us_per_call": us,
+                      "algo_bytes": algo, "gbs": algo / us / 1e3}))
+
+
+def lmhead(args):
+    import torch
+    from cyb_b200 import qeng
+    ctx = qeng.Context(0)
+    V, D = 32000, 4096
+    tb = (torch.randn(V, D, device="cuda") * 0.02).bfloat16().view(torch.int16)
+    x = torch.randn(args.m, D, device="cuda")
+    for _ in range(3):
+        ctx.lm_head(tb, x)
+    e0, e1 = _events(torch)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    tot = 0.0
+    for it in range(args.iters):
+        flush.zero_()
+        e0.record()
+        ctx.lm_head(tb, x)
+        e1.record()
+        torch.cuda.synchronize()
+        tot += e0.elapsed_time(e1)
+    us = tot * 1e3 / args.iters
+    algo = V * D * 2 + args.m * (D + V) * 4
+    print(json.dumps({"kernel": "lm_head", "m": args.m, "us_per_call": us, "algo_bytes": algo, "gbs": algo / us / 1e3}))
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="cyb_b200.microbench")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("gemv")
+    g.add_argument("--n", type=int, default=4096)
+    g.add_argument("--k", type=int, default=4096)
+    g.add_argument("--m", type=int, default=1)
+    g.add_argument("--dtype", default="f32")
+    g.add_argument("--pool", type=int, default=0)
+    g.add_argument("--iters", type=int, default=20)
+    g.add_argument("--flags", type=int, default=0)
+    a = sub.add_parser("attn")
+    a.add_argument("--batch", type=int, default=16)
+    a.add_argument("--lo", type=int, default=512)
+    a.add_argument("--hi", type=int, default=4096)
+    a.add_argument("--pool", type=int, default=2)
+    a.add_argument("--iters", type=int, default=20)
+    l = sub.add_parser("lmhead")
+    l.add_argument("--m", type=int, default=1)
+    l.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args(argv)
+    {"gemv": gemv, "attn": attn, "lmhead": lmhead}[args.cmd](args)
+
+
+if __name__ == "__main__":
+    main()
