@@ -244,6 +244,20 @@ __global__ void kv_append_kernel(__half* pool, const float* k, const float* v, c
 
 }  // namespace
 
+// ---- scratch for the entry point that allocates nothing ---------------------------------
+// Some hosts may not allocate device memory once they are running: a runtime that hands the
+// engine a fixed memory budget at start-up, or a caller inside a region where the CUDA
+// allocator must not be entered (a latency-critical token loop, a process that shares the GPU
+// under a hard memory cap).  For them the split partials live in this file-scope array, which
+// every GPU that loads the library holds from load to exit.  4 MiB covers
+// B * Hq * splits * 130 <= 1048576 floats, e.g. 16 sequences x 32 heads x 15 splits.
+constexpr size_t kStaticScratchFloats = (size_t)1 << 20;
+static __device__ __align__(256) float g_attn_static_scratch[kStaticScratchFloats];
+// In host code the array's name is only a handle: the device address comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+constexpr int kMaxDevices = 64;
+static float* g_attn_static_addr[kMaxDevices] = {};
+
 // Splits: enough CTAs to fill the machine several times over, at least one page per warp.
 static int pages_per_split(const qeng_ctx* ctx, int64_t B, int64_t Hkv, int64_t max_pages) {
   int64_t target = (int64_t)ctx->sm_count * 8;
@@ -336,6 +350,55 @@ int32_t qeng_attn_decode(qeng_ctx* ctx, const qeng_kv_pool* pool, const uint16_t
   if (rc != QENG_OK) return rc;
   p.part_o = ctx->attn_scratch;
   p.part_ml = ctx->attn_scratch + (size_t)B * Hq * p.S * kHD;
+  dim3 grid((unsigned)p.S, (unsigned)p.Hkv, (unsigned)B);
+  attn_decode_kernel<<<grid, kAW * 32, 0, (cudaStream_t)stream>>>(p);
+  QENG_LAUNCH_CHECK(ctx);
+  dim3 grid2((unsigned)Hq, (unsigned)B);
+  attn_combine_kernel<<<grid2, kHD, 0, (cudaStream_t)stream>>>(p);
+  QENG_LAUNCH_CHECK(ctx);
+  return QENG_OK;
+}
+
+int32_t qeng_attn_decode_noalloc(qeng_ctx* ctx, const qeng_kv_pool* pool, const uint16_t* q_f16,
+                                 const int32_t* page_table, int64_t max_pages, const int32_t* lens, int64_t B,
+                                 int64_t Hq, float scale, float* out, void* stream) {
+  if (!ctx || !pool || !q_f16 || !page_table || !lens || !out)
+    return qeng_fail(ctx, QENG_ERR_ARG, "attn_decode_noalloc: null argument");
+  if (B <= 0 || max_pages <= 0 || Hq <= 0)
+    return qeng_fail(ctx, QENG_ERR_ARG, "attn_decode_noalloc: B, Hq, max_pages must be positive");
+  if (Hq % pool->kv_heads != 0 || Hq / pool->kv_heads > 8)
+    return qeng_fail(ctx, QENG_ERR_SHAPE, "attn_decode_noalloc: query heads per kv head must divide evenly and be <= 8");
+  if ((reinterpret_cast<uintptr_t>(q_f16) & 15) != 0)
+    return qeng_fail(ctx, QENG_ERR_ALIGN, "attn_decode_noalloc: q must be 16-byte aligned");
+  if (ctx->device < 0 || ctx->device >= kMaxDevices)
+    return qeng_fail(ctx, QENG_ERR_ARG, "attn_decode_noalloc: device index %d outside 0..%d", ctx->device, kMaxDevices - 1);
+  AttnParams p;
+  p.pps = pages_per_split(ctx, B, pool->kv_heads, max_pages);
+  p.S = (int)((max_pages + p.pps - 1) / p.pps);
+  const size_t need = (size_t)B * Hq * p.S * (kHD + 2);
+  if (need > kStaticScratchFloats)
+    return qeng_fail(ctx, QENG_ERR_SHAPE,
+                     "attn_decode_noalloc: B*Hq*splits*130 = %zu floats exceeds the built-in scratch of %zu floats "
+                     "(B=%lld Hq=%lld splits=%d); use qeng_attn_decode",
+                     need, kStaticScratchFloats, (long long)B, (long long)Hq, p.S);
+  // set-up, once per device: resolve the array's device address with that device current
+  if (!g_attn_static_addr[ctx->device]) {
+    QENG_CUDA(ctx, cudaSetDevice(ctx->device));
+    float* addr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&addr), g_attn_static_scratch);
+    if (e != cudaSuccess || !addr)
+      return qeng_fail(ctx, QENG_ERR_CUDA, "attn_decode_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    g_attn_static_addr[ctx->device] = addr;
+  }
+  float* scratch = g_attn_static_addr[ctx->device];
+  p.pool = pool->data; p.q = reinterpret_cast<const __half*>(q_f16);
+  p.table = page_table; p.lens = lens; p.out = out; p.status = ctx->status;
+  p.pages = (int)pool->pages; p.Hkv = (int)pool->kv_heads; p.Hq = (int)Hq; p.grp = (int)(Hq / pool->kv_heads);
+  p.max_pages = (int)max_pages;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  // every partial that the merge reads is written by this call first: nothing has to start at zero
+  p.part_o = scratch;
+  p.part_ml = scratch + (size_t)B * Hq * p.S * kHD;
   dim3 grid((unsigned)p.S, (unsigned)p.Hkv, (unsigned)B);
   attn_decode_kernel<<<grid, kAW * 32, 0, (cudaStream_t)stream>>>(p);
   QENG_LAUNCH_CHECK(ctx);

@@ -90,6 +90,7 @@ _sig("qeng_kv_pool_data", _vp, _vp)
 _sig("qeng_kv_pool_pages", _i64, _vp)
 _sig("qeng_kv_append", _i32, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp)
 _sig("qeng_attn_decode", _i32, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _f32, _vp, _vp)
+_sig("qeng_attn_decode_noalloc", _i32, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _f32, _vp, _vp)
 _sig("qeng_decoder_create", _i32, _vp, C.POINTER(ModelCfg), C.POINTER(_vp))
 _sig("qeng_decoder_free", _i32, _vp, _vp)
 _sig("qeng_decoder_load_matrix", _i32, _vp, _vp, _i32, _i32, _vp, _vp, _i64, _i64)
@@ -248,6 +249,19 @@ class Context:
         scale = float(hd) ** -0.5 if scale is None else scale
         self.check(_lib.qeng_attn_decode(self.h, pool.h, _dev_ptr(q), _dev_ptr(table), table.shape[1], _dev_ptr(lens),
                                          b, hq, scale, _dev_ptr(out), _cur_stream()))
+        return out
+
+    def attn_decode_noalloc(self, pool, q, table, lens, scale=None, out=None):
+        """qeng_attn_decode_noalloc: the split scratch is the library's built-in array, nothing is
+        allocated by the engine (pass `out` to keep the caller side allocation-free as well)."""
+        import torch
+        b, hq, hd = q.shape
+        assert q.dtype == torch.float16 and q.is_contiguous()
+        if out is None:
+            out = torch.empty((b, hq, hd), dtype=torch.float32, device=q.device)
+        scale = float(hd) ** -0.5 if scale is None else scale
+        self.check(_lib.qeng_attn_decode_noalloc(self.h, pool.h, _dev_ptr(q), _dev_ptr(table), table.shape[1],
+                                                 _dev_ptr(lens), b, hq, scale, _dev_ptr(out), _cur_stream()))
         return out
 
     def decoder(self, **kw):

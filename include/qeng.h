@@ -141,6 +141,25 @@ int32_t qeng_attn_decode(qeng_ctx* ctx, const qeng_kv_pool* pool, const uint16_t
                          const int32_t* page_table, int64_t max_pages, const int32_t* lens,
                          int64_t B, int64_t Hq, float scale, float* out, void* stream);
 
+/* Same result as qeng_attn_decode, for callers that cannot allocate device memory
+ * while they run: hosts that give the engine a fixed memory budget at start-up and
+ * forbid later growth, or token loops that must never enter the CUDA allocator.
+ * (No counterpart in the reference: its runtime owns all memory itself.)
+ * The split partials go to a 4 MiB array built into the library (held on every GPU
+ * that loads it, until exit) instead of context-owned scratch; the call makes no
+ * cudaMalloc/cudaFree and calls no allocating library routine.  Limit:
+ * B * Hq * splits * 130 <= 1048576 floats, where splits = ceil(max_pages /
+ * pages_per_split) as the engine chooses it (e.g. 16 sequences x 32 heads x 15
+ * splits); larger shapes return QENG_ERR_SHAPE with the sizes in the error text.
+ * The first call on a device resolves the array's device address
+ * (cudaGetSymbolAddress), so make that first call outside any stream capture.
+ * All calls on a device share the array: two calls whose kernels overlap on the GPU
+ * (different streams, or different contexts on one device) race; calls on one
+ * stream are ordered and safe.  Nothing in the array has to start at zero. */
+int32_t qeng_attn_decode_noalloc(qeng_ctx* ctx, const qeng_kv_pool* pool, const uint16_t* q_f16,
+                                 const int32_t* page_table, int64_t max_pages, const int32_t* lens,
+                                 int64_t B, int64_t Hq, float scale, float* out, void* stream);
+
 /* ---- the layer executor (the whole loop of decide/pipeline.md:51; what
  *      soma-kernel drives between SomaEvent::Prefill and SomaEvent::Answer,
  *      shell/src/worlds/soma_bridge.rs:244-277) -------------------------------- */
