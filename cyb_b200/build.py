@@ -44,15 +44,20 @@ def up_to_date():
     return all(os.path.getmtime(p) <= t for p in _deps())
 
 
-def build(force=False, verbose=False):
-    if not force and up_to_date():
+def build(force=False, verbose=False, extra_flags=(), out_dir=None):
+    """Compile every .cu and link libqeng.so.  `extra_flags` (e.g. -D tuning macros) and
+    `out_dir` build a variant beside the default library (load it with QENG_LIB=path)."""
+    global_default = out_dir is None and not extra_flags
+    if global_default and not force and up_to_date():
         return LIB
-    os.makedirs(OUT_DIR, exist_ok=True)
+    OUT_DIR_ = out_dir or OUT_DIR
+    LIB_ = os.path.join(OUT_DIR_, "libqeng.so")
+    os.makedirs(OUT_DIR_, exist_ok=True)
     nvcc = _nvcc()
-    flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
+    flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"] + list(extra_flags)
 
     def compile_one(src):
-        obj = os.path.join(OUT_DIR, os.path.basename(src)[:-3] + ".o")
+        obj = os.path.join(OUT_DIR_, os.path.basename(src)[:-3] + ".o")
         cmd = [nvcc] + flags + ["-c", src, "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
@@ -62,16 +67,16 @@ def build(force=False, verbose=False):
     with ThreadPoolExecutor(max_workers=min(8, len(sources()))) as ex:
         results = list(ex.map(compile_one, sources()))
     log = "\n".join(err for _, err in results)
-    with open(os.path.join(OUT_DIR, "ptxas.log"), "w") as f:
+    with open(os.path.join(OUT_DIR_, "ptxas.log"), "w") as f:
         f.write(log)
     if verbose:
         print(log)
     objs = [o for o, _ in results]
-    cmd = [nvcc] + ARCH + ["-shared", "-o", LIB] + objs + ["-Xcompiler", "-fopenmp", "-lgomp"]
+    cmd = [nvcc] + ARCH + ["-shared", "-o", LIB_] + objs + ["-Xcompiler", "-fopenmp", "-lgomp"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))
-    return LIB
+    return LIB_
 
 
 if __name__ == "__main__":

@@ -1,5 +1,6 @@
 // Context and error plumbing of libqeng.
 #include <stdarg.h>
+#include <stdlib.h>
 
 #include "qeng_internal.h"
 
@@ -35,6 +36,7 @@ int32_t qeng_create(int32_t device, qeng_ctx** out) {
     return QENG_ERR_CUDA;
   }
   ctx->sm_count = prop.multiProcessorCount;
+  ctx->pdl = getenv("QENG_NO_PDL") == nullptr;
   if (cudaMalloc(&ctx->status, 64) != cudaSuccess || cudaMemset(ctx->status, 0, 64) != cudaSuccess) {
     delete ctx;
     return QENG_ERR_CUDA;

@@ -24,6 +24,7 @@ constexpr int kCW = 16;                        // consumer warps
 constexpr int kCT = kCW * 32;                  // consumer threads
 constexpr int kThreadsS = kCT + 32;            // + producer warp
 constexpr int kMaxStages = 12;
+constexpr int kGroups = 3;                     // groups of 8 k one consumer thread stages: K <= 8 * kGroups * kCT
 
 struct StreamParams {
   const uint4* qs;
@@ -129,8 +130,9 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
   __half* xs_h = reinterpret_cast<__half*>(after_ring + 2 * kMaxStages * 8 + 64);
   float* xsum = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(xs_h) + (size_t)p.cols * CS * 2);
   float* red = xsum + (size_t)nblk * 8 * NT;  // [2][kCW][16 * 8 * NT]
-  __shared__ float warp_part[kCW], warp_max[kCW], oscale[32];
+  __shared__ float warp_part[4 * kCW], oscale[32];
 
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");  // the next kernel may start its own weight stream
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(smem_u32(full + s), 1);
@@ -171,38 +173,73 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
   }
 
   // ===== consumers ====================================================================
+  // The weights never change, so only the consumers wait for the kernel that produced the
+  // activations (a no-op unless launched with programmatic stream serialization).
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
   // ---- stage the activations as f16 (hi | lo columns), fused RMSNorm -----------------
   // Row m is scaled by a power of two 2^sh so that its largest magnitude lands in
   // [2^14, 2^15): the f16 split hi + lo then never touches the subnormal range for
   // values that matter, and the slots that meet a code pre-multiplied by 16 (see the
   // unpacking below) can hold x/16 exactly.  The epilogue multiplies by 2^-sh.
-  // One thread handles groups of 8 consecutive k; the 4 groups of a 32-block sit in one quad.
+  // One thread owns up to kGroups groups of 8 consecutive k (loaded once, kept in
+  // registers across the reduction); the 4 groups of a 32-block sit in one quad.
   const int ngroups = Kp / 8;
+  const bool vec_ok = p.x_dtype == QENG_F32 && ((reinterpret_cast<uintptr_t>(p.x) | (uintptr_t)(p.ldx * 4)) & 15) == 0 &&
+                      (p.gamma == nullptr || (reinterpret_cast<uintptr_t>(p.gamma) & 15) == 0) && (p.K & 7) == 0;
   for (int m = 0; m < p.M; ++m) {
+    float v[kGroups][8];
     float ss = 0.f, amax = 0.f;
-    for (int k = tid; k < p.K; k += kCT) {
-      float v = act_f32(p.x, p.x_dtype, (long long)m * p.ldx + k);
-      ss += v * v;
-      if (p.gamma != nullptr) v *= p.gamma[k];
-      amax = fmaxf(amax, fabsf(v));
+#pragma unroll
+    for (int j = 0; j < kGroups; ++j) {
+      const int k0 = (tid + j * kCT) * 8;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[j][i] = 0.f;
+      if (k0 < p.K) {
+        if (vec_ok) {
+          const float4* xp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x) + (long long)m * p.ldx + k0);
+          const float4 a = xp[0], b = xp[1];
+          v[j][0] = a.x; v[j][1] = a.y; v[j][2] = a.z; v[j][3] = a.w;
+          v[j][4] = b.x; v[j][5] = b.y; v[j][6] = b.z; v[j][7] = b.w;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (k0 + i < p.K) v[j][i] = act_f32(p.x, p.x_dtype, (long long)m * p.ldx + k0 + i);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss = fmaf(v[j][i], v[j][i], ss);
+        if (p.gamma != nullptr) {
+          if (vec_ok) {
+            const float4* gp = reinterpret_cast<const float4*>(p.gamma + k0);
+            const float4 a = gp[0], b = gp[1];
+            v[j][0] *= a.x; v[j][1] *= a.y; v[j][2] *= a.z; v[j][3] *= a.w;
+            v[j][4] *= b.x; v[j][5] *= b.y; v[j][6] *= b.z; v[j][7] *= b.w;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (k0 + i < p.K) v[j][i] *= p.gamma[k0 + i];
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
+      }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       ss += __shfl_xor_sync(0xffffffffu, ss, o);
       amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     }
+    float* wp = warp_part + (m & 1) * (2 * kCW);  // double-buffered: one barrier per row
     if (lane == 0) {
-      warp_part[warp] = ss;
-      warp_max[warp] = amax;
+      wp[warp] = ss;
+      wp[kCW + warp] = amax;
     }
     consumer_sync();
     float tot = 0.f, mx = 0.f;
 #pragma unroll
     for (int w = 0; w < kCW; ++w) {
-      tot += warp_part[w];
-      mx = fmaxf(mx, warp_max[w]);
+      tot += wp[w];
+      mx = fmaxf(mx, wp[kCW + w]);
     }
-    consumer_sync();
     float rs = 1.f;
     if (p.gamma != nullptr) {
       rs = rsqrtf(tot / (float)p.K + p.eps);
@@ -211,60 +248,55 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
     int sh = 0;
     if (mx > 0.f && mx < 3.0e38f) sh = 14 - (((int)(__float_as_uint(mx) >> 23) & 0xff) - 127);
     sh = max(-100, min(100, sh));
-    const float up = __uint_as_float((uint32_t)(sh + 127) << 23);
+    const float mul = rs * __uint_as_float((uint32_t)(sh + 127) << 23);
     if (tid == 0) oscale[m] = __uint_as_float((uint32_t)(127 - sh) << 23);
-    const float mul = rs * up;
-    // whole warps iterate together (the block sums use shuffles); ngroups is a multiple of 8,
-    // so a quad is either entirely valid or entirely past the end
-    for (int grp = tid; grp < ((ngroups + 31) & ~31); grp += kCT) {
-      const bool valid = grp < ngroups;
-      const int k0 = grp * 8;
-      float v[8];
+    const int colh = p.split ? 2 * m : m;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int k = k0 + j;
-        float a = 0.f;
-        if (valid && k < p.K) {
-          a = act_f32(p.x, p.x_dtype, (long long)m * p.ldx + k) * mul;
-          if (p.gamma != nullptr) a *= p.gamma[k];
+    for (int j = 0; j < kGroups; ++j) {
+      const int grp = tid + j * kCT;
+      // whole warps take part (the block sums use shuffles); ngroups is a multiple of 8, so a quad
+      // is either entirely valid or entirely past the end
+      if ((grp & ~31) < ngroups) {
+        const bool valid = grp < ngroups;
+        const int k0 = grp * 8;
+        float a[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float t0 = v[j][i] * mul;
+          a[i] = (i & 1) ? t0 * 0.0625f : t0;  // odd k of the group meet codes pre-multiplied by 16
         }
-        v[j] = (j & 1) ? a * 0.0625f : a;  // odd k of the group meet codes pre-multiplied by 16
-      }
-      // order 0,4,1,5,2,6,3,7: one 128-bit shared load yields the B registers of both MMAs of a block
-      uint4 hi;
-      hi.x = h2bits(v[0], v[4]); hi.y = h2bits(v[1], v[5]); hi.z = h2bits(v[2], v[6]); hi.w = h2bits(v[3], v[7]);
-      const __half2* hh = reinterpret_cast<const __half2*>(&hi);
-      const float2 a0 = __half22float2(hh[0]), a1 = __half22float2(hh[1]), a2 = __half22float2(hh[2]),
-                   a3 = __half22float2(hh[3]);
-      // block sums carry the zero point: -8 * 2^-24 * sum of the values the MMA effectively sees
-      float hsum = ((a0.x + a0.y) + (a2.x + a2.y)) + 16.f * ((a1.x + a1.y) + (a3.x + a3.y));
-      float lsum = 0.f;
-      const int colh = p.split ? 2 * m : m;
-      if (valid) *reinterpret_cast<uint4*>(xs_h + (size_t)colh * CS + k0) = hi;
-      if (p.split) {
-        uint4 lo;
-        lo.x = h2bits(v[0] - a0.x, v[4] - a0.y); lo.y = h2bits(v[1] - a1.x, v[5] - a1.y);
-        lo.z = h2bits(v[2] - a2.x, v[6] - a2.y); lo.w = h2bits(v[3] - a3.x, v[7] - a3.y);
-        const __half2* ll = reinterpret_cast<const __half2*>(&lo);
-        const float2 b0 = __half22float2(ll[0]), b1 = __half22float2(ll[1]), b2 = __half22float2(ll[2]),
-                     b3 = __half22float2(ll[3]);
-        lsum = ((b0.x + b0.y) + (b2.x + b2.y)) + 16.f * ((b1.x + b1.y) + (b3.x + b3.y));
-        if (valid) *reinterpret_cast<uint4*>(xs_h + (size_t)(colh + 1) * CS + k0) = lo;
-      }
-      hsum += __shfl_xor_sync(0xffffffffu, hsum, 1);
-      hsum += __shfl_xor_sync(0xffffffffu, hsum, 2);
-      lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
-      lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
-      if (valid && (lane & 3) == 0) {
-        const int blk = grp >> 2;
-        xsum[blk * (8 * NT) + colh] = hsum * (-8.0f * 5.9604644775390625e-08f);
-        if (p.split) xsum[blk * (8 * NT) + colh + 1] = lsum * (-8.0f * 5.9604644775390625e-08f);
+        // order 0,4,1,5,2,6,3,7: one 128-bit shared load yields the B registers of both MMAs of a block
+        uint4 hi;
+        hi.x = h2bits(a[0], a[4]); hi.y = h2bits(a[1], a[5]); hi.z = h2bits(a[2], a[6]); hi.w = h2bits(a[3], a[7]);
+        const __half2* hh = reinterpret_cast<const __half2*>(&hi);
+        const float2 a0 = __half22float2(hh[0]), a1 = __half22float2(hh[1]), a2 = __half22float2(hh[2]),
+                     a3 = __half22float2(hh[3]);
+        // block sums carry the zero point: -8 * 2^-24 * sum of the values the MMA effectively sees
+        float hsum = ((a0.x + a0.y) + (a2.x + a2.y)) + 16.f * ((a1.x + a1.y) + (a3.x + a3.y));
+        float lsum = 0.f;
+        if (valid) *reinterpret_cast<uint4*>(xs_h + (size_t)colh * CS + k0) = hi;
+        if (p.split) {
+          uint4 lo;
+          lo.x = h2bits(a[0] - a0.x, a[4] - a0.y); lo.y = h2bits(a[1] - a1.x, a[5] - a1.y);
+          lo.z = h2bits(a[2] - a2.x, a[6] - a2.y); lo.w = h2bits(a[3] - a3.x, a[7] - a3.y);
+          const __half2* ll = reinterpret_cast<const __half2*>(&lo);
+          const float2 b0 = __half22float2(ll[0]), b1 = __half22float2(ll[1]), b2 = __half22float2(ll[2]),
+                       b3 = __half22float2(ll[3]);
+          lsum = ((b0.x + b0.y) + (b2.x + b2.y)) + 16.f * ((b1.x + b1.y) + (b3.x + b3.y));
+          if (valid) *reinterpret_cast<uint4*>(xs_h + (size_t)(colh + 1) * CS + k0) = lo;
+        }
+        hsum += __shfl_xor_sync(0xffffffffu, hsum, 1);
+        hsum += __shfl_xor_sync(0xffffffffu, hsum, 2);
+        lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
+        lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
+        if (valid && (lane & 3) == 0) {
+          const int blk = grp >> 2;
+          xsum[blk * (8 * NT) + colh] = hsum * (-8.0f * 5.9604644775390625e-08f);
+          if (p.split) xsum[blk * (8 * NT) + colh + 1] = lsum * (-8.0f * 5.9604644775390625e-08f);
+        }
       }
     }
   }
-  // unused columns of the block-sum table must be finite (their results are never read)
-  for (int i = tid; i < nblk * 8 * NT; i += kCT)
-    if ((i % (8 * NT)) >= p.cols) xsum[i] = 0.f;
   consumer_sync();
 
   // ---- main loop over this CTA's row tiles -------------------------------------------
@@ -395,8 +427,19 @@ int32_t launch_stream(qeng_ctx* ctx, const StreamParams& p, size_t smem, cudaStr
     configured = true;
   }
   const int grid = p.ntiles < ctx->sm_count ? p.ntiles : ctx->sm_count;
-  gemv_q4_stream_kernel<NT><<<grid, kThreadsS, smem, stream>>>(p);
-  QENG_LAUNCH_CHECK(ctx);
+  // programmatic stream serialization: this kernel may become resident while its predecessor is still
+  // running; everything that depends on the predecessor sits behind griddepcontrol.wait
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kThreadsS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->pdl ? 1 : 0;
+  QENG_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4_stream_kernel<NT>, p));
   return QENG_OK;
 }
 
@@ -411,6 +454,7 @@ int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
   const int split = (x_dtype == QENG_F32 && split_f32) ? 1 : 0;
   const int cols = split ? 2 * (int)M : (int)M;
   if (M < 1 || cols > 32) return QENG_OK;
+  if (w->nchunks * 64 > 8 * kGroups * kCT) return QENG_OK;  // staged through registers: K <= 12288
   const int NT = cols <= 8 ? 1 : (cols <= 16 ? 2 : 4);
   const int64_t Kp = w->nchunks * 64;
   const size_t fixed = (size_t)2 * kMaxStages * 8 + 64                  // barriers

@@ -44,6 +44,7 @@ struct qeng_ctx {
   float* attn_scratch = nullptr;
   size_t attn_scratch_bytes = 0;
   int32_t* status = nullptr;  // device status word (0 = ok)
+  bool pdl = true;            // launch the streaming matmul with programmatic stream serialization
 };
 
 int32_t qeng_fail(qeng_ctx* ctx, int32_t code, const char* fmt, ...);

@@ -14,7 +14,7 @@ import re
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "_lib", "libqeng.so")
+LIB_PATH = os.environ.get("QENG_LIB") or os.path.join(_HERE, "_lib", "libqeng.so")
 HEADER_PATH = os.path.join(_HERE, "..", "include", "qeng.h")
 
 F32, F16, BF16 = 0, 1, 2
