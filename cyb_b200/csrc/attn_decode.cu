@@ -28,6 +28,7 @@ struct AttnParams {
   float* part_ml;  // [B][Hq][S][2]
   float* out;      // [B][Hq][128]
   int32_t* status;
+  int* counters;   // [B][Hkv] arrivals per (sequence, kv head); null = merge in a second kernel
   int pages, Hkv, Hq, grp, max_pages, pps, S;
   float scale_log2;
 };
@@ -56,9 +57,13 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnParams 
   const int len = p.lens[b];
   const int npages = min((len + 15) >> 4, p.max_pages);
   const int p0 = s * p.pps;
-  if (p0 >= npages) return;
-  const int p1 = min(npages, p0 + p.pps);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  if (p0 >= npages) {
+    if (p.counters != nullptr && s == 0)  // empty sequence: nobody else writes its output
+      for (int hh = 0; hh < p.grp; ++hh) p.out[((size_t)b * p.Hq + (size_t)h * p.grp + hh) * kHD + tid] = 0.f;
+    return;
+  }
+  const int p1 = min(npages, p0 + p.pps);
 
   __shared__ float sm_o[kAW][8][kHD];
   __shared__ float sm_m[kAW][8], sm_l[kAW][8];
@@ -186,6 +191,8 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnParams 
     }
   }
   __syncthreads();
+  const int ns = (npages + p.pps - 1) / p.pps;
+  const bool direct = p.counters != nullptr && ns == 1;  // a single split: no partials needed
   for (int hh = 0; hh < p.grp; ++hh) {
     float M = -INFINITY;
 #pragma unroll
@@ -197,13 +204,54 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnParams 
       L += sm_l[w][hh] * f;
       O += sm_o[w][hh][tid] * f;
     }
-    const size_t row = ((size_t)b * p.Hq + (size_t)h * p.grp + hh) * p.S + s;
-    p.part_o[row * kHD + tid] = O;
-    if (tid == 0) {
-      p.part_ml[row * 2] = M;
-      p.part_ml[row * 2 + 1] = L;
+    if (direct) {
+      p.out[((size_t)b * p.Hq + (size_t)h * p.grp + hh) * kHD + tid] = O / L;
+    } else {
+      const size_t row = ((size_t)b * p.Hq + (size_t)h * p.grp + hh) * p.S + s;
+      __stcg(p.part_o + row * kHD + tid, O);
+      if (tid == 0) {
+        __stcg(p.part_ml + row * 2, M);
+        __stcg(p.part_ml + row * 2 + 1, L);
+      }
     }
   }
+  if (p.counters == nullptr || direct) return;
+  // ---- the CTA that completes this (sequence, kv head) merges its splits (no waiting) ----
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_last = atomicAdd(p.counters + b * p.Hkv + h, 1) == ns - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // one warp per query head; lanes first share the (max, sum) pairs of the splits, then each lane
+  // merges 4 of the 128 output dims with independent (pipelined) loads
+  for (int hh = warp; hh < p.grp; hh += kAW) {
+    const size_t row0 = ((size_t)b * p.Hq + (size_t)h * p.grp + hh) * p.S;
+    float M = -INFINITY;
+    for (int s2 = lane; s2 < ns; s2 += 32) M = fmaxf(M, __ldcg(p.part_ml + (row0 + s2) * 2));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    float L = 0.f;
+    for (int s2 = lane; s2 < ns; s2 += 32) {
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + (row0 + s2) * 2));
+      L += ml.y * exp2f(ml.x - M);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int s2 = 0; s2 < ns; ++s2) {
+      const float f = exp2f(__ldcg(p.part_ml + (row0 + s2) * 2) - M);
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(p.part_o + (row0 + s2) * kHD) + lane);
+      O.x = fmaf(v.x, f, O.x); O.y = fmaf(v.y, f, O.y); O.z = fmaf(v.z, f, O.z); O.w = fmaf(v.w, f, O.w);
+    }
+    const float inv = 1.f / L;
+    reinterpret_cast<float4*>(p.out + ((size_t)b * p.Hq + (size_t)h * p.grp + hh) * kHD)[lane] =
+        make_float4(O.x * inv, O.y * inv, O.z * inv, O.w * inv);
+  }
+  __syncthreads();
+  if (tid == 0) p.counters[b * p.Hkv + h] = 0;  // ready for the next call
 }
 
 __global__ void __launch_bounds__(kHD) attn_combine_kernel(const AttnParams p) {
@@ -258,6 +306,8 @@ static __device__ __align__(256) float g_attn_static_scratch[kStaticScratchFloat
 constexpr int kMaxDevices = 64;
 static float* g_attn_static_addr[kMaxDevices] = {};
 
+constexpr int kMaxAttnCounters = 1 << 16;  // (sequence, kv head) pairs per call
+
 // Splits: enough CTAs to fill the machine several times over, at least one page per warp.
 static int pages_per_split(const qeng_ctx* ctx, int64_t B, int64_t Hkv, int64_t max_pages) {
   int64_t target = (int64_t)ctx->sm_count * 8;
@@ -273,7 +323,10 @@ static int pages_per_split(const qeng_ctx* ctx, int64_t B, int64_t Hkv, int64_t 
 int32_t qeng_attn_reserve(qeng_ctx* ctx, int64_t B, int64_t Hq, int64_t Hkv, int64_t max_pages) {
   const int pps = pages_per_split(ctx, B, Hkv, max_pages);
   const int64_t S = (max_pages + pps - 1) / pps;
-  size_t need = (size_t)B * Hq * S * (kHD + 2) * sizeof(float);
+  if (B * Hkv > kMaxAttnCounters)
+    return qeng_fail(ctx, QENG_ERR_SHAPE, "attn: B * kv_heads = %lld exceeds %d", (long long)(B * Hkv), kMaxAttnCounters);
+  // arrival counters first (fixed place for every shape), partials behind them
+  size_t need = (size_t)kMaxAttnCounters * sizeof(int) + (size_t)B * Hq * S * (kHD + 2) * sizeof(float);
   if (need <= ctx->attn_scratch_bytes) return QENG_OK;
   QENG_CUDA(ctx, cudaSetDevice(ctx->device));
   QENG_CUDA(ctx, cudaDeviceSynchronize());
@@ -281,6 +334,7 @@ int32_t qeng_attn_reserve(qeng_ctx* ctx, int64_t B, int64_t Hq, int64_t Hkv, int
   ctx->attn_scratch = nullptr;
   ctx->attn_scratch_bytes = 0;
   QENG_CUDA(ctx, cudaMalloc(&ctx->attn_scratch, need));
+  QENG_CUDA(ctx, cudaMemset(ctx->attn_scratch, 0, need));  // the arrival counters start at zero and return to it
   ctx->attn_scratch_bytes = need;
   return QENG_OK;
 }
@@ -337,7 +391,8 @@ int32_t qeng_attn_decode(qeng_ctx* ctx, const qeng_kv_pool* pool, const uint16_t
   if (B <= 0 || max_pages <= 0 || Hq <= 0) return qeng_fail(ctx, QENG_ERR_ARG, "attn_decode: B, Hq, max_pages must be positive");
   if (Hq % pool->kv_heads != 0 || Hq / pool->kv_heads > 8)
     return qeng_fail(ctx, QENG_ERR_SHAPE, "attn_decode: query heads per kv head must divide evenly and be <= 8");
-  if ((reinterpret_cast<uintptr_t>(q_f16) & 15) != 0) return qeng_fail(ctx, QENG_ERR_ALIGN, "attn_decode: q must be 16-byte aligned");
+  if (((reinterpret_cast<uintptr_t>(q_f16) | reinterpret_cast<uintptr_t>(out)) & 15) != 0)
+    return qeng_fail(ctx, QENG_ERR_ALIGN, "attn_decode: q and out must be 16-byte aligned");
   AttnParams p;
   p.pool = pool->data; p.q = reinterpret_cast<const __half*>(q_f16);
   p.table = page_table; p.lens = lens; p.out = out; p.status = ctx->status;
@@ -348,13 +403,11 @@ int32_t qeng_attn_decode(qeng_ctx* ctx, const qeng_kv_pool* pool, const uint16_t
   p.scale_log2 = scale * 1.4426950408889634f;
   int32_t rc = qeng_attn_reserve(ctx, B, Hq, pool->kv_heads, max_pages);
   if (rc != QENG_OK) return rc;
-  p.part_o = ctx->attn_scratch;
-  p.part_ml = ctx->attn_scratch + (size_t)B * Hq * p.S * kHD;
+  p.counters = reinterpret_cast<int*>(ctx->attn_scratch);
+  p.part_o = ctx->attn_scratch + kMaxAttnCounters;
+  p.part_ml = p.part_o + (size_t)B * Hq * p.S * kHD;
   dim3 grid((unsigned)p.S, (unsigned)p.Hkv, (unsigned)B);
   attn_decode_kernel<<<grid, kAW * 32, 0, (cudaStream_t)stream>>>(p);
-  QENG_LAUNCH_CHECK(ctx);
-  dim3 grid2((unsigned)Hq, (unsigned)B);
-  attn_combine_kernel<<<grid2, kHD, 0, (cudaStream_t)stream>>>(p);
   QENG_LAUNCH_CHECK(ctx);
   return QENG_OK;
 }
@@ -397,6 +450,7 @@ int32_t qeng_attn_decode_noalloc(qeng_ctx* ctx, const qeng_kv_pool* pool, const 
   p.max_pages = (int)max_pages;
   p.scale_log2 = scale * 1.4426950408889634f;
   // every partial that the merge reads is written by this call first: nothing has to start at zero
+  p.counters = nullptr;  // merge in a second kernel
   p.part_o = scratch;
   p.part_ml = scratch + (size_t)B * Hq * p.S * kHD;
   dim3 grid((unsigned)p.S, (unsigned)p.Hkv, (unsigned)B);

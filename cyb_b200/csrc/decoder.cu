@@ -61,7 +61,9 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const float* __restric
   for (int idx = threadIdx.x; idx < (Hq + Hkv) * 64; idx += blockDim.x) {
     const int h = idx >> 6, i = idx & 63;
     const float c = cosr[i], s = cosr[64 + i];
-    const float a = src[h * kHD + i], b = src[h * kHD + i + 64];
+    // the q|k|v rows of a head are stored permuted: dim i sits at 16*((i&63)>>3) + (i&7) + 8*(i>>6)
+    const int pi = ((i >> 3) << 4) + (i & 7);
+    const float a = src[h * kHD + pi], b = src[h * kHD + pi + 8];
     const __half lo = __float2half_rn(a * c - b * s), hi = __float2half_rn(b * c + a * s);
     if (h < Hq) {
       q16[(size_t)row * nq + h * kHD + i] = lo;
@@ -74,8 +76,9 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const float* __restric
   }
   for (int idx = threadIdx.x; idx < nkv; idx += blockDim.x) {
     const int h = idx >> 7, i = idx & 127;
+    const int pi = (((i & 63) >> 3) << 4) + (i & 7) + ((i >> 6) << 3);
     pool[((size_t)pid * Hkv + h) * (2 * kPage * kHD) + kPage * kHD + (ps & 15) * kHD + i] =
-        __float2half_rn(src[nq + nkv + idx]);
+        __float2half_rn(src[nq + nkv + h * kHD + pi]);
   }
 }
 
@@ -173,20 +176,31 @@ int32_t run_layer(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, const int
   if (!L.wqkv || !L.wo || !L.wgu || !L.wdown || !L.norm1 || !L.norm2)
     return qeng_fail(ctx, QENG_ERR_STATE, "decoder: layer %d is not fully loaded", l);
   const int64_t dm = d->cfg.d_model;
+  __half* pool = d->pool + (size_t)l * d->pages * d->Hkv * 2 * kPage * kHD;
   qeng_gemm_fuse f;
   f.norm_gamma = L.norm1; f.norm_eps = d->cfg.rms_eps; f.epilogue = QENG_EPI_STORE;
-  int32_t rc = mm(ctx, d, L.wqkv, d->x, dm, rows, d->qkv, d->nqkv, f, st);
-  if (rc != QENG_OK) return rc;
-  __half* pool = d->pool + (size_t)l * d->pages * d->Hkv * 2 * kPage * kHD;
-  rope_append_kernel<<<(unsigned)rows, 256, 0, st>>>(d->qkv, d->rope_cs, d->pos, table, d->max_pages, (int)d->pages,
-                                                     d->Hq, d->Hkv, d->cfg.max_seq, d->q16, pool, ctx->status);
-  QENG_LAUNCH_CHECK(ctx);
-  d->launches++;
+  int32_t rc;
+  if (rows <= 16 && qeng_gemm_q4_stream_fits(L.wqkv, rows, true)) {
+    // q|k|v projection with rotary embedding, f16 rounding and KV append in its epilogue
+    qeng_qkv_epi E;
+    E.pos = d->pos; E.table = table; E.cs = d->rope_cs; E.q16 = d->q16; E.pool = pool;
+    E.max_pages = d->max_pages; E.pages = (int)d->pages; E.Hq = d->Hq; E.Hkv = d->Hkv; E.max_seq = d->cfg.max_seq;
+    f.epilogue = QENG_EPI_QKV; f.qkv = &E;
+    rc = mm(ctx, d, L.wqkv, d->x, dm, rows, d->qkv, d->nqkv, f, st);
+    if (rc != QENG_OK) return rc;
+  } else {
+    rc = mm(ctx, d, L.wqkv, d->x, dm, rows, d->qkv, d->nqkv, f, st);
+    if (rc != QENG_OK) return rc;
+    rope_append_kernel<<<(unsigned)rows, 256, 0, st>>>(d->qkv, d->rope_cs, d->pos, table, d->max_pages, (int)d->pages,
+                                                       d->Hq, d->Hkv, d->cfg.max_seq, d->q16, pool, ctx->status);
+    QENG_LAUNCH_CHECK(ctx);
+    d->launches++;
+  }
   d->view.pages = d->pages; d->view.kv_heads = d->Hkv; d->view.hd = kHD; d->view.data = pool;
   rc = qeng_attn_decode(ctx, &d->view, reinterpret_cast<const uint16_t*>(d->q16), table, d->max_pages, d->lens, rows,
                         d->Hq, 1.0f / sqrtf((float)kHD), d->att, st);
   if (rc != QENG_OK) return rc;
-  d->launches += 2;
+  d->launches += 1;
   qeng_gemm_fuse fo;
   fo.epilogue = QENG_EPI_ACCUM;
   rc = mm(ctx, d, L.wo, d->att, (int64_t)d->Hq * kHD, rows, d->x, dm, fo, st);
@@ -356,6 +370,19 @@ int32_t qeng_decoder_load_matrix(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, 
   const bool row_split = which == QENG_W_O || which == QENG_W_DOWN;  // split along K, partial sums
   if (row_split) take_shard(q, s, K, 0, N, K / t * r, K / t * (r + 1), hm);
   else take_shard(q, s, K, N / t * r, N / t * (r + 1), 0, K, hm);
+  if (which <= QENG_W_V) {  // rotary pairs (i, i+64) of every head become MMA rows g / g+8 of one tile
+    HostMat pm;
+    pm.N = hm.N; pm.K = hm.K;
+    pm.q.resize(hm.q.size());
+    pm.s.resize(hm.s.size());
+    for (int64_t row = 0; row < hm.N; ++row) {
+      const int64_t head = row / kHD, i = row % kHD;
+      const int64_t prow = head * kHD + (((i & 63) >> 3) << 4) + (i & 7) + ((i >> 6) << 3);
+      memcpy(&pm.q[(size_t)prow * hm.K], &hm.q[(size_t)row * hm.K], (size_t)hm.K);
+      memcpy(&pm.s[(size_t)prow * (hm.K / 32)], &hm.s[(size_t)row * (hm.K / 32)], (size_t)(hm.K / 32) * 2);
+    }
+    hm = pm;
+  }
   int32_t rc = QENG_OK;
   if (row_split) {
     qeng_weight** dst = which == QENG_W_O ? &L.wo : &L.wdown;

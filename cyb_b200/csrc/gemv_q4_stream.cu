@@ -43,6 +43,7 @@ struct StreamParams {
   const float* resid;
   int nstages;
   int32_t* status;
+  qeng_qkv_epi qkv;
 };
 
 // d = a.b + c (m16n8k16, f16 operands, f32 accumulate)
@@ -386,7 +387,50 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
     consumer_sync();
     if (warp == (tcount & (kCW - 1))) {
       const float* rb = red + (size_t)buf * kCW * red_stride;
-      if (p.epilogue == QENG_EPI_SWIGLU) {
+      if (p.epilogue == QENG_EPI_QKV) {
+        const qeng_qkv_epi& E = p.qkv;
+        const int head = tile >> 3, i = ((tile & 7) << 3);
+        for (int e = lane; e < p.M * 8; e += 32) {
+          const int a = e >> 3, r = e & 7;
+          float lo = 0.f, hi = 0.f;  // dims i+r and i+r+64 of this head
+#pragma unroll
+          for (int w = 0; w < kCW; ++w) {
+            lo += rb[w * red_stride + a * 16 + r];
+            hi += rb[w * red_stride + a * 16 + r + 8];
+          }
+          const float os = oscale[a];
+          lo = lo * 16777216.0f * os;
+          hi = hi * 16777216.0f * os;
+          const int ps = E.pos[a];
+          if (ps < 0 || ps >= E.max_seq || (ps >> 4) >= E.max_pages) {
+            atomicExch(p.status, 2);
+            continue;
+          }
+          const int d = i + r;
+          if (head < E.Hq + E.Hkv) {
+            const float c = E.cs[(size_t)ps * 128 + d], sn = E.cs[(size_t)ps * 128 + 64 + d];
+            const float a0 = lo * c - hi * sn, a1 = hi * c + lo * sn;
+            lo = a0;
+            hi = a1;
+          }
+          if (head < E.Hq) {
+            __half* dst = E.q16 + ((size_t)a * E.Hq + head) * 128 + d;
+            dst[0] = __float2half_rn(lo);
+            dst[64] = __float2half_rn(hi);
+          } else {
+            const int pid = E.table[(size_t)a * E.max_pages + (ps >> 4)];
+            if ((unsigned)pid >= (unsigned)E.pages) {
+              atomicExch(p.status, 1);
+              continue;
+            }
+            const int kh = head - E.Hq;
+            const int isv = kh >= E.Hkv ? 1 : 0;
+            __half* dst = E.pool + (((size_t)pid * E.Hkv + (kh - isv * E.Hkv)) * 2 + isv) * (16 * 128) + (ps & 15) * 128 + d;
+            dst[0] = __float2half_rn(lo);
+            dst[64] = __float2half_rn(hi);
+          }
+        }
+      } else if (p.epilogue == QENG_EPI_SWIGLU) {
         for (int e = lane; e < p.M * 8; e += 32) {
           const int a = e >> 3, r = e & 7;
           float gate = 0.f, up = 0.f;
@@ -445,38 +489,65 @@ int32_t launch_stream(qeng_ctx* ctx, const StreamParams& p, size_t smem, cudaStr
 
 }  // namespace
 
+namespace {
+struct StreamFit {
+  bool ok;
+  int split, cols, NT, nstages;
+  size_t smem;
+};
+StreamFit stream_fit(const qeng_weight* w, int x_dtype, int64_t M, bool split_f32) {
+  StreamFit f = {};
+  f.split = (x_dtype == QENG_F32 && split_f32) ? 1 : 0;
+  f.cols = f.split ? 2 * (int)M : (int)M;
+  if (M < 1 || f.cols > 32) return f;
+  if (w->nchunks * 64 > 8 * kGroups * kCT) return f;  // staged through registers: K <= 12288
+  f.NT = f.cols <= 8 ? 1 : (f.cols <= 16 ? 2 : 4);
+  const int64_t Kp = w->nchunks * 64;
+  const size_t fixed = (size_t)2 * kMaxStages * 8 + 64                  // barriers
+                       + (size_t)f.cols * (Kp + 32) * 2                 // staged activations
+                       + (size_t)w->nchunks * 2 * 8 * f.NT * 4          // block sums
+                       + (size_t)2 * kCW * 16 * 8 * f.NT * 4;           // reduction buffers
+  const size_t budget = 226 * 1024 - 512;
+  if (fixed + (size_t)2 * kStageBytes > budget) return f;
+  f.nstages = (int)((budget - fixed) / kStageBytes);
+  if (f.nstages > kMaxStages) f.nstages = kMaxStages;
+  f.smem = (size_t)f.nstages * kStageBytes + fixed;
+  f.ok = true;
+  return f;
+}
+}  // namespace
+
+bool qeng_gemm_q4_stream_fits(const qeng_weight* w, int64_t M, bool split) {
+  return stream_fit(w, QENG_F32, M, split).ok;
+}
+
 // *handled = false when the shape does not fit this kernel (activations too large to keep
 // resident in shared memory); the caller then uses the register-streaming kernel.
 int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t x_dtype, int64_t M,
                             int64_t ldx, float* y, int64_t ldy, bool split_f32, const qeng_gemm_fuse& fuse,
                             cudaStream_t stream, bool* handled) {
   *handled = false;
-  const int split = (x_dtype == QENG_F32 && split_f32) ? 1 : 0;
-  const int cols = split ? 2 * (int)M : (int)M;
-  if (M < 1 || cols > 32) return QENG_OK;
-  if (w->nchunks * 64 > 8 * kGroups * kCT) return QENG_OK;  // staged through registers: K <= 12288
-  const int NT = cols <= 8 ? 1 : (cols <= 16 ? 2 : 4);
-  const int64_t Kp = w->nchunks * 64;
-  const size_t fixed = (size_t)2 * kMaxStages * 8 + 64                  // barriers
-                       + (size_t)cols * (Kp + 32) * 2                   // staged activations
-                       + (size_t)w->nchunks * 2 * 8 * NT * 4            // block sums
-                       + (size_t)2 * kCW * 16 * 8 * NT * 4;             // reduction buffers
-  const size_t budget = 226 * 1024 - 256;
-  if (fixed + (size_t)3 * kStageBytes > budget) return QENG_OK;
-  int nstages = (int)((budget - fixed) / kStageBytes);
-  if (nstages > kMaxStages) nstages = kMaxStages;
+  const StreamFit f = stream_fit(w, x_dtype, M, split_f32);
+  if (!f.ok) {
+    if (fuse.epilogue == QENG_EPI_QKV) return qeng_fail(ctx, QENG_ERR_SHAPE, "gemm_q4: the fused q|k|v epilogue needs the streaming kernel");
+    return QENG_OK;
+  }
   StreamParams p;
   p.qs = w->qs; p.sc = w->sc;
   p.ntiles = (int)w->ntiles; p.nchunks = (int)w->nchunks; p.K = (int)w->K;
-  p.x = x; p.x_dtype = x_dtype; p.ldx = ldx; p.M = (int)M; p.cols = cols; p.split = split;
+  p.x = x; p.x_dtype = x_dtype; p.ldx = ldx; p.M = (int)M; p.cols = f.cols; p.split = f.split;
   p.y = y; p.ldy = ldy;
   p.gamma = fuse.norm_gamma; p.eps = fuse.norm_eps; p.epilogue = fuse.epilogue; p.resid = fuse.resid;
-  p.nstages = nstages; p.status = ctx->status;
-  const size_t smem = (size_t)nstages * kStageBytes + fixed;
+  p.nstages = f.nstages; p.status = ctx->status;
+  p.qkv = qeng_qkv_epi();
+  if (fuse.epilogue == QENG_EPI_QKV) {
+    if (!fuse.qkv) return qeng_fail(ctx, QENG_ERR_ARG, "gemm_q4: fused q|k|v epilogue without its arguments");
+    p.qkv = *fuse.qkv;
+  }
   *handled = true;
-  switch (NT) {
-    case 1: return launch_stream<1>(ctx, p, smem, stream);
-    case 2: return launch_stream<2>(ctx, p, smem, stream);
-    default: return launch_stream<4>(ctx, p, smem, stream);
+  switch (f.NT) {
+    case 1: return launch_stream<1>(ctx, p, f.smem, stream);
+    case 2: return launch_stream<2>(ctx, p, f.smem, stream);
+    default: return launch_stream<4>(ctx, p, f.smem, stream);
   }
 }

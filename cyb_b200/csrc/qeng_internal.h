@@ -66,15 +66,29 @@ int32_t qeng_fail(qeng_ctx* ctx, int32_t code, const char* fmt, ...);
   } while (0)
 
 // ---- fused entry used by the executor (gemv_q4.cu) -------------------------
+// Epilogue of the fused q|k|v projection: rotary embedding, f16 rounding, q to its buffer and
+// k, v straight into the page pool.  The rows of every 128-row head are stored permuted so that
+// MMA rows g / g+8 of one tile are the rotary pair (i, i+64): tile j of a head holds dims
+// 8j..8j+7 then 64+8j..64+8j+7.
+struct qeng_qkv_epi {
+  const int32_t* pos;      // [M] token position of each activation row
+  const int32_t* table;    // [M][max_pages]
+  const float* cs;         // [max_seq][64 cos | 64 sin]
+  __half* q16;             // [M][Hq][128]
+  __half* pool;            // [pages][Hkv][2][16][128]
+  int max_pages, pages, Hq, Hkv, max_seq;
+};
+
 struct qeng_gemm_fuse {
   const float* norm_gamma = nullptr;  // if set: x is RMS-normalised (gain gamma) while it is staged
   float norm_eps = 0.f;
   int epilogue = 0;                   // see QENG_EPI_*
   const float* resid = nullptr;       // QENG_EPI_RESID: y = resid + x.W^T
+  const qeng_qkv_epi* qkv = nullptr;  // QENG_EPI_QKV (streaming kernel only)
 };
 // SWIGLU: rows g (gate) and g+8 (up) of every 16-row tile are combined into one
 // output y[8*tile + g] = silu(gate) * up, so y has N/2 columns.
-enum { QENG_EPI_STORE = 0, QENG_EPI_ACCUM = 1, QENG_EPI_RESID = 2, QENG_EPI_SWIGLU = 3 };
+enum { QENG_EPI_STORE = 0, QENG_EPI_ACCUM = 1, QENG_EPI_RESID = 2, QENG_EPI_SWIGLU = 3, QENG_EPI_QKV = 4 };
 
 int32_t qeng_gemm_q4_decode(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t x_dtype,
                             int64_t M, int64_t ldx, float* y, int64_t ldy, bool split_f32,
@@ -87,3 +101,5 @@ int32_t qeng_attn_reserve(qeng_ctx* ctx, int64_t B, int64_t Hq, int64_t Hkv, int
 int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t x_dtype, int64_t M,
                             int64_t ldx, float* y, int64_t ldy, bool split_f32, const qeng_gemm_fuse& fuse,
                             cudaStream_t stream, bool* handled);
+// true when the streaming kernel takes this shape (its fused-only epilogues may then be used)
+bool qeng_gemm_q4_stream_fits(const qeng_weight* w, int64_t M, bool split);
