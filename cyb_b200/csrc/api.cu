@@ -41,6 +41,12 @@ int32_t qeng_create(int32_t device, qeng_ctx** out) {
     delete ctx;
     return QENG_ERR_CUDA;
   }
+  const size_t tail_slots = (size_t)ctx->sm_count * 4 * 4;  // CTAs x rows of the fused LM head
+  if (cudaMalloc(&ctx->tail_val, tail_slots * 4) != cudaSuccess || cudaMalloc(&ctx->tail_idx, tail_slots * 4) != cudaSuccess ||
+      cudaMalloc(&ctx->tail_cnt, 64) != cudaSuccess || cudaMemset(ctx->tail_cnt, 0, 64) != cudaSuccess) {
+    qeng_destroy(ctx);
+    return QENG_ERR_CUDA;
+  }
   *out = ctx;
   return QENG_OK;
 }
@@ -50,6 +56,9 @@ int32_t qeng_destroy(qeng_ctx* ctx) {
   cudaSetDevice(ctx->device);
   if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);
   if (ctx->status) cudaFree(ctx->status);
+  if (ctx->tail_val) cudaFree(ctx->tail_val);
+  if (ctx->tail_idx) cudaFree(ctx->tail_idx);
+  if (ctx->tail_cnt) cudaFree(ctx->tail_cnt);
   delete ctx;
   return QENG_OK;
 }
@@ -64,6 +73,7 @@ int32_t qeng_device_status(qeng_ctx* ctx) {
   QENG_CUDA(ctx, cudaMemcpy(&status, ctx->status, 4, cudaMemcpyDeviceToHost));
   if (status == 0) return QENG_OK;
   QENG_CUDA(ctx, cudaMemset(ctx->status, 0, 4));
+  QENG_CUDA(ctx, cudaMemset(ctx->tail_cnt, 0, 64));
   return qeng_fail(ctx, QENG_ERR_DEVICE_STATUS,
                    "a kernel reported status %d (1 = page id outside the pool, 2 = position outside the cache, "
                    "3 = token id outside the vocabulary, 4 = a bounded wait on a bulk copy ran out)", status);

@@ -82,18 +82,24 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const float* __restric
   }
 }
 
-// End of a decode step: record the sampled tokens, move every sequence one token on.
+// Unfused end of a decode step (batches the fused LM head does not take): record the sampled
+// tokens as entry step+1, move every sequence one token on.
 __global__ void advance_kernel(const int32_t* __restrict__ next, int32_t* pos, int32_t* lens, int32_t* out_tokens,
                                int32_t* step, int B) {
   const int b = threadIdx.x;
   const int st = *step;
   __syncthreads();
   if (b < B) {
-    out_tokens[(size_t)st * B + b] = next[b];
+    out_tokens[(size_t)(st + 1) * B + b] = next[b];
     pos[b] += 1;
     lens[b] += 1;
   }
   if (b == 0) *step = st + 1;
+}
+
+// Start of a decode call: the token sampled from the logits already present is entry 0.
+__global__ void record_first_kernel(const int32_t* __restrict__ next, int32_t* out_tokens, int B) {
+  if ((int)threadIdx.x < B) out_tokens[threadIdx.x] = next[threadIdx.x];
 }
 
 }  // namespace
@@ -213,33 +219,42 @@ int32_t run_layer(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, const int
   return rc;
 }
 
-int32_t tail(qeng_ctx* ctx, qeng_decoder* d, const float* x_last, int B, cudaStream_t st) {
+// final norm + LM head (+ greedy finalisation: sample, record, advance, embed the next token)
+int32_t tail(qeng_ctx* ctx, qeng_decoder* d, const float* x_last, int B, bool finalize, cudaStream_t st) {
+  if (B <= 4) {
+    qeng_lm_tail t;
+    t.table = d->lm_head; t.x = x_last; t.M = B; t.D = d->cfg.d_model; t.V = d->cfg.vocab; t.logits = d->logits;
+    t.gamma = d->final_norm; t.eps = d->cfg.rms_eps;
+    if (finalize) {
+      t.next = d->next; t.emb = d->emb; t.xout = d->x; t.pos = d->pos; t.lens = d->lens;
+      t.out_tokens = d->out_tokens; t.step = d->step;
+    }
+    d->launches += 1;
+    return qeng_lm_head_fused(ctx, t, st);
+  }
   int32_t rc = qeng_rmsnorm(ctx, x_last, d->final_norm, B, d->cfg.d_model, d->cfg.rms_eps, d->xn, st);
   if (rc != QENG_OK) return rc;
   rc = qeng_lm_head(ctx, d->lm_head, d->xn, B, d->cfg.d_model, d->cfg.vocab, d->logits, st);
   if (rc != QENG_OK) return rc;
   d->launches += 1 + (B + 3) / 4;
-  return QENG_OK;
-}
-
-// one decode step, all state on the device
-int32_t decode_step(qeng_ctx* ctx, qeng_decoder* d, cudaStream_t st) {
-  const int B = d->batch;
-  int32_t rc = qeng_argmax(ctx, d->logits, B, d->cfg.vocab, d->next, st);
-  if (rc != QENG_OK) return rc;
-  rc = qeng_embed(ctx, d->emb, d->next, B, d->cfg.d_model, d->cfg.vocab, d->x, st);
-  if (rc != QENG_OK) return rc;
-  d->launches += 2;
-  for (int l = 0; l < d->cfg.layers; ++l) {
-    rc = run_layer(ctx, d, l, B, d->dec_table, st);
-    if (rc != QENG_OK) return rc;
-  }
-  rc = tail(ctx, d, d->x, B, st);
+  if (!finalize) return QENG_OK;
+  rc = qeng_argmax(ctx, d->logits, B, d->cfg.vocab, d->next, st);
   if (rc != QENG_OK) return rc;
   advance_kernel<<<1, 32 * ((B + 31) / 32), 0, st>>>(d->next, d->pos, d->lens, d->out_tokens, d->step, B);
   QENG_LAUNCH_CHECK(ctx);
-  d->launches++;
-  return QENG_OK;
+  rc = qeng_embed(ctx, d->emb, d->next, B, d->cfg.d_model, d->cfg.vocab, d->x, st);
+  d->launches += 3;
+  return rc;
+}
+
+// one decode step, all state on the device: x holds the embedding of the token to feed
+int32_t decode_step(qeng_ctx* ctx, qeng_decoder* d, cudaStream_t st) {
+  const int B = d->batch;
+  for (int l = 0; l < d->cfg.layers; ++l) {
+    int32_t rc = run_layer(ctx, d, l, B, d->dec_table, st);
+    if (rc != QENG_OK) return rc;
+  }
+  return tail(ctx, d, d->x, B, true, st);
 }
 
 // shard of a full host matrix: rows [r0,r1) x columns [k0,k1)
@@ -291,7 +306,7 @@ int32_t qeng_decoder_create(qeng_ctx* ctx, const qeng_model_cfg* cfg, qeng_decod
   if (e == cudaSuccess) e = cudaMalloc(&d->logits, (size_t)cfg->max_batch * cfg->vocab * 4);
   if (e == cudaSuccess) e = cudaMalloc(&d->next, 64 * 4);
   if (e == cudaSuccess) e = cudaMalloc(&d->step, 4);
-  if (e == cudaSuccess) e = cudaMalloc(&d->out_tokens, (size_t)d->max_steps * cfg->max_batch * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&d->out_tokens, (size_t)(d->max_steps + 1) * cfg->max_batch * 4);
   if (e == cudaSuccess) e = cudaMalloc(&d->dec_table, (size_t)cfg->max_batch * d->max_pages * 4);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&d->own_stream, cudaStreamNonBlocking);
   d->stream = d->own_stream;
@@ -492,7 +507,7 @@ int32_t qeng_decoder_prefill(qeng_ctx* ctx, qeng_decoder* d, const int32_t* toke
     for (int b = 0; b < batch; ++b)
       cudaMemcpyAsync(d->xlast + (size_t)b * d->cfg.d_model, d->x + ((size_t)b * T + T - 1) * d->cfg.d_model,
                       (size_t)d->cfg.d_model * 4, cudaMemcpyDeviceToDevice, st);
-    rc = tail(ctx, d, d->xlast, batch, st);
+    rc = tail(ctx, d, d->xlast, batch, false, st);
   }
   cudaError_t e = cudaStreamSynchronize(st);
   cudaFree(dtok);
@@ -521,6 +536,13 @@ int32_t qeng_decoder_decode(qeng_ctx* ctx, qeng_decoder* d, int32_t steps, int32
   QENG_CUDA(ctx, cudaMemcpyAsync(d->pos, pos.data(), B * 4, cudaMemcpyHostToDevice, st));
   QENG_CUDA(ctx, cudaMemcpyAsync(d->lens, lens.data(), B * 4, cudaMemcpyHostToDevice, st));
   QENG_CUDA(ctx, cudaMemsetAsync(d->step, 0, 4, st));
+  {  // the token sampled from the logits at hand is fed first
+    int32_t rc = qeng_argmax(ctx, d->logits, B, d->cfg.vocab, d->next, st);
+    if (rc == QENG_OK) rc = qeng_embed(ctx, d->emb, d->next, B, d->cfg.d_model, d->cfg.vocab, d->x, st);
+    if (rc != QENG_OK) return rc;
+    record_first_kernel<<<1, 32, 0, st>>>(d->next, d->out_tokens, B);
+    QENG_LAUNCH_CHECK(ctx);
+  }
   QENG_CUDA(ctx, cudaStreamSynchronize(st));
   if (!d->graph || d->graph_batch != B) {
     if (d->graph) { cudaGraphExecDestroy(d->graph); d->graph = nullptr; }

@@ -45,6 +45,10 @@ struct qeng_ctx {
   size_t attn_scratch_bytes = 0;
   int32_t* status = nullptr;  // device status word (0 = ok)
   bool pdl = true;            // launch the streaming matmul with programmatic stream serialization
+  // per-CTA argmax partials and the arrival counter of the fused LM head
+  float* tail_val = nullptr;
+  int32_t* tail_idx = nullptr;
+  int32_t* tail_cnt = nullptr;
 };
 
 int32_t qeng_fail(qeng_ctx* ctx, int32_t code, const char* fmt, ...);
@@ -103,3 +107,22 @@ int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
                             cudaStream_t stream, bool* handled);
 // true when the streaming kernel takes this shape (its fused-only epilogues may then be used)
 bool qeng_gemm_q4_stream_fits(const qeng_weight* w, int64_t M, bool split);
+
+// ops.cu: LM head with optional fused RMSNorm and optional greedy finalisation (argmax over the
+// vocabulary, record the token, advance the sequences, gather the next embedding) in one launch.
+struct qeng_lm_tail {
+  const uint16_t* table = nullptr;  // bf16 [V][D]
+  const float* x = nullptr;         // [M][D]
+  int M = 0, D = 0, V = 0;
+  float* logits = nullptr;          // [M][V]
+  const float* gamma = nullptr;     // fused RMSNorm gain (null = x is used as is)
+  float eps = 0.f;
+  int32_t* next = nullptr;          // [M] sampled token (null = no finalisation)
+  const uint16_t* emb = nullptr;    // bf16 [V][D]
+  float* xout = nullptr;            // [M][D] embedding of the sampled token
+  int32_t* pos = nullptr;           // [M] += 1
+  int32_t* lens = nullptr;          // [M] += 1
+  int32_t* out_tokens = nullptr;    // out_tokens[(*step + 1) * M + m] = token
+  int32_t* step = nullptr;          // += 1
+};
+int32_t qeng_lm_head_fused(qeng_ctx* ctx, const qeng_lm_tail& t, cudaStream_t stream);
