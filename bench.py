@@ -218,11 +218,15 @@ def main():
     m["layers"] = args.layers
     B, K, Wm = args.batch, args.steps, max(args.warmup, 3)
     ctx = qeng.Context(local)
+    if world > 1:
+        def exchange(b):
+            obj = [b]
+            dist.broadcast_object_list(obj, src=0)
+            return obj[0]
+        ctx.tp_init(rank, world, exchange)
     max_seq = PROMPT + Wm + 2 * K + 64
     dec = ctx.decoder(layers=m["layers"], d_model=m["d"], ffn=m["ffn"], heads=m["heads"], kv_heads=m["kv_heads"],
                       vocab=m["vocab"], max_batch=B, max_seq=max_seq, tp_rank=rank, tp_world=world)
-    if world > 1:
-        dec.init_tp(dist)
     t_load = time.perf_counter()
     for l in range(m["layers"]):
         for j, (nm, n, k) in enumerate(layer_shapes(m)):

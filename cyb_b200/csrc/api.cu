@@ -54,6 +54,7 @@ int32_t qeng_create(int32_t device, qeng_ctx** out) {
 int32_t qeng_destroy(qeng_ctx* ctx) {
   if (!ctx) return QENG_ERR_ARG;
   cudaSetDevice(ctx->device);
+  qeng_tp_release(ctx);
   if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);
   if (ctx->status) cudaFree(ctx->status);
   if (ctx->tail_val) cudaFree(ctx->tail_val);

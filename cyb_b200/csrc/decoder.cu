@@ -119,7 +119,7 @@ struct qeng_decoder {
   qeng_kv_pool view;           // per-layer view handed to the attention entry point
   // activations (rows = batch in decode, batch*T in prefill)
   int64_t rows_cap = 0;
-  float *x = nullptr, *qkv = nullptr, *att = nullptr, *act = nullptr;
+  float *x = nullptr, *qkv = nullptr, *att = nullptr, *act = nullptr, *part = nullptr;
   __half* q16 = nullptr;
   int32_t *pos = nullptr, *lens = nullptr, *table = nullptr;  // per row
   // decode state
@@ -141,7 +141,7 @@ namespace {
 int32_t ensure_rows(qeng_ctx* ctx, qeng_decoder* d, int64_t rows) {
   if (rows <= d->rows_cap) return QENG_OK;
   QENG_CUDA(ctx, cudaDeviceSynchronize());
-  float** fb[] = {&d->x, &d->qkv, &d->att, &d->act};
+  float** fb[] = {&d->x, &d->qkv, &d->att, &d->act, &d->part};
   for (auto p : fb)
     if (*p) { cudaFree(*p); *p = nullptr; }
   if (d->q16) { cudaFree(d->q16); d->q16 = nullptr; }
@@ -154,6 +154,7 @@ int32_t ensure_rows(qeng_ctx* ctx, qeng_decoder* d, int64_t rows) {
   QENG_CUDA(ctx, cudaMalloc(&d->qkv, rows * d->nqkv * 4));
   QENG_CUDA(ctx, cudaMalloc(&d->att, rows * d->Hq * kHD * 4));
   QENG_CUDA(ctx, cudaMalloc(&d->act, rows * d->F * 4));
+  QENG_CUDA(ctx, cudaMalloc(&d->part, rows * dm * 4));
   QENG_CUDA(ctx, cudaMalloc(&d->q16, rows * d->Hq * kHD * 2));
   QENG_CUDA(ctx, cudaMalloc(&d->pos, rows * 4));
   QENG_CUDA(ctx, cudaMalloc(&d->lens, rows * 4));
@@ -173,6 +174,33 @@ int32_t mm(qeng_ctx* ctx, qeng_decoder* d, const qeng_weight* w, const float* x,
     if (rc != QENG_OK) return rc;
     d->launches++;
   }
+  return QENG_OK;
+}
+
+// Row-split projection: x += in . W^T summed over the ranks.  One rank: the residual add is the
+// matmul's epilogue.  Several ranks: partial sums, all-reduce over NVLink, then the add.
+__global__ void add_inplace_kernel(float* __restrict__ x, const float* __restrict__ p, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] += p[i];
+}
+
+int32_t row_split(qeng_ctx* ctx, qeng_decoder* d, const qeng_weight* w, const float* in, int64_t ldin, int64_t rows,
+                  cudaStream_t st) {
+  const int64_t dm = d->cfg.d_model;
+  qeng_gemm_fuse f;
+  if (d->cfg.tp_world == 1) {
+    f.epilogue = QENG_EPI_ACCUM;
+    return mm(ctx, d, w, in, ldin, rows, d->x, dm, f, st);
+  }
+  f.epilogue = QENG_EPI_STORE;
+  int32_t rc = mm(ctx, d, w, in, ldin, rows, d->part, dm, f, st);
+  if (rc != QENG_OK) return rc;
+  rc = qeng_tp_all_reduce_internal(ctx, d->part, rows * dm, st);
+  if (rc != QENG_OK) return rc;
+  const int64_t n = rows * dm;
+  add_inplace_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(d->x, d->part, n);
+  QENG_LAUNCH_CHECK(ctx);
+  d->launches += 2;
   return QENG_OK;
 }
 
@@ -207,16 +235,13 @@ int32_t run_layer(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, const int
                         d->Hq, 1.0f / sqrtf((float)kHD), d->att, st);
   if (rc != QENG_OK) return rc;
   d->launches += 1;
-  qeng_gemm_fuse fo;
-  fo.epilogue = QENG_EPI_ACCUM;
-  rc = mm(ctx, d, L.wo, d->att, (int64_t)d->Hq * kHD, rows, d->x, dm, fo, st);
+  rc = row_split(ctx, d, L.wo, d->att, (int64_t)d->Hq * kHD, rows, st);
   if (rc != QENG_OK) return rc;
   qeng_gemm_fuse fg;
   fg.norm_gamma = L.norm2; fg.norm_eps = d->cfg.rms_eps; fg.epilogue = QENG_EPI_SWIGLU;
   rc = mm(ctx, d, L.wgu, d->x, dm, rows, d->act, d->F, fg, st);
   if (rc != QENG_OK) return rc;
-  rc = mm(ctx, d, L.wdown, d->act, d->F, rows, d->x, dm, fo, st);
-  return rc;
+  return row_split(ctx, d, L.wdown, d->act, d->F, rows, st);
 }
 
 // final norm + LM head (+ greedy finalisation: sample, record, advance, embed the next token)
@@ -287,6 +312,8 @@ int32_t qeng_decoder_create(qeng_ctx* ctx, const qeng_model_cfg* cfg, qeng_decod
     return qeng_fail(ctx, QENG_ERR_SHAPE, "decoder_create: shapes do not shard evenly over %d ranks", t);
   if (cfg->max_batch < 1 || cfg->max_batch > 16 || cfg->max_seq < 1)
     return qeng_fail(ctx, QENG_ERR_SHAPE, "decoder_create: max_batch must be 1..16 and max_seq positive");
+  if (t > 1 && (ctx->tp_world != t || ctx->tp_rank != cfg->tp_rank))
+    return qeng_fail(ctx, QENG_ERR_STATE, "decoder_create: call qeng_tp_init(rank %d, world %d) on this context first", cfg->tp_rank, t);
   QENG_CUDA(ctx, cudaSetDevice(ctx->device));
   qeng_decoder* d = new qeng_decoder();
   d->cfg = *cfg;
@@ -352,7 +379,7 @@ int32_t qeng_decoder_free(qeng_ctx* ctx, qeng_decoder* d) {
     if (L.norm1) cudaFree(L.norm1);
     if (L.norm2) cudaFree(L.norm2);
   }
-  void* bufs[] = {d->emb, d->lm_head, d->final_norm, d->rope_cs, d->pool, d->x, d->qkv, d->att, d->act, d->q16,
+  void* bufs[] = {d->emb, d->lm_head, d->final_norm, d->rope_cs, d->pool, d->x, d->qkv, d->att, d->act, d->part, d->q16,
                   d->pos, d->lens, d->table, d->xn, d->xlast, d->logits, d->next, d->out_tokens, d->step, d->dec_table};
   for (void* p : bufs)
     if (p) cudaFree(p);

@@ -44,6 +44,9 @@ struct qeng_ctx {
   float* attn_scratch = nullptr;
   size_t attn_scratch_bytes = 0;
   int32_t* status = nullptr;  // device status word (0 = ok)
+  // tensor parallelism (tp.cu)
+  void* nccl_comm = nullptr;
+  int tp_rank = 0, tp_world = 1;
   bool pdl = true;            // launch the streaming matmul with programmatic stream serialization
   // per-CTA argmax partials and the arrival counter of the fused LM head
   float* tail_val = nullptr;
@@ -126,3 +129,7 @@ struct qeng_lm_tail {
   int32_t* step = nullptr;          // += 1
 };
 int32_t qeng_lm_head_fused(qeng_ctx* ctx, const qeng_lm_tail& t, cudaStream_t stream);
+
+// tp.cu
+int32_t qeng_tp_all_reduce_internal(qeng_ctx* ctx, float* buf, int64_t n, cudaStream_t stream);
+void qeng_tp_release(qeng_ctx* ctx);

@@ -68,6 +68,9 @@ _sig("qeng_destroy", _i32, _vp)
 _sig("qeng_last_error", C.c_char_p, _vp)
 _sig("qeng_device_status", _i32, _vp)
 _sig("qeng_sm_count", _i32, _vp)
+_sig("qeng_tp_unique_id", _i32, _vp)
+_sig("qeng_tp_init", _i32, _vp, _i32, _i32, _vp)
+_sig("qeng_tp_all_reduce_f32", _i32, _vp, _vp, _i64, _vp)
 _sig("qeng_weight_pack_q4", _i32, _vp, _vp, _vp, _i64, _i64, C.POINTER(_vp))
 _sig("qeng_weight_unpack_q4", _i32, _vp, _vp, _vp, _vp)
 _sig("qeng_weight_dequant_f32", _i32, _vp, _vp, _vp, _vp)
@@ -148,6 +151,23 @@ class Context:
     @property
     def sm_count(self):
         return _lib.qeng_sm_count(self.h)
+
+    # ---- tensor parallelism ---------------------------------------------------
+    def tp_init(self, rank, world, exchange):
+        """Collective.  `exchange(bytes_or_None) -> bytes` must broadcast rank 0's 128-byte id
+        to every rank over any host channel (e.g. torch.distributed.broadcast_object_list)."""
+        buf = (C.c_uint8 * 128)()
+        if rank == 0:
+            rc = _lib.qeng_tp_unique_id(buf)
+            if rc != 0:
+                raise QengError(rc, "qeng_tp_unique_id failed (libnccl.so.2 not loadable?)")
+        ident = exchange(bytes(buf) if rank == 0 else None)
+        arr = (C.c_uint8 * 128).from_buffer_copy(ident)
+        self.check(_lib.qeng_tp_init(self.h, rank, world, arr))
+
+    def all_reduce_(self, t):
+        self.check(_lib.qeng_tp_all_reduce_f32(self.h, _dev_ptr(t), t.numel(), _cur_stream()))
+        return t
 
     def device_status(self):
         self.check(_lib.qeng_device_status(self.h))

@@ -70,6 +70,16 @@ int32_t qeng_device_status(qeng_ctx* ctx);
 /* SM count of the context's device (grid sizing, reporting). */
 int32_t qeng_sm_count(const qeng_ctx* ctx);
 
+/* ---- tensor parallelism (not in the reference: its runtime is single-device; the
+ *      sharding is BASELINE's: column-split q/k/v/gate/up, row-split o/down, one sum
+ *      after each row-split projection) ----------------------------------------------
+ * One context per GPU and rank.  Rank 0 makes an id, the host program hands the 128
+ * bytes to every rank (any channel), every rank calls qeng_tp_init (collective). */
+int32_t qeng_tp_unique_id(uint8_t* out128);
+int32_t qeng_tp_init(qeng_ctx* ctx, int32_t rank, int32_t world, const uint8_t* id128);
+/* In-place sum of buf[n] (f32, device) over the ranks, on `stream` (NCCL over NVLink). */
+int32_t qeng_tp_all_reduce_f32(qeng_ctx* ctx, float* buf, int64_t n, void* stream);
+
 /* ---- 4-bit block weights ("Q4_0 ... for all backends", decide/pipeline.md:38,59;
  *      "tensor data (Q4/Q8/F16/F32)", decide/pipeline.md:28) --------------------
  * Import: q[N*K] holds one code 0..15 per byte (row-major, K contiguous),

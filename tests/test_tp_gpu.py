@@ -1,0 +1,77 @@
+"""Tensor parallelism on real GPUs (needs >= 2): two ranks, NCCL all-reduce after the row-split
+projections; tokens and logits must match the unsharded oracle decoder."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from oracle import ref
+
+pytestmark = pytest.mark.gpu
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "golden.npz"))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _rank_main(rank, world, port, out):
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from cyb_b200 import qeng
+    ctx = qeng.Context(rank)
+
+    def exchange(b):
+        obj = [b]
+        dist.broadcast_object_list(obj, src=0)
+        return obj[0]
+    ctx.tp_init(rank, world, exchange)
+    t = torch.full((1000,), float(rank + 1), device="cuda")
+    ctx.all_reduce_(t)
+    torch.cuda.synchronize()
+    assert float(t[0]) == sum(range(1, world + 1))
+    cfg = ref.DecoderConfig(layers=2, d=256, ffn=512, heads=4, kv_heads=2, vocab=320)
+    W = ref.make_decoder_weights(cfg, seed=5)
+    dec = ctx.decoder(layers=2, d_model=256, ffn=512, heads=4, kv_heads=2, vocab=320, max_batch=2, max_seq=64,
+                      tp_rank=rank, tp_world=world)
+    qeng.load_decoder_weights(dec, W, cfg)
+    prompt = GOLD["dec_prompt"]
+    dec.reset(prompt.shape[0])
+    dec.prefill(prompt)
+    e = ref.err_inf(dec.logits(), GOLD["dec_logits"][0])
+    toks = dec.decode(GOLD["dec_tokens"].shape[1])
+    ctx.device_status()
+    out.put((rank, e, toks.tolist()))
+    dist.barrier()
+    dec.free()
+    dist.destroy_process_group()
+
+
+def test_two_rank_decoder_matches_golden(built_lib):
+    import torch
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [out.get(timeout=300) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank, e, toks in res:
+        assert e < 2e-3, (rank, e)
+        assert toks == GOLD["dec_tokens"].tolist(), rank
