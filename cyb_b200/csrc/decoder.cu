@@ -120,6 +120,7 @@ struct qeng_decoder {
   // activations (rows = batch in decode, batch*T in prefill)
   int64_t rows_cap = 0;
   float *x = nullptr, *qkv = nullptr, *att = nullptr, *act = nullptr, *part = nullptr;
+  float *xnr = nullptr, *gu = nullptr;  // prefill only: normalised rows, gate|up before SwiGLU
   __half* q16 = nullptr;
   int32_t *pos = nullptr, *lens = nullptr, *table = nullptr;  // per row
   // decode state
@@ -141,7 +142,7 @@ namespace {
 int32_t ensure_rows(qeng_ctx* ctx, qeng_decoder* d, int64_t rows) {
   if (rows <= d->rows_cap) return QENG_OK;
   QENG_CUDA(ctx, cudaDeviceSynchronize());
-  float** fb[] = {&d->x, &d->qkv, &d->att, &d->act, &d->part};
+  float** fb[] = {&d->x, &d->qkv, &d->att, &d->act, &d->part, &d->xnr, &d->gu};
   for (auto p : fb)
     if (*p) { cudaFree(*p); *p = nullptr; }
   if (d->q16) { cudaFree(d->q16); d->q16 = nullptr; }
@@ -155,6 +156,10 @@ int32_t ensure_rows(qeng_ctx* ctx, qeng_decoder* d, int64_t rows) {
   QENG_CUDA(ctx, cudaMalloc(&d->att, rows * d->Hq * kHD * 4));
   QENG_CUDA(ctx, cudaMalloc(&d->act, rows * d->F * 4));
   QENG_CUDA(ctx, cudaMalloc(&d->part, rows * dm * 4));
+  if (rows >= kPrefillRows) {
+    QENG_CUDA(ctx, cudaMalloc(&d->xnr, rows * dm * 4));
+    QENG_CUDA(ctx, cudaMalloc(&d->gu, rows * 2 * d->F * 4));
+  }
   QENG_CUDA(ctx, cudaMalloc(&d->q16, rows * d->Hq * kHD * 2));
   QENG_CUDA(ctx, cudaMalloc(&d->pos, rows * 4));
   QENG_CUDA(ctx, cudaMalloc(&d->lens, rows * 4));
@@ -204,11 +209,58 @@ int32_t row_split(qeng_ctx* ctx, qeng_decoder* d, const qeng_weight* w, const fl
   return QENG_OK;
 }
 
+// gate|up rows are interleaved 8/8 per 16-row tile: act[m][8j + r] = silu(gu[m][16j + r]) * gu[m][16j + r + 8]
+__global__ void swiglu_interleaved_kernel(const float* __restrict__ gu, int64_t rows, int F, float* __restrict__ act) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * F) return;
+  const int64_t m = i / F;
+  const int c = (int)(i - m * F);
+  const float* src = gu + m * 2 * F + (c >> 3) * 16 + (c & 7);
+  const float g = src[0];
+  act[i] = g / (1.0f + __expf(-g)) * src[8];
+}
+
+// The same layer for many rows (prompt phase): unfused small operators around the tensor-core matmul.
+int32_t run_layer_prefill(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, const int32_t* table, cudaStream_t st) {
+  Layer& L = d->layers[l];
+  const int64_t dm = d->cfg.d_model, nq = (int64_t)d->Hq * kHD;
+  const bool tp = d->cfg.tp_world > 1;
+  __half* pool = d->pool + (size_t)l * d->pages * d->Hkv * 2 * kPage * kHD;
+  int32_t rc = qeng_rmsnorm(ctx, d->x, L.norm1, rows, dm, d->cfg.rms_eps, d->xnr, st);
+  if (rc == QENG_OK) rc = qeng_gemm_q4_prefill(ctx, L.wqkv, d->xnr, QENG_F32, rows, dm, d->qkv, d->nqkv, 0, st);
+  if (rc != QENG_OK) return rc;
+  rope_append_kernel<<<(unsigned)rows, 256, 0, st>>>(d->qkv, d->rope_cs, d->pos, table, d->max_pages, (int)d->pages,
+                                                     d->Hq, d->Hkv, d->cfg.max_seq, d->q16, pool, ctx->status);
+  QENG_LAUNCH_CHECK(ctx);
+  d->view.pages = d->pages; d->view.kv_heads = d->Hkv; d->view.hd = kHD; d->view.data = pool;
+  rc = qeng_attn_decode(ctx, &d->view, reinterpret_cast<const uint16_t*>(d->q16), table, d->max_pages, d->lens, rows,
+                        d->Hq, 1.0f / sqrtf((float)kHD), d->att, st);
+  if (rc != QENG_OK) return rc;
+  const int64_t n = rows * dm;
+  auto row_split_tc = [&](const qeng_weight* w, const float* in, int64_t ldin) -> int32_t {
+    if (!tp) return qeng_gemm_q4_prefill(ctx, w, in, QENG_F32, rows, ldin, d->x, dm, 1, st);
+    int32_t r = qeng_gemm_q4_prefill(ctx, w, in, QENG_F32, rows, ldin, d->part, dm, 0, st);
+    if (r == QENG_OK) r = qeng_tp_all_reduce_internal(ctx, d->part, n, st);
+    if (r != QENG_OK) return r;
+    add_inplace_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(d->x, d->part, n);
+    return QENG_OK;
+  };
+  rc = row_split_tc(L.wo, d->att, nq);
+  if (rc == QENG_OK) rc = qeng_rmsnorm(ctx, d->x, L.norm2, rows, dm, d->cfg.rms_eps, d->xnr, st);
+  if (rc == QENG_OK) rc = qeng_gemm_q4_prefill(ctx, L.wgu, d->xnr, QENG_F32, rows, dm, d->gu, 2 * d->F, 0, st);
+  if (rc != QENG_OK) return rc;
+  const int64_t na = rows * d->F;
+  swiglu_interleaved_kernel<<<(unsigned)((na + 255) / 256), 256, 0, st>>>(d->gu, rows, d->F, d->act);
+  QENG_LAUNCH_CHECK(ctx);
+  return row_split_tc(L.wdown, d->act, d->F);
+}
+
 // One layer over `rows` rows whose positions / lengths / page-table rows are on the device.
 int32_t run_layer(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, const int32_t* table, cudaStream_t st) {
   Layer& L = d->layers[l];
   if (!L.wqkv || !L.wo || !L.wgu || !L.wdown || !L.norm1 || !L.norm2)
     return qeng_fail(ctx, QENG_ERR_STATE, "decoder: layer %d is not fully loaded", l);
+  if (rows >= kPrefillRows) return run_layer_prefill(ctx, d, l, rows, table, st);
   const int64_t dm = d->cfg.d_model;
   __half* pool = d->pool + (size_t)l * d->pages * d->Hkv * 2 * kPage * kHD;
   qeng_gemm_fuse f;
@@ -379,7 +431,7 @@ int32_t qeng_decoder_free(qeng_ctx* ctx, qeng_decoder* d) {
     if (L.norm1) cudaFree(L.norm1);
     if (L.norm2) cudaFree(L.norm2);
   }
-  void* bufs[] = {d->emb, d->lm_head, d->final_norm, d->rope_cs, d->pool, d->x, d->qkv, d->att, d->act, d->part, d->q16,
+  void* bufs[] = {d->emb, d->lm_head, d->final_norm, d->rope_cs, d->pool, d->x, d->qkv, d->att, d->act, d->part, d->xnr, d->gu, d->q16,
                   d->pos, d->lens, d->table, d->xn, d->xlast, d->logits, d->next, d->out_tokens, d->step, d->dec_table};
   for (void* p : bufs)
     if (p) cudaFree(p);

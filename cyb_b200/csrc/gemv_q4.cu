@@ -344,6 +344,8 @@ int32_t qeng_gemm_q4(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t
   if (x_dtype < QENG_F32 || x_dtype > QENG_BF16) return qeng_fail(ctx, QENG_ERR_ARG, "gemm_q4: bad x_dtype %d", x_dtype);
   if (M < 1) return qeng_fail(ctx, QENG_ERR_SHAPE, "gemm_q4: M=%lld", (long long)M);
   if (ldx < w->K || ldy < w->N) return qeng_fail(ctx, QENG_ERR_SHAPE, "gemm_q4: leading dimension smaller than the row");
+  if (M >= kPrefillRows)  // dense contraction: dequantise to bf16 in shared memory, tcgen05 MMA
+    return qeng_gemm_q4_prefill(ctx, w, x, x_dtype, M, ldx, y, ldy, (flags & QENG_GEMM_ACCUMULATE) ? 1 : 0, (cudaStream_t)stream);
   qeng_gemm_fuse fuse;
   fuse.epilogue = (flags & QENG_GEMM_ACCUMULATE) ? QENG_EPI_ACCUM : QENG_EPI_STORE;
   const bool split = x_dtype == QENG_F32 && !(flags & QENG_GEMM_FAST_F16);

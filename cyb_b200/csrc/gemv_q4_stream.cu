@@ -71,15 +71,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   asm volatile(
       "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
       : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(100000u)
+      : "r"(bar), "r"(parity), "r"(1000u)
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up (false) after 2^24 attempts, which is seconds; a healthy wait ends in microseconds.
+// Bounded wait: gives up (false) two seconds after the first failed attempt; a healthy wait ends
+// in microseconds.  The clock is read once per 64 attempts.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (int i = 0; i < (1 << 24); ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t0));
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t1;
+    asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t1));
+    if (t1 - t0 > 2000000000ull) return false;
+  }
 }
 // 1-D bulk copy global -> shared, completion counted in bytes on the mbarrier
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {

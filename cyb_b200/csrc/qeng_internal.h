@@ -44,6 +44,9 @@ struct qeng_ctx {
   float* attn_scratch = nullptr;
   size_t attn_scratch_bytes = 0;
   int32_t* status = nullptr;  // device status word (0 = ok)
+  // bf16 copy of f32 activations for the tensor-core prefill matmul
+  void* xbf16 = nullptr;
+  size_t xbf16_bytes = 0;
   // tensor parallelism (tp.cu)
   void* nccl_comm = nullptr;
   int tp_rank = 0, tp_world = 1;
@@ -133,3 +136,8 @@ int32_t qeng_lm_head_fused(qeng_ctx* ctx, const qeng_lm_tail& t, cudaStream_t st
 // tp.cu
 int32_t qeng_tp_all_reduce_internal(qeng_ctx* ctx, float* buf, int64_t n, cudaStream_t stream);
 void qeng_tp_release(qeng_ctx* ctx);
+
+// gemm_q4_tc.cu: tcgen05 prefill matmul (bf16 operands, f32 accumulation in tensor memory)
+int32_t qeng_gemm_q4_prefill(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t x_dtype, int64_t M, int64_t ldx,
+                             float* y, int64_t ldy, int accumulate, cudaStream_t stream);
+constexpr int64_t kPrefillRows = 256;  // from this many rows on, matmuls take the tensor-core path

@@ -100,8 +100,9 @@ int64_t qeng_weight_device_bytes(const qeng_weight* w);
 
 /* ---- quantized matmul (the "QKV / O proj / FFN" steps of decide/pipeline.md:51)
  * y[M,N] (f32, leading dimension ldy) = x[M,K] (x_dtype, leading dimension ldx)
- * . dequant(W)^T, f32 accumulation.  M <= 256 runs the decode kernel
- * (dequantise in registers); larger M the tensor-core prefill kernel. */
+ * . dequant(W)^T, f32 accumulation.  M < 256 runs the decode kernels (dequantise in
+ * registers, activations exact); M >= 256 the tensor-core prefill kernel, which rounds
+ * activations and dequantised weights to bf16 (tolerance 5e-3 instead of 2e-3). */
 int32_t qeng_gemm_q4(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t x_dtype,
                      int64_t M, int64_t ldx, float* y, int64_t ldy, int32_t flags, void* stream);
 /* M = 1, f32 activations: the decode GEMV. */

@@ -73,3 +73,22 @@ def test_state_errors(ctx):
         dec.prefill(np.zeros((1, 33), np.int32))  # longer than the cache
     assert e.value.code == -2
     dec.free()
+
+
+def test_teacher_forced_layer_on_the_tensor_core_path(ctx):
+    """256 rows or more take the tcgen05 matmul (bf16 operands): gate 5e-3 per layer against the
+    unrounded float64 teacher; the decode step on top of that cache is back on the exact path."""
+    import torch
+    cfg, W, dec = _make(ctx, max_batch=1, max_seq=320)
+    teacher = ref.Decoder(cfg, W)
+    teacher.reset(1)
+    rng = ref.rng_of(41)
+    T = 272
+    x = rng.standard_normal((1, T, cfg.d), dtype=np.float32)
+    pos = np.arange(T)
+    want = teacher.layer(0, x.astype(np.float64), pos[None])
+    got = dec.layer(0, torch.from_numpy(x[0]).cuda(), pos).cpu().numpy()
+    ctx.device_status()
+    e = ref.err_inf(got, want[0])
+    assert e < 5e-3, e
+    dec.free()

@@ -133,3 +133,24 @@ def test_linearity_at_full_size(ctx):
     lin = (2 * y1 - 3 * y2)
     assert float((y3 - lin).abs().max() / lin.abs().max()) < 1e-5
     w.free()
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 128, 64), (300, 144, 96), (512, 1376, 4096), (512, 11008, 4096), (512, 4096, 11008)])
+def test_prefill_tensor_core_path(ctx, m, n, k):
+    """M >= 256 takes the tcgen05 kernel: activations and dequantised weights are rounded to bf16
+    (tolerance 5e-3 against the unrounded oracle; ~1e-5 against the oracle with the same roundings)."""
+    import torch
+    rng = ref.rng_of(1000 + m + n + k)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    q, s = ref.make_q4(rng, n, k)
+    w = ctx.pack_q4(q, s)
+    y = ctx.gemm_q4(w, _t(x)).cpu().numpy()
+    ctx.device_status()
+    xb = ref.to_bf16(x)
+    same = ref.gemm_q4_bf16w(xb, q, s)
+    assert ref.err_inf(y, same) < 2e-5, ref.err_inf(y, same)
+    assert ref.err_inf(y, ref.gemm_q4_fast(x, q, s)) < 5e-3
+    # bf16 activations go in directly; accumulate adds to what is there
+    yb = ctx.gemm_q4(w, _t(xb).to(torch.bfloat16), out=_t(y.copy()), flags=1).cpu().numpy()
+    assert ref.err_inf(yb, 2 * same) < 2e-5
+    w.free()
