@@ -3,6 +3,7 @@
     python -m cyb_b200.microbench gemv --n 4096 --k 4096 [--m 1] [--dtype f32|bf16] [--pool 24] [--iters 20]
     python -m cyb_b200.microbench attn [--batch 16] [--lo 512] [--hi 4096]
     python -m cyb_b200.microbench lmhead [--m 1]
+    python -m cyb_b200.microbench prefill [--m 2048] [--n 11008] [--k 4096]
 
 `gemv` rotates through a pool of distinct packed weights larger than the 126 MB
 L2, so every launch streams its weights from HBM; the figure printed is
@@ -123,6 +124,32 @@ def lmhead(args):
     print(json.dumps({"kernel": "lm_head", "m": args.m, "us_per_call": us, "algo_bytes": algo, "gbs": algo / us / 1e3}))
 
 
+def prefill(args):
+    import torch
+    from cyb_b200 import qeng
+    ctx = qeng.Context(0)
+    n, k, m = args.n, args.k, args.m
+    rng = np.random.Generator(np.random.PCG64(0))
+    q = rng.integers(0, 16, (n, k), dtype=np.uint8)
+    s = rng.uniform(0.002, 0.02, (n, k // 32)).astype(np.float16)
+    w = ctx.pack_q4(q, s)
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    y = torch.empty(m, n, device="cuda")
+    for _ in range(3):
+        ctx.gemm_q4(w, x, out=y)
+    e0, e1 = _events(torch)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.iters):
+        ctx.gemm_q4(w, x, out=y)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.iters
+    ctx.device_status()
+    print(json.dumps({"kernel": "gemm_q4 (tcgen05 prefill)", "m": m, "n": n, "k": k, "ms": ms,
+                      "tflops": 2.0 * m * n * k / ms / 1e9}))
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="cyb_b200.microbench")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -143,8 +170,13 @@ def main(argv=None):
     l = sub.add_parser("lmhead")
     l.add_argument("--m", type=int, default=1)
     l.add_argument("--iters", type=int, default=10)
+    pf = sub.add_parser("prefill")
+    pf.add_argument("--m", type=int, default=2048)
+    pf.add_argument("--n", type=int, default=11008)
+    pf.add_argument("--k", type=int, default=4096)
+    pf.add_argument("--iters", type=int, default=10)
     args = ap.parse_args(argv)
-    {"gemv": gemv, "attn": attn, "lmhead": lmhead}[args.cmd](args)
+    {"gemv": gemv, "attn": attn, "lmhead": lmhead, "prefill": prefill}[args.cmd](args)
 
 
 if __name__ == "__main__":
