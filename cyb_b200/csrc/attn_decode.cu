@@ -11,6 +11,7 @@
 //
 // HBM-bound: algorithmic bytes = sum_b len_b * kv_heads * 2 * 128 * 2.
 #include <math.h>
+#include <stdlib.h>
 
 #include "qeng_internal.h"
 
@@ -85,29 +86,38 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnParams 
 #pragma unroll
     for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
 
-  for (int pg = p0 + warp; pg < p1; pg += kAW) {
-    const int pid = p.table[(size_t)b * p.max_pages + pg];
+  // Page tiles are double-buffered in registers: the loads of the next tile are in flight while the
+  // tensor cores work on the current one.
+  // all page ids of this warp are fetched up front (lane i holds the id of the warp's i-th page), so a
+  // tile load is one memory round trip, not a table lookup followed by a dependent load
+  int my_pid = -1;
+  {
+    const int pg = p0 + warp + lane * kAW;  // at most 64 pages per split: 16 per warp
+    if (pg < p1) my_pid = p.table[(size_t)b * p.max_pages + pg];
+  }
+  auto load_tile = [&](int pg, uint4 (&kq)[2][4], uint4 (&vv)[4][2]) -> bool {
+    const int pid = __shfl_sync(0xffffffffu, my_pid, (pg - p0 - warp) / kAW);
     if ((unsigned)pid >= (unsigned)p.pages) {  // malformed page table: record and skip
       if (lane == 0) atomicExch(p.status, 1);
-      continue;
+      return false;
     }
     const uint4* kt = reinterpret_cast<const uint4*>(p.pool + ((size_t)pid * p.Hkv + h) * (2 * 16 * kHD));
     const uint4* vt = kt + 16 * kHD / 8;
     // K rows of tokens g and g+8: the 16 bytes at d = 32i + 8t .. +7
-    uint4 kq[2][4];
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) kq[nt][i] = ldg_nc(kt + (nt * 8 + g) * 16 + i * 4 + t);
     // V rows of tokens 2t, 2t+1, 2t+8, 2t+9: d = 8g..8g+7 and 64+8g..64+8g+7
-    uint4 vv[4][2];
 #pragma unroll
     for (int x = 0; x < 4; ++x) {
       const int tk = 2 * t + (x & 1) + ((x >> 1) << 3);
 #pragma unroll
       for (int r = 0; r < 2; ++r) vv[x][r] = ldg_nc(vt + tk * 16 + r * 8 + g);
     }
-
+    return true;
+  };
+  auto compute_tile = [&](int pg, uint4 (&kq)[2][4], uint4 (&vv)[4][2]) {
     // S = Q K^T for 16 tokens: two n-tiles of 8 tokens
     float sacc[2][4];
 #pragma unroll
@@ -172,6 +182,22 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnParams 
       const uint32_t b1 = __byte_perm(vc[jj >> 1], vd[jj >> 1], sel);
       mma16816(o[j], ph0, 0u, ph1, 0u, b0, b1);
       mma16816(o[j], pl0, 0u, pl1, 0u, b0, b1);
+    }
+  };
+  {
+    uint4 kqA[2][4], vvA[4][2], kqB[2][4], vvB[4][2];
+    int pg = p0 + warp;
+    bool okA = false, okB = false;
+    if (pg < p1) okA = load_tile(pg, kqA, vvA);
+    while (pg < p1) {
+      const int pgn = pg + kAW;
+      if (pgn < p1) okB = load_tile(pgn, kqB, vvB);
+      if (okA) compute_tile(pg, kqA, vvA);
+      if (pgn >= p1) break;
+      const int pgnn = pgn + kAW;
+      if (pgnn < p1) okA = load_tile(pgnn, kqA, vvA);
+      if (okB) compute_tile(pgn, kqB, vvB);
+      pg = pgnn;
     }
   }
 
@@ -310,7 +336,8 @@ constexpr int kMaxAttnCounters = 1 << 16;  // (sequence, kv head) pairs per call
 
 // Splits: enough CTAs to fill the machine several times over, at least one page per warp.
 static int pages_per_split(const qeng_ctx* ctx, int64_t B, int64_t Hkv, int64_t max_pages) {
-  int64_t target = (int64_t)ctx->sm_count * 8;
+  static const int mult = getenv("QENG_ATTN_CTAS_PER_SM") ? atoi(getenv("QENG_ATTN_CTAS_PER_SM")) : 8;
+  int64_t target = (int64_t)ctx->sm_count * mult;
   int64_t pps = (B * Hkv * max_pages + target - 1) / target;
   pps = (pps + kAW - 1) / kAW * kAW;
   if (pps < kAW) pps = kAW;

@@ -168,13 +168,26 @@ int32_t ensure_rows(qeng_ctx* ctx, qeng_decoder* d, int64_t rows) {
   return qeng_attn_reserve(ctx, rows, d->Hq, d->Hkv, d->max_pages);
 }
 
-// matmul over `rows` activation rows in chunks the decode kernel accepts
+// matmul over `rows` activation rows in chunks the decode kernels accept: the largest row count
+// whose staged activations still fit the streaming kernel's shared memory (the weights are
+// streamed once per chunk), else 16 rows on the register-streaming kernel
 int32_t mm(qeng_ctx* ctx, qeng_decoder* d, const qeng_weight* w, const float* x, int64_t ldx, int64_t rows, float* y,
            int64_t ldy, const qeng_gemm_fuse& fuse, cudaStream_t st) {
-  for (int64_t m0 = 0; m0 < rows; m0 += 16) {
-    const int64_t mm_ = rows - m0 < 16 ? rows - m0 : 16;
+  int64_t chunk = 16;
+  for (int64_t c = 16; c >= 1; c >>= 1)
+    if (qeng_gemm_q4_stream_fits(w, c, true)) { chunk = c; break; }
+  for (int64_t m0 = 0; m0 < rows; m0 += chunk) {
+    const int64_t mm_ = rows - m0 < chunk ? rows - m0 : chunk;
     qeng_gemm_fuse f = fuse;
     if (f.resid) f.resid = fuse.resid + m0 * ldy;
+    qeng_qkv_epi E;
+    if (f.qkv) {  // the fused q|k|v epilogue addresses its outputs by activation row
+      E = *fuse.qkv;
+      E.pos += m0;
+      E.table += m0 * E.max_pages;
+      E.q16 += m0 * E.Hq * kHD;
+      f.qkv = &E;
+    }
     int32_t rc = qeng_gemm_q4_decode(ctx, w, x + m0 * ldx, QENG_F32, mm_, ldx, y + m0 * ldy, ldy, true, f, st);
     if (rc != QENG_OK) return rc;
     d->launches++;
@@ -266,7 +279,7 @@ int32_t run_layer(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, const int
   qeng_gemm_fuse f;
   f.norm_gamma = L.norm1; f.norm_eps = d->cfg.rms_eps; f.epilogue = QENG_EPI_STORE;
   int32_t rc;
-  if (rows <= 16 && qeng_gemm_q4_stream_fits(L.wqkv, rows, true)) {
+  if (qeng_gemm_q4_stream_fits(L.wqkv, 1, true)) {
     // q|k|v projection with rotary embedding, f16 rounding and KV append in its epilogue
     qeng_qkv_epi E;
     E.pos = d->pos; E.table = table; E.cs = d->rope_cs; E.q16 = d->q16; E.pool = pool;
