@@ -29,9 +29,10 @@ if ROOT not in sys.path:
 MODEL = dict(layers=32, d=4096, ffn=11008, heads=32, kv_heads=8, hd=128, vocab=32000)
 PROMPT = 512
 METRIC = "decode tokens/s (7B 4-bit, 1/2/4/8 B200); quant GEMV HBM GB/s vs peak"
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of gemv_q4_kernel, from the ncu
-# capture summarised in profiles/ (None until a capture exists for the current kernel).
-NCU_TRAFFIC_PER_ALGO_BYTE = None
+# (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of one launch of the decode
+# matmul, from the ncu capture summarised in profiles/gemv_q4_stream_22016x4096_m1.md
+# (50.80 MB read + 9.5 KB written against 50.83 MB algorithmic); traffic grows with N*K.
+NCU_TRAFFIC_PER_ALGO_BYTE = 0.9996
 
 
 def parse():
@@ -223,7 +224,11 @@ def main():
             obj = [b]
             dist.broadcast_object_list(obj, src=0)
             return obj[0]
-        ctx.tp_init(rank, world, exchange)
+        def allgather(b):
+            out = [None] * world
+            dist.all_gather_object(out, b)
+            return out
+        ctx.tp_init(rank, world, exchange, allgather)
     max_seq = PROMPT + Wm + 2 * K + 64
     dec = ctx.decoder(layers=m["layers"], d_model=m["d"], ffn=m["ffn"], heads=m["heads"], kv_heads=m["kv_heads"],
                       vocab=m["vocab"], max_batch=B, max_seq=max_seq, tp_rank=rank, tp_world=world)
@@ -315,7 +320,7 @@ def main():
         achieved = algo / len(ws) / per_launch_s / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": (NCU_TRAFFIC_PER_ALGO_BYTE * algo / len(ws)) if NCU_TRAFFIC_PER_ALGO_BYTE else None,
-                "kernel": "gemv_q4_kernel (M=1, f32 activations)", "bytes_per_launch": algo / len(ws),
+                "kernel": "gemv_q4_stream_kernel (M=1, f32 activations)", "bytes_per_launch": algo / len(ws),
                 "us_per_launch": per_launch_s * 1e6,
                 "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback",
                 "step_frac": algo_bytes_per_step(m, B, ctx_mid, world) / (ms * 1e-3 / K) / 1e9 / peak}

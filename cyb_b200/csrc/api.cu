@@ -78,7 +78,7 @@ int32_t qeng_device_status(qeng_ctx* ctx) {
   QENG_CUDA(ctx, cudaMemset(ctx->tail_cnt, 0, 64));
   return qeng_fail(ctx, QENG_ERR_DEVICE_STATUS,
                    "a kernel reported status %d (1 = page id outside the pool, 2 = position outside the cache, "
-                   "3 = token id outside the vocabulary, 4 = a bounded wait on a bulk copy ran out)", status);
+                   "3 = token id outside the vocabulary, 4 = a bounded wait on a copy or MMA ran out, 5 = a peer never delivered its part of an all-reduce)", status);
 }
 
 int32_t qeng_sm_count(const qeng_ctx* ctx) { return ctx ? ctx->sm_count : 0; }

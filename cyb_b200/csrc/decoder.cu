@@ -9,6 +9,7 @@
 // residual add and SwiGLU into the matmul epilogues, RoPE + f16 rounding + KV
 // append + q conversion into one small kernel.
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <vector>
@@ -213,9 +214,13 @@ int32_t row_split(qeng_ctx* ctx, qeng_decoder* d, const qeng_weight* w, const fl
   f.epilogue = QENG_EPI_STORE;
   int32_t rc = mm(ctx, d, w, in, ldin, rows, d->part, dm, f, st);
   if (rc != QENG_OK) return rc;
-  rc = qeng_tp_all_reduce_internal(ctx, d->part, rows * dm, st);
-  if (rc != QENG_OK) return rc;
   const int64_t n = rows * dm;
+  if (qeng_tp_p2p_ready(ctx, n)) {  // push, wait, sum and residual add in one kernel
+    d->launches += 1;
+    return qeng_tp_allreduce_add(ctx, d->x, d->part, n, st);
+  }
+  rc = qeng_tp_all_reduce_internal(ctx, d->part, n, st);
+  if (rc != QENG_OK) return rc;
   add_inplace_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(d->x, d->part, n);
   QENG_LAUNCH_CHECK(ctx);
   d->launches += 2;

@@ -50,6 +50,11 @@ struct qeng_ctx {
   // tensor parallelism (tp.cu)
   void* nccl_comm = nullptr;
   int tp_rank = 0, tp_world = 1;
+  // peer-mapped inboxes of the one-shot all-reduce
+  void* p2p_local = nullptr;
+  void* p2p_peer[8] = {};
+  size_t p2p_flag_off = 0, p2p_counter_off = 0;
+  bool p2p_ready = false;
   bool pdl = true;            // launch the streaming matmul with programmatic stream serialization
   // per-CTA argmax partials and the arrival counter of the fused LM head
   float* tail_val = nullptr;
@@ -136,6 +141,8 @@ int32_t qeng_lm_head_fused(qeng_ctx* ctx, const qeng_lm_tail& t, cudaStream_t st
 // tp.cu
 int32_t qeng_tp_all_reduce_internal(qeng_ctx* ctx, float* buf, int64_t n, cudaStream_t stream);
 void qeng_tp_release(qeng_ctx* ctx);
+bool qeng_tp_p2p_ready(const qeng_ctx* ctx, int64_t n);
+int32_t qeng_tp_allreduce_add(qeng_ctx* ctx, float* dst, const float* part, int64_t n, cudaStream_t stream);
 
 // gemm_q4_tc.cu: tcgen05 prefill matmul (bf16 operands, f32 accumulation in tensor memory)
 int32_t qeng_gemm_q4_prefill(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t x_dtype, int64_t M, int64_t ldx,

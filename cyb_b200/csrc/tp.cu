@@ -3,6 +3,7 @@
 // opened at run time (dlopen) so that single-GPU users do not need it.
 #include <dlfcn.h>
 #include <nccl.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "qeng_internal.h"
@@ -36,6 +37,101 @@ NcclApi& api() {
 
 }  // namespace
 
+// ---- one-shot all-reduce over peer memory ---------------------------------------------------
+// For the small messages of decode (16 KB .. 256 KB) the cost of a collective is latency, not
+// bandwidth.  Every rank owns an inbox [2 slots][world][kP2pMaxElems] of (value, tag) pairs in its
+// own memory, mapped into every peer with CUDA IPC.  A call pushes the local partial sums, each
+// paired with the call's sequence number in one 8-byte store, into the inbox of every rank (plain
+// stores over NVLink, no multicast, no fences), then reads the `world` slices of its OWN inbox,
+// waiting (bounded) until each pair carries this call's tag, and adds them in rank order, so all
+// ranks get bit-identical sums.  Slots alternate per call (a rank can be at most one call ahead
+// of a peer); a device-side call counter supplies the tag, so a captured graph can be replayed.
+// The sum is added into `dst` (the residual stream): collective and residual add are one kernel.
+constexpr int kP2pMaxElems = 16 * 4096;   // f32 elements per call (16 rows of d_model 4096)
+constexpr int kP2pThreads = 256;
+constexpr int kP2pSlice = kP2pThreads * 4;  // elements per CTA
+
+struct P2pParams {
+  uint2* inbox[8];     // inbox base of every rank (peer-mapped), [2][world][kP2pMaxElems]
+  unsigned* counter;   // local: [0] completed calls, [1] CTAs done in the running call
+  const float* src;    // local partial sums [n]
+  float* dst;          // dst[i] += sum over ranks
+  int n, rank, world;
+  int32_t* status;
+};
+
+__global__ void __launch_bounds__(kP2pThreads) p2p_allreduce_add_kernel(const P2pParams p) {
+  const int tid = threadIdx.x, cta = blockIdx.x;
+  const unsigned seq = *p.counter + 1;  // read by every CTA before the last one to finish bumps it
+  const int slot = seq & 1;
+  const int i0 = cta * kP2pSlice + tid * 4;
+  const bool active = i0 < p.n;  // n is a multiple of 4
+  if (active) {
+    const float4 v = *reinterpret_cast<const float4*>(p.src + i0);
+    const uint32_t w[4] = {__float_as_uint(v.x), __float_as_uint(v.y), __float_as_uint(v.z), __float_as_uint(v.w)};
+    for (int r = 0; r < p.world; ++r) {
+      const int peer = (p.rank + r) % p.world;  // spread the first stores over the links
+      uint2* in = p.inbox[peer] + ((size_t)slot * p.world + p.rank) * kP2pMaxElems + i0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};\n" ::"l"(in + e), "r"(w[e]), "r"(seq) : "memory");
+    }
+    float4 acc = *reinterpret_cast<const float4*>(p.dst + i0);
+    float* a = reinterpret_cast<float*>(&acc);
+    bool failed = false;
+    for (int r = 0; r < p.world && !failed; ++r) {
+      const uint2* in = p.inbox[p.rank] + ((size_t)slot * p.world + r) * kP2pMaxElems + i0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        uint32_t val, tag;
+        unsigned long long t0 = 0;
+        for (int spin = 0;; ++spin) {
+          asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];\n" : "=r"(val), "=r"(tag) : "l"(in + e) : "memory");
+          if (tag == seq) break;
+          if ((spin & 1023) == 1023) {  // bounded: two seconds, then report and leave
+            unsigned long long t1;
+            asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t1));
+            if (t0 == 0) t0 = t1;
+            if (t1 - t0 > 2000000000ull) {
+              failed = true;
+              atomicExch(p.status, 5);
+              break;
+            }
+          }
+        }
+        a[e] += __uint_as_float(val);
+      }
+    }
+    if (!failed) *reinterpret_cast<float4*>(p.dst + i0) = acc;
+  }
+  // the last CTA to finish advances the call counter (all CTAs have read it by then)
+  __shared__ unsigned s_done;
+  __syncthreads();
+  if (tid == 0) s_done = atomicAdd(p.counter + 1, 1u);
+  __syncthreads();
+  if (s_done == gridDim.x - 1 && tid == 0) {
+    p.counter[1] = 0;
+    __threadfence();
+    p.counter[0] = seq;
+  }
+}
+
+// x += all-reduce(part) with the one-shot kernel when the peers are mapped and the message is small
+bool qeng_tp_p2p_ready(const qeng_ctx* ctx, int64_t n) {
+  return ctx->p2p_ready && n <= kP2pMaxElems && (n & 3) == 0;
+}
+
+int32_t qeng_tp_allreduce_add(qeng_ctx* ctx, float* dst, const float* part, int64_t n, cudaStream_t stream) {
+  P2pParams p;
+  for (int r = 0; r < 8; ++r) p.inbox[r] = r < ctx->tp_world ? reinterpret_cast<uint2*>(ctx->p2p_peer[r]) : nullptr;
+  p.counter = reinterpret_cast<unsigned*>(reinterpret_cast<char*>(ctx->p2p_local) + ctx->p2p_counter_off);
+  p.src = part; p.dst = dst; p.n = (int)n; p.rank = ctx->tp_rank; p.world = ctx->tp_world; p.status = ctx->status;
+  const int grid = (int)((n + kP2pSlice - 1) / kP2pSlice);
+  p2p_allreduce_add_kernel<<<grid, kP2pThreads, 0, stream>>>(p);
+  QENG_LAUNCH_CHECK(ctx);
+  return QENG_OK;
+}
+
 int32_t qeng_tp_all_reduce_internal(qeng_ctx* ctx, float* buf, int64_t n, cudaStream_t stream) {
   if (ctx->tp_world <= 1) return QENG_OK;
   NcclApi& a = api();
@@ -45,6 +141,13 @@ int32_t qeng_tp_all_reduce_internal(qeng_ctx* ctx, float* buf, int64_t n, cudaSt
 }
 
 void qeng_tp_release(qeng_ctx* ctx) {
+  if (ctx->p2p_local) {
+    for (int r = 0; r < ctx->tp_world; ++r)
+      if (r != ctx->tp_rank && ctx->p2p_peer[r]) cudaIpcCloseMemHandle(ctx->p2p_peer[r]);
+    cudaFree(ctx->p2p_local);
+    ctx->p2p_local = nullptr;
+    ctx->p2p_ready = false;
+  }
   if (ctx->nccl_comm) {
     api().CommDestroy((ncclComm_t)ctx->nccl_comm);
     ctx->nccl_comm = nullptr;
@@ -78,6 +181,60 @@ int32_t qeng_tp_init(qeng_ctx* ctx, int32_t rank, int32_t world, const uint8_t* 
   ctx->nccl_comm = comm;
   ctx->tp_rank = rank;
   ctx->tp_world = world;
+  return QENG_OK;
+}
+
+int32_t qeng_tp_p2p_handle(qeng_ctx* ctx, uint8_t* out64) {
+  if (!ctx || !out64) return qeng_fail(ctx, QENG_ERR_ARG, "tp_p2p_handle: null argument");
+  if (ctx->tp_world < 2 || ctx->tp_world > 8) return qeng_fail(ctx, QENG_ERR_STATE, "tp_p2p_handle: needs 2..8 ranks (tp_init first)");
+  QENG_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (!ctx->p2p_local) {
+    const size_t inbox = (size_t)2 * ctx->tp_world * kP2pMaxElems * sizeof(uint2);
+    ctx->p2p_flag_off = inbox;
+    ctx->p2p_counter_off = inbox;
+    QENG_CUDA(ctx, cudaMalloc(&ctx->p2p_local, inbox + 256));
+    QENG_CUDA(ctx, cudaMemset(ctx->p2p_local, 0, inbox + 256));
+  }
+  cudaIpcMemHandle_t h;
+  QENG_CUDA(ctx, cudaIpcGetMemHandle(&h, ctx->p2p_local));
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(out64, &h, 64);
+  return QENG_OK;
+}
+
+int32_t qeng_tp_p2p_open(qeng_ctx* ctx, const uint8_t* handles) {
+  if (!ctx || !handles) return qeng_fail(ctx, QENG_ERR_ARG, "tp_p2p_open: null argument");
+  if (!ctx->p2p_local) return qeng_fail(ctx, QENG_ERR_STATE, "tp_p2p_open: call tp_p2p_handle first");
+  QENG_CUDA(ctx, cudaSetDevice(ctx->device));
+  for (int r = 0; r < ctx->tp_world; ++r) {
+    if (r == ctx->tp_rank) {
+      ctx->p2p_peer[r] = ctx->p2p_local;
+      continue;
+    }
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handles + (size_t)r * 64, 64);
+    void* ptr = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return qeng_fail(ctx, QENG_ERR_CUDA, "tp_p2p_open: rank %d: %s", r, cudaGetErrorString(e));
+    ctx->p2p_peer[r] = ptr;
+  }
+  ctx->p2p_ready = getenv("QENG_NO_P2P") == nullptr;
+  return QENG_OK;
+}
+
+__global__ void tp_add_kernel(float* __restrict__ x, const float* __restrict__ p, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] += p[i];
+}
+
+int32_t qeng_tp_all_reduce_add_f32(qeng_ctx* ctx, float* dst, float* part, int64_t n, void* stream) {
+  if (!ctx || !dst || !part || n <= 0) return qeng_fail(ctx, QENG_ERR_ARG, "tp_all_reduce_add_f32: bad argument");
+  if (ctx->tp_world > 1 && !ctx->nccl_comm) return qeng_fail(ctx, QENG_ERR_STATE, "tp_all_reduce_add_f32: tp_init first");
+  if (ctx->tp_world > 1 && qeng_tp_p2p_ready(ctx, n)) return qeng_tp_allreduce_add(ctx, dst, part, n, (cudaStream_t)stream);
+  int32_t rc = qeng_tp_all_reduce_internal(ctx, part, n, (cudaStream_t)stream);
+  if (rc != QENG_OK) return rc;
+  tp_add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(dst, part, n);
+  QENG_LAUNCH_CHECK(ctx);
   return QENG_OK;
 }
 

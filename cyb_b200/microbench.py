@@ -4,6 +4,7 @@
     python -m cyb_b200.microbench attn [--batch 16] [--lo 512] [--hi 4096]
     python -m cyb_b200.microbench lmhead [--m 1]
     python -m cyb_b200.microbench prefill [--m 2048] [--n 11008] [--k 4096]
+    python -m torch.distributed.run --nproc-per-node 2 -m cyb_b200.microbench allreduce [--elems 4096]
 
 `gemv` rotates through a pool of distinct packed weights larger than the 126 MB
 L2, so every launch streams its weights from HBM; the figure printed is
@@ -150,6 +151,57 @@ def prefill(args):
                       "tflops": 2.0 * m * n * k / ms / 1e9}))
 
 
+def allreduce(args):
+    """Run under torch.distributed.run, one rank per GPU: latency of dst += allreduce(part)."""
+    import os
+    import torch
+    import torch.distributed as dist
+    from cyb_b200 import qeng
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo")
+    ctx = qeng.Context(rank)
+
+    def bc(b):
+        o = [b]
+        dist.broadcast_object_list(o, src=0)
+        return o[0]
+
+    def ag(b):
+        o = [None] * world
+        dist.all_gather_object(o, b)
+        return o
+    ctx.tp_init(rank, world, bc, ag)
+    part = torch.ones(args.elems, device="cuda")
+    dst = torch.zeros(args.elems, device="cuda")
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for _ in range(4):
+            ctx.all_reduce_add_(dst, part)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        for _ in range(50):
+            ctx.all_reduce_add_(dst, part)
+    g.replay()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = _events(torch)
+    e0.record()
+    for _ in range(args.iters):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (args.iters * 50)
+    ctx.device_status()
+    expect = world * (4 + 50 * (args.iters + 1))
+    if rank == 0:
+        print(json.dumps({"kernel": "all_reduce_add", "world": world, "n": args.elems, "us_per_call": us,
+                          "correct": bool(float(dst[0]) == expect and float(dst[-1]) == expect)}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="cyb_b200.microbench")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -175,8 +227,11 @@ def main(argv=None):
     pf.add_argument("--n", type=int, default=11008)
     pf.add_argument("--k", type=int, default=4096)
     pf.add_argument("--iters", type=int, default=10)
+    ar = sub.add_parser("allreduce")
+    ar.add_argument("--elems", type=int, default=4096)
+    ar.add_argument("--iters", type=int, default=20)
     args = ap.parse_args(argv)
-    {"gemv": gemv, "attn": attn, "lmhead": lmhead, "prefill": prefill}[args.cmd](args)
+    {"allreduce": allreduce, "gemv": gemv, "attn": attn, "lmhead": lmhead, "prefill": prefill}[args.cmd](args)
 
 
 if __name__ == "__main__":

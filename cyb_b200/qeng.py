@@ -70,6 +70,9 @@ _sig("qeng_device_status", _i32, _vp)
 _sig("qeng_sm_count", _i32, _vp)
 _sig("qeng_tp_unique_id", _i32, _vp)
 _sig("qeng_tp_init", _i32, _vp, _i32, _i32, _vp)
+_sig("qeng_tp_p2p_handle", _i32, _vp, _vp)
+_sig("qeng_tp_p2p_open", _i32, _vp, _vp)
+_sig("qeng_tp_all_reduce_add_f32", _i32, _vp, _vp, _vp, _i64, _vp)
 _sig("qeng_tp_all_reduce_f32", _i32, _vp, _vp, _i64, _vp)
 _sig("qeng_weight_pack_q4", _i32, _vp, _vp, _vp, _i64, _i64, C.POINTER(_vp))
 _sig("qeng_weight_unpack_q4", _i32, _vp, _vp, _vp, _vp)
@@ -153,9 +156,11 @@ class Context:
         return _lib.qeng_sm_count(self.h)
 
     # ---- tensor parallelism ---------------------------------------------------
-    def tp_init(self, rank, world, exchange):
+    def tp_init(self, rank, world, exchange, allgather=None):
         """Collective.  `exchange(bytes_or_None) -> bytes` must broadcast rank 0's 128-byte id
-        to every rank over any host channel (e.g. torch.distributed.broadcast_object_list)."""
+        to every rank over any host channel (e.g. torch.distributed.broadcast_object_list).
+        `allgather(bytes) -> [bytes per rank]`, if given, also maps the peers' inboxes for the
+        one-shot all-reduce of decode."""
         buf = (C.c_uint8 * 128)()
         if rank == 0:
             rc = _lib.qeng_tp_unique_id(buf)
@@ -164,6 +169,16 @@ class Context:
         ident = exchange(bytes(buf) if rank == 0 else None)
         arr = (C.c_uint8 * 128).from_buffer_copy(ident)
         self.check(_lib.qeng_tp_init(self.h, rank, world, arr))
+        if allgather is not None and 2 <= world <= 8:
+            hb = (C.c_uint8 * 64)()
+            self.check(_lib.qeng_tp_p2p_handle(self.h, hb))
+            parts = allgather(bytes(hb))
+            allb = (C.c_uint8 * (64 * world)).from_buffer_copy(b"".join(parts))
+            self.check(_lib.qeng_tp_p2p_open(self.h, allb))
+
+    def all_reduce_add_(self, dst, part):
+        self.check(_lib.qeng_tp_all_reduce_add_f32(self.h, _dev_ptr(dst), _dev_ptr(part), part.numel(), _cur_stream()))
+        return dst
 
     def all_reduce_(self, t):
         self.check(_lib.qeng_tp_all_reduce_f32(self.h, _dev_ptr(t), t.numel(), _cur_stream()))

@@ -77,6 +77,16 @@ int32_t qeng_sm_count(const qeng_ctx* ctx);
  * bytes to every rank (any channel), every rank calls qeng_tp_init (collective). */
 int32_t qeng_tp_unique_id(uint8_t* out128);
 int32_t qeng_tp_init(qeng_ctx* ctx, int32_t rank, int32_t world, const uint8_t* id128);
+/* Optional, after qeng_tp_init: map every rank's inbox into every peer (CUDA IPC) so that the
+ * small all-reduces of decode run as one low-latency push kernel over NVLink instead of NCCL.
+ * Each rank exports 64 bytes with qeng_tp_p2p_handle; the host program gathers the world*64
+ * bytes (rank order) and gives them to qeng_tp_p2p_open on every rank. */
+int32_t qeng_tp_p2p_handle(qeng_ctx* ctx, uint8_t* out64);
+int32_t qeng_tp_p2p_open(qeng_ctx* ctx, const uint8_t* handles);
+/* dst[n] += sum over ranks of part[n] (f32, device): the collective after a row-split projection
+ * fused with the residual add.  Uses the one-shot peer-memory kernel when the peers are mapped
+ * and n <= 65536 (n % 4 == 0), else NCCL followed by an add. */
+int32_t qeng_tp_all_reduce_add_f32(qeng_ctx* ctx, float* dst, float* part, int64_t n, void* stream);
 /* In-place sum of buf[n] (f32, device) over the ranks, on `stream` (NCCL over NVLink). */
 int32_t qeng_tp_all_reduce_f32(qeng_ctx* ctx, float* buf, int64_t n, void* stream);
 

@@ -35,7 +35,11 @@ def _rank_main(rank, world, port, out):
         obj = [b]
         dist.broadcast_object_list(obj, src=0)
         return obj[0]
-    ctx.tp_init(rank, world, exchange)
+    def allgather(b):
+        outl = [None] * world
+        dist.all_gather_object(outl, b)
+        return outl
+    ctx.tp_init(rank, world, exchange, allgather)
     t = torch.full((1000,), float(rank + 1), device="cuda")
     ctx.all_reduce_(t)
     torch.cuda.synchronize()
