@@ -92,3 +92,30 @@ def test_teacher_forced_layer_on_the_tensor_core_path(ctx):
     e = ref.err_inf(got, want[0])
     assert e < 5e-3, e
     dec.free()
+
+
+def test_full_size_layer_teacher_forced(ctx):
+    """One layer at BASELINE's full widths (d 4096, FFN 11008, 32/8 heads): 6 prompt rows then one
+    decode row, teacher-forced against the float64 oracle (gate 2e-3; the kernels reach ~1e-5)."""
+    import torch
+    from cyb_b200 import qeng
+    cfg = ref.DecoderConfig(layers=1, d=4096, ffn=11008, heads=32, kv_heads=8, vocab=256)
+    W = ref.make_decoder_weights(cfg, seed=77)
+    dec = ctx.decoder(layers=1, d_model=4096, ffn=11008, heads=32, kv_heads=8, vocab=256, max_batch=1, max_seq=32)
+    qeng.load_decoder_weights(dec, W, cfg)
+    teacher = ref.Decoder(cfg, W)
+    teacher.reset(1)
+    rng = ref.rng_of(78)
+    T = 6
+    x = rng.standard_normal((1, T, cfg.d), dtype=np.float32) * 2
+    want = teacher.layer(0, x.astype(np.float64), np.arange(T)[None])
+    got = dec.layer(0, torch.from_numpy(x[0]).cuda(), np.arange(T)).cpu().numpy()
+    e = ref.err_inf(got, want[0])
+    assert e < 2e-3 and e < 5e-5, e
+    x1 = rng.standard_normal((1, 1, cfg.d), dtype=np.float32) * 2
+    want1 = teacher.layer(0, x1.astype(np.float64), np.array([[T]]))
+    got1 = dec.layer(0, torch.from_numpy(x1[0]).cuda(), np.array([T])).cpu().numpy()
+    e1 = ref.err_inf(got1, want1[0])
+    assert e1 < 5e-5, e1
+    ctx.device_status()
+    dec.free()
