@@ -214,6 +214,9 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
+    # the weight import (re-tiling on the host) is OpenMP-parallel; torch.distributed.run pins
+    # OMP_NUM_THREADS to 1, so give every rank its share of the cores before the library loads
+    os.environ["OMP_NUM_THREADS"] = str(max(1, (os.cpu_count() or 1) // max(world, 1)))
     from cyb_b200 import qeng
     m = dict(MODEL)
     m["layers"] = args.layers

@@ -154,3 +154,19 @@ def test_prefill_tensor_core_path(ctx, m, n, k):
     yb = ctx.gemm_q4(w, _t(xb).to(torch.bfloat16), out=_t(y.copy()), flags=1).cpu().numpy()
     assert ref.err_inf(yb, 2 * same) < 2e-5
     w.free()
+
+
+@pytest.mark.parametrize("n,k", [(768, 4096), (4096, 512), (2752, 4096), (4096, 1376), (1536, 4096), (4096, 2752)])
+def test_tensor_parallel_shard_shapes(ctx, n, k):
+    """The per-rank matrices of the 2/4/8-way sharded decoder (K = 1376 has an odd number of
+    32-blocks, K = 512 fills a quarter of a copy stage): GEMV with the fused epilogues' plain form."""
+    rng = ref.rng_of(n + 3 * k)
+    x = rng.standard_normal((1, k), dtype=np.float32)
+    q, s = ref.make_q4(rng, n, k)
+    w = ctx.pack_q4(q, s)
+    y = ctx.gemm_q4(w, _t(x)).cpu().numpy()
+    assert ref.err_inf(y, ref.gemm_q4_fast(x, q, s)) < 2e-6
+    x4 = rng.standard_normal((4, k), dtype=np.float32)
+    y4 = ctx.gemm_q4(w, _t(x4)).cpu().numpy()
+    assert ref.err_inf(y4, ref.gemm_q4_fast(x4, q, s)) < 2e-6
+    w.free()
