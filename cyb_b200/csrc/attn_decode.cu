@@ -54,6 +54,8 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
 }
 
 __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnParams p) {
+  // the output projection that follows may start streaming its weights as CTAs of this kernel retire
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   const int s = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int len = p.lens[b];
   const int npages = min((len + 15) >> 4, p.max_pages);

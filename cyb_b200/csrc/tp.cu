@@ -61,6 +61,8 @@ struct P2pParams {
 };
 
 __global__ void __launch_bounds__(kP2pThreads) p2p_allreduce_add_kernel(const P2pParams p) {
+  // the matmul that follows may start streaming its weights while this kernel waits for the peers
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   const int tid = threadIdx.x, cta = blockIdx.x;
   const unsigned seq = *p.counter + 1;  // read by every CTA before the last one to finish bumps it
   const int slot = seq & 1;
