@@ -40,6 +40,7 @@ struct TcParams {
   float* y;
   long long ldy;
   int accumulate;
+  int accs;  // accumulators per CTA: the output tile is (128 * accs) x 128
   int32_t* status;
 };
 
@@ -113,9 +114,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_q4_tc_kernel(const TcParam
   uint64_t* acc_full = bars + 3 * kStages;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int m_tiles = (p.M + kBM - 1) / kBM;
+  const int bm = 128 * p.accs;
+  const int m_tiles = (p.M + bm - 1) / bm;
   const int mt = blockIdx.x % m_tiles, nt = blockIdx.x / m_tiles;  // M walks fastest: the weight tile stays in L2
-  const int m0 = mt * kBM, n0 = nt * kBN;
+  const int m0 = mt * bm, n0 = nt * kBN;
   const int nk = p.nchunks;
 
   if (tid == 0) {
@@ -154,7 +156,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_q4_tc_kernel(const TcParam
           const uint64_t bdesc = make_desc(b_addr + k * 32);
           const uint32_t acc = (kt > 0 || k > 0) ? 1u : 0u;
           umma_bf16(tmem_base, make_desc(a_addr + k * 32), bdesc, idesc, acc);
-          umma_bf16(tmem_base + kBN, make_desc(a_addr + 128 * 128 + k * 32), bdesc, idesc, acc);
+          if (p.accs > 1) umma_bf16(tmem_base + kBN, make_desc(a_addr + 128 * 128 + k * 32), bdesc, idesc, acc);
         }
         umma_commit(smem_u32(empty + s));  // the stage is free once these MMAs have read it
         if (++s == kStages) { s = 0; ph ^= 1u; }
@@ -175,6 +177,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_q4_tc_kernel(const TcParam
         const int k0 = kt * kBK;
 #pragma unroll
         for (int i = 0; i < (kBM * 8) / kLoaders; ++i) {
+          if (i * kLoaders >= bm * 8) break;  // a 128-row tile fills half of the stage
           const int c = lt + i * kLoaders;  // chunk id: row = c / 8, 16-byte chunk j = c % 8
           const int r = c >> 3, j = c & 7;
           const int gm = m0 + r, gk = k0 + j * 8;
@@ -202,20 +205,26 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_q4_tc_kernel(const TcParam
     int s = 0;
     uint32_t ph = 0;
     // a thread handles packed lanes dt and dt+128 of the 256 (8 row tiles x 32 lanes)
-    for (int kt = 0; kt < nk; ++kt) {
-      uint4 w[2];
-      uint2 sc2[2];
+    uint4 wn[2];
+    uint2 scn[2];
+    auto fetch = [&](int kt) {
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int pl = dt + h * 128, tl = pl >> 5, ln = pl & 31;
         const int tile = (n0 >> 4) + tl;
-        w[h] = make_uint4(0u, 0u, 0u, 0u);
-        sc2[h] = make_uint2(0u, 0u);
-        if (tile < p.ntiles) {
-          w[h] = __ldg(p.qs + ((size_t)tile * p.nchunks + kt) * 32 + ln);
-          sc2[h] = __ldg(p.sc + ((size_t)tile * p.nchunks + kt) * 8 + (ln >> 2));
+        wn[h] = make_uint4(0u, 0u, 0u, 0u);
+        scn[h] = make_uint2(0u, 0u);
+        if (tile < p.ntiles && kt < nk) {
+          wn[h] = __ldg(p.qs + ((size_t)tile * p.nchunks + kt) * 32 + ln);
+          scn[h] = __ldg(p.sc + ((size_t)tile * p.nchunks + kt) * 8 + (ln >> 2));
         }
       }
+    };
+    fetch(0);
+    for (int kt = 0; kt < nk; ++kt) {
+      uint4 w[2] = {wn[0], wn[1]};
+      uint2 sc2[2] = {scn[0], scn[1]};
+      fetch(kt + 1);  // the next stage's packed words travel while this one is converted
       if (!failed && !mbar_wait(smem_u32(empty + s), ph ^ 1u)) failed = true;
       const uint32_t b_addr = smem_u32(smem + (size_t)s * kStage) + kATile;
 #pragma unroll
@@ -258,7 +267,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_q4_tc_kernel(const TcParam
     const int quad = warp & 3;  // a warp may touch lanes 32*(warp%4) .. +31
     if (ok) {
 #pragma unroll 1
-      for (int acc = 0; acc < 2; ++acc) {
+      for (int acc = 0; acc < p.accs; ++acc) {
         const int gm = m0 + acc * 128 + quad * 32 + lane;
 #pragma unroll 1
         for (int c0 = 0; c0 < kBN; c0 += 32) {
@@ -343,7 +352,10 @@ int32_t qeng_gemm_q4_prefill(qeng_ctx* ctx, const qeng_weight* w, const void* x,
   p.qs = w->qs; p.sc = w->sc; p.nchunks = (int)w->nchunks; p.ntiles = (int)w->ntiles;
   p.x = xb; p.ldx = ldb; p.M = (int)M; p.N = (int)w->N; p.K = (int)w->K;
   p.y = y; p.ldy = ldy; p.accumulate = accumulate; p.status = ctx->status;
-  const int m_tiles = (int)((M + kBM - 1) / kBM), n_tiles = (int)((w->N + kBN - 1) / kBN);
+  const int n_tiles = (int)((w->N + kBN - 1) / kBN);
+  // 256-row tiles amortise the dequantisation; 128-row tiles when those would leave SMs idle
+  p.accs = ((M + kBM - 1) / kBM) * n_tiles >= ctx->sm_count ? 2 : 1;
+  const int m_tiles = (int)((M + 128 * p.accs - 1) / (128 * p.accs));
   gemm_q4_tc_kernel<<<m_tiles * n_tiles, kTcThreads, smem, stream>>>(p);
   QENG_LAUNCH_CHECK(ctx);
   return QENG_OK;
