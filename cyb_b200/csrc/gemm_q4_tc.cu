@@ -1,13 +1,13 @@
 // Prefill-side quantized matmul on the 5th-generation tensor cores:
 //   y[M,N] (f32) = x[M,K] (bf16) . bf16(dequant(W))[N,K]^T, f32 accumulation in TMEM.
 //
-// One CTA computes a 256 x 128 output tile.  Per 64-wide K stage:
+// One CTA computes a 256 x 128 or 256 x 256 output tile (128 rows when M is small).  Per 64-wide K stage:
 //   * loader warps copy the 256 x 64 bf16 activation tile into shared memory with 16-byte
 //     cp.async, placing every chunk where the 128-byte swizzled K-major layout wants it;
 //   * dequant warps read the packed 4-bit tile (8 row tiles x one chunk: 4.6 KB), turn each
 //     code into bf16((c-8)*s) and store the 128 x 64 tile in the same swizzled layout;
-//   * one thread issues tcgen05.mma (M=128, N=128, K=16; two accumulators share the weight
-//     tile, so the dequantisation is amortised over 256 rows); tcgen05.commit hands the stage
+//   * one thread issues tcgen05.mma (M=128, N=128 or 256, K=16; two accumulators share the
+//     weight tile, so the dequantisation is amortised over 256 rows); tcgen05.commit hands the stage
 //     back to the producers.
 // The epilogue reads the accumulators with tcgen05.ld and stores f32 rows.
 // Tensor-bound: 2*M*N*K flop; packed weights are re-read M/256 times from L2, activations
@@ -21,14 +21,19 @@
 
 namespace {
 
-constexpr int kBM = 256, kBN = 128, kBK = 64;
-constexpr int kStages = 4;
+constexpr int kBM = 256, kBK = 64;
 constexpr int kATile = kBM * kBK * 2;  // 32 KB
-constexpr int kBTile = kBN * kBK * 2;  // 16 KB
-constexpr int kStage = kATile + kBTile;
-constexpr int kLoaders = 128, kDequant = 128;
-constexpr int kTcThreads = 32 + kLoaders + kDequant;  // warp 0 issues MMAs
-constexpr int kTmemCols = 256;                        // two 128 x 128 f32 accumulators
+constexpr int kLoaders = 128;
+// Two tile widths: BN = 128 (4 stages of 48 KB, 256 TMEM columns) and BN = 256 (3 stages of 64 KB,
+// all 512 TMEM columns), which halves the L2 reads of the activation tile per flop.
+template <int BN> struct TcCfg {
+  static constexpr int kBTile = BN * kBK * 2;
+  static constexpr int kStage = kATile + kBTile;
+  static constexpr int kStages = BN == 128 ? 4 : 3;
+  static constexpr int kDequant = BN;                        // one thread per two packed lanes
+  static constexpr int kThreads = 32 + kLoaders + kDequant;  // warp 0 issues MMAs
+  static constexpr int kTmemCols = 2 * BN;                   // two 128 x BN f32 accumulators
+};
 
 struct TcParams {
   const uint4* qs;
@@ -102,11 +107,14 @@ __device__ __forceinline__ uint32_t bf16x2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-__global__ void __launch_bounds__(kTcThreads, 1) gemm_q4_tc_kernel(const TcParams p) {
+template <int kBN>
+__global__ void __launch_bounds__(TcCfg<kBN>::kThreads, 1) gemm_q4_tc_kernel(const TcParams p) {
+  constexpr int kStages = TcCfg<kBN>::kStages, kStage = TcCfg<kBN>::kStage, kDequant = TcCfg<kBN>::kDequant;
+  constexpr int kTmemCols = TcCfg<kBN>::kTmemCols;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // the swizzle pattern is a function of the address: the tiles must start on 1024-byte boundaries
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  __shared__ __align__(8) uint64_t bars[3 * kStages + 1];
+  __shared__ __align__(8) uint64_t bars[3 * 4 + 1];
   __shared__ uint32_t tmem_slot;
   uint64_t* full_a = bars;
   uint64_t* full_b = bars + kStages;
@@ -200,17 +208,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_q4_tc_kernel(const TcParam
     if (failed && lt == 0) atomicExch(p.status, 4);
   } else {
     // ===== dequant: 128 rows x 64 k per stage; thread = (row tile, lane of the packed layout) ====
-    const int dt = tid - 32 - kLoaders;  // 0..127
+    const int dt = tid - 32 - kLoaders;  // 0..kDequant-1
     bool failed = false;
     int s = 0;
     uint32_t ph = 0;
-    // a thread handles packed lanes dt and dt+128 of the 256 (8 row tiles x 32 lanes)
+    // a thread handles packed lanes dt and dt+kDequant of the 2*kBN (kBN/16 row tiles x 32 lanes)
     uint4 wn[2];
     uint2 scn[2];
     auto fetch = [&](int kt) {
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const int pl = dt + h * 128, tl = pl >> 5, ln = pl & 31;
+        const int pl = dt + h * kDequant, tl = pl >> 5, ln = pl & 31;
         const int tile = (n0 >> 4) + tl;
         wn[h] = make_uint4(0u, 0u, 0u, 0u);
         scn[h] = make_uint2(0u, 0u);
@@ -229,7 +237,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_q4_tc_kernel(const TcParam
       const uint32_t b_addr = smem_u32(smem + (size_t)s * kStage) + kATile;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const int pl = dt + h * 128, tl = pl >> 5, ln = pl & 31, g = ln >> 2, t = ln & 3;
+        const int pl = dt + h * kDequant, tl = pl >> 5, ln = pl & 31, g = ln >> 2, t = ln & 3;
         const uint32_t words[4] = {w[h].x, w[h].y, w[h].z, w[h].w};
         const __half2 s01 = *reinterpret_cast<const __half2*>(&sc2[h].x);  // (row g, blk 0), (row g+8, blk 0)
         const __half2 s23 = *reinterpret_cast<const __half2*>(&sc2[h].y);  // (row g, blk 1), (row g+8, blk 1)
@@ -342,21 +350,30 @@ int32_t qeng_gemm_q4_prefill(qeng_ctx* ctx, const qeng_weight* w, const void* x,
   }
   if ((reinterpret_cast<uintptr_t>(xb) & 15) != 0 || (ldb & 7) != 0)
     return qeng_fail(ctx, QENG_ERR_ALIGN, "gemm_q4 (prefill): activations must be 16-byte aligned with a leading dimension multiple of 8");
-  static bool configured = false;
-  const size_t smem = (size_t)kStages * kStage + 1024;
-  if (!configured) {
-    QENG_CUDA(ctx, cudaFuncSetAttribute(gemm_q4_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
-  }
   TcParams p;
   p.qs = w->qs; p.sc = w->sc; p.nchunks = (int)w->nchunks; p.ntiles = (int)w->ntiles;
   p.x = xb; p.ldx = ldb; p.M = (int)M; p.N = (int)w->N; p.K = (int)w->K;
   p.y = y; p.ldy = ldy; p.accumulate = accumulate; p.status = ctx->status;
-  const int n_tiles = (int)((w->N + kBN - 1) / kBN);
-  // 256-row tiles amortise the dequantisation; 128-row tiles when those would leave SMs idle
-  p.accs = ((M + kBM - 1) / kBM) * n_tiles >= ctx->sm_count ? 2 : 1;
+  // 256-wide tiles when they still give every SM at least two tiles, else 128-wide; 256-row tiles
+  // amortise the dequantisation, 128-row tiles when those would leave SMs idle
+  const int64_t mt256 = (M + kBM - 1) / kBM;
+  const bool wide = mt256 * ((w->N + 255) / 256) >= 2 * (int64_t)ctx->sm_count;
+  const int bn = wide ? 256 : 128;
+  const int n_tiles = (int)((w->N + bn - 1) / bn);
+  p.accs = mt256 * n_tiles >= ctx->sm_count ? 2 : 1;
   const int m_tiles = (int)((M + 128 * p.accs - 1) / (128 * p.accs));
-  gemm_q4_tc_kernel<<<m_tiles * n_tiles, kTcThreads, smem, stream>>>(p);
+  static bool configured = false;
+  if (!configured) {
+    QENG_CUDA(ctx, cudaFuncSetAttribute(gemm_q4_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        TcCfg<128>::kStages * TcCfg<128>::kStage + 1024));
+    QENG_CUDA(ctx, cudaFuncSetAttribute(gemm_q4_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        TcCfg<256>::kStages * TcCfg<256>::kStage + 1024));
+    configured = true;
+  }
+  if (wide)
+    gemm_q4_tc_kernel<256><<<m_tiles * n_tiles, TcCfg<256>::kThreads, TcCfg<256>::kStages * TcCfg<256>::kStage + 1024, stream>>>(p);
+  else
+    gemm_q4_tc_kernel<128><<<m_tiles * n_tiles, TcCfg<128>::kThreads, TcCfg<128>::kStages * TcCfg<128>::kStage + 1024, stream>>>(p);
   QENG_LAUNCH_CHECK(ctx);
   return QENG_OK;
 }
