@@ -152,9 +152,13 @@ def cpu_decode_rate(m, batch, ctx_len, budget_s, steps=None):
     toks = rng.integers(0, m["vocab"], batch).astype(np.int32)
     # time layers and head separately: t_layers from the 2-layer model minus head, head from a direct call
     x = rng.standard_normal((batch, m["d"]), dtype=np.float32)
-    t0 = time.perf_counter()
-    cport.gemm_bf16(x, dec.lm)
-    t_head = time.perf_counter() - t0
+    cport.gemm_bf16(x, dec.lm)  # warm (first touch of the table)
+    th = []
+    for _ in range(3):
+        t0 = time.perf_counter()
+        cport.gemm_bf16(x, dec.lm)
+        th.append(time.perf_counter() - t0)
+    t_head = statistics.median(th)
     dec.step(toks, np.full(batch, ctx_len, np.int32), table)  # warm
     times = []
     t_start = time.perf_counter()
@@ -164,13 +168,13 @@ def cpu_decode_rate(m, batch, ctx_len, budget_s, steps=None):
         dec.step(toks, np.full(batch, ctx_len + 1 + n % 32, np.int32), table)
         times.append(time.perf_counter() - t0)
         n += 1
-        per_full = (statistics.median(times) - t_head) / sample_layers * m["layers"] + t_head
         if steps is not None:
             if n >= steps:
                 break
         elif time.perf_counter() - t_start > budget_s or n >= 64:
             break
     t_step = statistics.median(times)
+    t_head = min(t_head, 0.9 * t_step)  # the slice's step contains the head: never extrapolate a negative layer time
     per_full = (t_step - t_head) / sample_layers * m["layers"] + t_head
     dec.close()
     desc = ("%d decode steps of a %d-layer slice (+ full LM head) at context %d, batch %d, extrapolated x%d/%d layers"
