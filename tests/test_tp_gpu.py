@@ -79,3 +79,66 @@ def test_two_rank_decoder_matches_golden(built_lib):
     for rank, e, toks in res:
         assert e < 2e-3, (rank, e)
         assert toks == GOLD["dec_tokens"].tolist(), rank
+
+
+def _lonely_rank_main(rank, world, port, out):
+    """Rank 0 starts an all-reduce that rank 1 never joins: the bounded wait must run out, the
+    status word must say so, and the context must stay usable.  Rank 1 is idle the whole time."""
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from cyb_b200 import qeng
+    ctx = qeng.Context(rank)
+
+    def exchange(b):
+        obj = [b]
+        dist.broadcast_object_list(obj, src=0)
+        return obj[0]
+
+    def allgather(b):
+        outl = [None] * world
+        dist.all_gather_object(outl, b)
+        return outl
+    ctx.tp_init(rank, world, exchange, allgather)
+    res = None
+    if rank == 0:
+        dst = torch.zeros(4096, device="cuda")
+        part = torch.ones(4096, device="cuda")
+        ctx.all_reduce_add_(dst, part)  # nobody answers
+        try:
+            ctx.device_status()
+            res = "no error"
+        except qeng.QengError as e:
+            res = (e.code, "peer" in str(e))
+        # the context still computes
+        rng = ref.rng_of(1)
+        q, s = ref.make_q4(rng, 32, 64)
+        x = rng.standard_normal((1, 64), dtype=np.float32)
+        w = ctx.pack_q4(q, s)
+        y = ctx.gemm_q4(w, torch.from_numpy(x).cuda()).cpu().numpy()
+        res = res + (ref.err_inf(y, ref.gemm_q4(x, q, s)) < 2e-6,) if isinstance(res, tuple) else res
+    dist.barrier()  # rank 1 only leaves after rank 0 is done, with nothing in flight
+    out.put((rank, res))
+    dist.destroy_process_group()
+
+
+def test_missing_peer_is_reported_not_hung(built_lib):
+    import torch
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_lonely_rank_main, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(out.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert res[0] == (-7, True, True), res
