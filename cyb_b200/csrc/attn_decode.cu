@@ -405,6 +405,7 @@ int32_t qeng_kv_append(qeng_ctx* ctx, qeng_kv_pool* pool, const float* k, const 
                        int64_t max_pages, const int32_t* pos, int64_t B, void* stream) {
   if (!ctx || !pool || !k || !v || !page_table || !pos) return qeng_fail(ctx, QENG_ERR_ARG, "kv_append: null argument");
   if (B <= 0 || max_pages <= 0) return qeng_fail(ctx, QENG_ERR_ARG, "kv_append: B and max_pages must be positive");
+  QENG_ENTER(ctx);
   dim3 grid((unsigned)pool->kv_heads, (unsigned)B);
   kv_append_kernel<<<grid, kHD, 0, (cudaStream_t)stream>>>(pool->data, k, v, page_table, pos, (int)B,
                                                            (int)pool->kv_heads, (int)pool->pages, (int)max_pages,
@@ -422,6 +423,7 @@ int32_t qeng_attn_decode(qeng_ctx* ctx, const qeng_kv_pool* pool, const uint16_t
     return qeng_fail(ctx, QENG_ERR_SHAPE, "attn_decode: query heads per kv head must divide evenly and be <= 8");
   if (((reinterpret_cast<uintptr_t>(q_f16) | reinterpret_cast<uintptr_t>(out)) & 15) != 0)
     return qeng_fail(ctx, QENG_ERR_ALIGN, "attn_decode: q and out must be 16-byte aligned");
+  QENG_ENTER(ctx);
   AttnParams p;
   p.pool = pool->data; p.q = reinterpret_cast<const __half*>(q_f16);
   p.table = page_table; p.lens = lens; p.out = out; p.status = ctx->status;
@@ -454,6 +456,7 @@ int32_t qeng_attn_decode_noalloc(qeng_ctx* ctx, const qeng_kv_pool* pool, const 
     return qeng_fail(ctx, QENG_ERR_ALIGN, "attn_decode_noalloc: q must be 16-byte aligned");
   if (ctx->device < 0 || ctx->device >= kMaxDevices)
     return qeng_fail(ctx, QENG_ERR_ARG, "attn_decode_noalloc: device index %d outside 0..%d", ctx->device, kMaxDevices - 1);
+  QENG_ENTER(ctx);
   AttnParams p;
   p.pps = pages_per_split(ctx, B, pool->kv_heads, max_pages);
   p.S = (int)((max_pages + p.pps - 1) / p.pps);

@@ -362,7 +362,8 @@ int32_t qeng_gemm_q4_prefill(qeng_ctx* ctx, const qeng_weight* w, const void* x,
   const int n_tiles = (int)((w->N + bn - 1) / bn);
   p.accs = mt256 * n_tiles >= ctx->sm_count ? 2 : 1;
   const int m_tiles = (int)((M + 128 * p.accs - 1) / (128 * p.accs));
-  static bool configured = false;
+  static bool configured_on[64] = {};  // the opt-in shared-memory size is set per device
+  bool& configured = configured_on[ctx->device & 63];
   if (!configured) {
     QENG_CUDA(ctx, cudaFuncSetAttribute(gemm_q4_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         TcCfg<128>::kStages * TcCfg<128>::kStage + 1024));

@@ -284,7 +284,8 @@ __global__ void __launch_bounds__(kThreads) gemv_q4_kernel(const GemvParams p) {
 
 template <int NT, int U>
 int32_t launch(qeng_ctx* ctx, const GemvParams& p, int grid, size_t smem, cudaStream_t stream) {
-  static bool configured = false;
+  static bool configured_on[64] = {};  // the opt-in shared-memory size is set per device
+  bool& configured = configured_on[ctx->device & 63];
   if (!configured) {
     QENG_CUDA(ctx, cudaFuncSetAttribute(gemv_q4_kernel<NT, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     configured = true;
@@ -344,6 +345,7 @@ int32_t qeng_gemm_q4(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t
   if (x_dtype < QENG_F32 || x_dtype > QENG_BF16) return qeng_fail(ctx, QENG_ERR_ARG, "gemm_q4: bad x_dtype %d", x_dtype);
   if (M < 1) return qeng_fail(ctx, QENG_ERR_SHAPE, "gemm_q4: M=%lld", (long long)M);
   if (ldx < w->K || ldy < w->N) return qeng_fail(ctx, QENG_ERR_SHAPE, "gemm_q4: leading dimension smaller than the row");
+  QENG_ENTER(ctx);
   if (M >= kPrefillRows)  // dense contraction: dequantise to bf16 in shared memory, tcgen05 MMA
     return qeng_gemm_q4_prefill(ctx, w, x, x_dtype, M, ldx, y, ldy, (flags & QENG_GEMM_ACCUMULATE) ? 1 : 0, (cudaStream_t)stream);
   qeng_gemm_fuse fuse;

@@ -473,7 +473,8 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
 
 template <int NT>
 int32_t launch_stream(qeng_ctx* ctx, const StreamParams& p, size_t smem, cudaStream_t stream) {
-  static bool configured = false;
+  static bool configured_on[64] = {};  // the opt-in shared-memory size is set per device
+  bool& configured = configured_on[ctx->device & 63];
   if (!configured) {
     QENG_CUDA(ctx, cudaFuncSetAttribute(gemv_q4_stream_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     configured = true;

@@ -255,7 +255,8 @@ int32_t qeng_lm_head_fused(qeng_ctx* ctx, const qeng_lm_tail& t, cudaStream_t st
   if (t.V <= 0 || t.D <= 0 || t.D % 8 != 0) return qeng_fail(ctx, QENG_ERR_SHAPE, "lm_head: D must be a positive multiple of 8");
   if ((size_t)t.M * t.D * 4 > 200 * 1024) return qeng_fail(ctx, QENG_ERR_SHAPE, "lm_head: D too large for the staging buffer");
   if ((reinterpret_cast<uintptr_t>(t.table) & 15) != 0) return qeng_fail(ctx, QENG_ERR_ALIGN, "lm_head: table must be 16-byte aligned");
-  static bool configured = false;
+  static bool configured_on[64] = {};  // the opt-in shared-memory size is set per device
+  bool& configured = configured_on[ctx->device & 63];
   if (!configured) {
     QENG_CUDA(ctx, cudaFuncSetAttribute(lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     configured = true;
@@ -272,6 +273,7 @@ int32_t qeng_rmsnorm(qeng_ctx* ctx, const float* x, const float* gamma, int64_t 
                      void* stream) {
   if (!ctx || !x || !gamma || !y) return qeng_fail(ctx, QENG_ERR_ARG, "rmsnorm: null argument");
   if (M <= 0 || D <= 0) return qeng_fail(ctx, QENG_ERR_SHAPE, "rmsnorm: empty shape");
+  QENG_ENTER(ctx);
   rmsnorm_kernel<<<(unsigned)M, 256, 0, (cudaStream_t)stream>>>(x, gamma, (int)D, eps, y);
   QENG_LAUNCH_CHECK(ctx);
   return QENG_OK;
@@ -281,6 +283,7 @@ int32_t qeng_rope(qeng_ctx* ctx, float* x, const int32_t* pos, int64_t M, int64_
                   void* stream) {
   if (!ctx || !x || !pos) return qeng_fail(ctx, QENG_ERR_ARG, "rope: null argument");
   if (M <= 0 || H <= 0 || hd <= 0 || hd % 2) return qeng_fail(ctx, QENG_ERR_SHAPE, "rope: bad shape");
+  QENG_ENTER(ctx);
   rope_kernel<<<(unsigned)M, 256, 0, (cudaStream_t)stream>>>(x, pos, (int)H, (int)hd, base);
   QENG_LAUNCH_CHECK(ctx);
   return QENG_OK;
@@ -289,6 +292,7 @@ int32_t qeng_rope(qeng_ctx* ctx, float* x, const int32_t* pos, int64_t M, int64_
 int32_t qeng_swiglu(qeng_ctx* ctx, const float* gate, const float* up, int64_t n, float* y, void* stream) {
   if (!ctx || !gate || !up || !y) return qeng_fail(ctx, QENG_ERR_ARG, "swiglu: null argument");
   if (n <= 0) return qeng_fail(ctx, QENG_ERR_SHAPE, "swiglu: empty shape");
+  QENG_ENTER(ctx);
   swiglu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(gate, up, n, y);
   QENG_LAUNCH_CHECK(ctx);
   return QENG_OK;
@@ -297,6 +301,7 @@ int32_t qeng_swiglu(qeng_ctx* ctx, const float* gate, const float* up, int64_t n
 int32_t qeng_add(qeng_ctx* ctx, const float* a, const float* b, int64_t n, float* y, void* stream) {
   if (!ctx || !a || !b || !y) return qeng_fail(ctx, QENG_ERR_ARG, "add: null argument");
   if (n <= 0) return qeng_fail(ctx, QENG_ERR_SHAPE, "add: empty shape");
+  QENG_ENTER(ctx);
   add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(a, b, n, y);
   QENG_LAUNCH_CHECK(ctx);
   return QENG_OK;
@@ -306,6 +311,7 @@ int32_t qeng_embed(qeng_ctx* ctx, const uint16_t* table_bf16, const int32_t* tok
                    float* x, void* stream) {
   if (!ctx || !table_bf16 || !tokens || !x) return qeng_fail(ctx, QENG_ERR_ARG, "embed: null argument");
   if (M <= 0 || D <= 0 || V <= 0) return qeng_fail(ctx, QENG_ERR_SHAPE, "embed: empty shape");
+  QENG_ENTER(ctx);
   embed_kernel<<<(unsigned)M, 256, 0, (cudaStream_t)stream>>>(table_bf16, tokens, (int)D, (int)V, x, ctx->status);
   QENG_LAUNCH_CHECK(ctx);
   return QENG_OK;
@@ -315,6 +321,7 @@ int32_t qeng_lm_head(qeng_ctx* ctx, const uint16_t* table_bf16, const float* x, 
                                 float* logits, void* stream) {
   if (!ctx || !table_bf16 || !x || !logits) return qeng_fail(ctx, QENG_ERR_ARG, "lm_head: null argument");
   if (M <= 0) return qeng_fail(ctx, QENG_ERR_SHAPE, "lm_head: empty shape");
+  QENG_ENTER(ctx);
   for (int64_t m0 = 0; m0 < M; m0 += kLmM) {
     qeng_lm_tail t;
     t.table = table_bf16; t.x = x + m0 * D; t.M = (int)(M - m0 < kLmM ? M - m0 : kLmM); t.D = (int)D; t.V = (int)V;
@@ -328,6 +335,7 @@ int32_t qeng_lm_head(qeng_ctx* ctx, const uint16_t* table_bf16, const float* x, 
 int32_t qeng_argmax(qeng_ctx* ctx, const float* logits, int64_t M, int64_t V, int32_t* idx, void* stream) {
   if (!ctx || !logits || !idx) return qeng_fail(ctx, QENG_ERR_ARG, "argmax: null argument");
   if (M <= 0 || V <= 0) return qeng_fail(ctx, QENG_ERR_SHAPE, "argmax: empty shape");
+  QENG_ENTER(ctx);
   argmax_kernel<<<(unsigned)M, 1024, 0, (cudaStream_t)stream>>>(logits, (int)V, idx);
   QENG_LAUNCH_CHECK(ctx);
   return QENG_OK;

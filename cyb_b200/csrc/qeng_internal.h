@@ -72,6 +72,13 @@ int32_t qeng_fail(qeng_ctx* ctx, int32_t code, const char* fmt, ...);
                        cudaGetErrorString(e__), __FILE__, __LINE__);                      \
   } while (0)
 
+// Entry points make the context's device current (cheap when it already is).
+#define QENG_ENTER(ctx)                                                                   \
+  do {                                                                                    \
+    int dev__ = -1;                                                                       \
+    if (cudaGetDevice(&dev__) != cudaSuccess || dev__ != (ctx)->device) QENG_CUDA(ctx, cudaSetDevice((ctx)->device)); \
+  } while (0)
+
 #define QENG_LAUNCH_CHECK(ctx)                                                            \
   do {                                                                                    \
     cudaError_t e__ = cudaGetLastError();                                                 \
