@@ -24,6 +24,8 @@ constexpr int kCW = 16;                        // consumer warps
 constexpr int kCT = kCW * 32;                  // consumer threads
 constexpr int kThreadsS = kCT + 32;            // + producer warp
 constexpr int kMaxStages = 12;
+constexpr int kTG = 2;                         // tile groups: consumer warps split into independent halves
+constexpr int kGW = kCW / kTG;                 // warps per tile group
 constexpr int kGroups = 3;                     // groups of 8 k one consumer thread stages: K <= 8 * kGroups * kCT
 
 struct StreamParams {
@@ -111,6 +113,8 @@ __device__ __forceinline__ float2 lds64f(uint32_t addr) {
   return v;
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(kCT) : "memory"); }
+// the warps of one tile group (named barriers 2, 3, ...)
+__device__ __forceinline__ void group_sync(int gi) { asm volatile("bar.sync %0, %1;\n" ::"r"(2 + gi), "n"(kGW * 32) : "memory"); }
 
 __device__ __forceinline__ float act_f32(const void* x, int dtype, long long i) {
   if (dtype == QENG_F32) return reinterpret_cast<const float*>(x)[i];
@@ -145,7 +149,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(smem_u32(full + s), 1);
-      mbar_init(smem_u32(empty + s), kCW);
+      mbar_init(smem_u32(empty + s), kGW);
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -309,21 +313,32 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
   consumer_sync();
 
   // ---- main loop over this CTA's row tiles -------------------------------------------
+  // The consumer warps form kTG independent groups that take the CTA's tiles in turn: while one
+  // group reduces a tile and waits for its next stage, the other keeps the pipes busy.
+  const int gi = warp / kGW, wi = warp % kGW;
   // Lanes whose B column lies beyond the activations read an existing column instead:
   // every load stays in bounds and unpredicated, and their output columns are ignored.
   // All addresses are 32-bit shared-space byte addresses advanced by compile-time strides.
   uint32_t xcol[NT];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
-    xcol[nt] = smem_u32(xs_h) + (uint32_t)((min(nt * 8 + g, p.cols - 1) * CS + t * 8) * 2) + (uint32_t)warp * 128u;
-  const uint32_t zcol = smem_u32(xsum) + (uint32_t)t * 8u + (uint32_t)warp * (2u * 32u * NT);
-  const uint32_t ring_w = smem_u32(ring) + (uint32_t)warp * 512u + (uint32_t)lane * 16u;
-  const uint32_t ring_s = smem_u32(ring) + kSC * 512u + (uint32_t)warp * 64u + (uint32_t)g * 8u;
+    xcol[nt] = smem_u32(xs_h) + (uint32_t)((min(nt * 8 + g, p.cols - 1) * CS + t * 8) * 2) + (uint32_t)wi * 128u;
+  const uint32_t zcol = smem_u32(xsum) + (uint32_t)t * 8u + (uint32_t)wi * (2u * 32u * NT);
+  const uint32_t ring_w = smem_u32(ring) + (uint32_t)wi * 512u + (uint32_t)lane * 16u;
+  const uint32_t ring_s = smem_u32(ring) + kSC * 512u + (uint32_t)wi * 64u + (uint32_t)g * 8u;
   const int red_stride = 16 * 8 * NT;  // floats per warp per buffer
   bool failed = false;
   int s = 0, buf = 0, tcount = 0;
   uint32_t ph = 0;
   for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++tcount) {
+    if ((tcount % kTG) != gi) {  // the other group's tile: only step over its stages
+      s += stages_per_tile;
+      while (s >= NS) {
+        s -= NS;
+        ph ^= 1u;
+      }
+      continue;
+    }
     float acc[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
@@ -335,10 +350,10 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
       const uint32_t wb = ring_w + (uint32_t)s * kStageBytes;
       const uint32_t sb = ring_s + (uint32_t)s * kStageBytes;
 #pragma unroll
-      for (int rep = 0; rep < kSC / kCW; ++rep) {
-        if (warp + rep * kCW < nc) {
-          const uint4 w = lds128(wb + rep * (kCW * 512));
-          const uint2 s2 = lds64(sb + rep * (kCW * 64));
+      for (int rep = 0; rep < kSC / kGW; ++rep) {
+        if (wi + rep * kGW < nc) {
+          const uint4 w = lds128(wb + rep * (kGW * 512));
+          const uint2 s2 = lds64(sb + rep * (kGW * 64));
 #pragma unroll
           for (int b1 = 0; b1 < 2; ++b1) {
             // A fragments: a 4-bit code c in the low mantissa bits of an f16 is the subnormal
@@ -350,8 +365,8 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
             const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&sbits));
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-              const uint4 xb = lds128(xcol[nt] + xo + (rep * kCW * 128 + b1 * 64));
-              const float2 z = lds64f(zcol + zo + ((rep * kCW * 2 + b1) * 32 * NT + nt * 32));
+              const uint4 xb = lds128(xcol[nt] + xo + (rep * kGW * 128 + b1 * 64));
+              const float2 z = lds64f(zcol + zo + ((rep * kGW * 2 + b1) * 32 * NT + nt * 32));
               float d[4];
               mma16816(d, w0 & mlo, w1 & mlo, w0 & mhi, w1 & mhi, xb.x, xb.y, z.x, z.y, z.x, z.y);
               mma16816(d, v0 & mlo, v1 & mlo, v0 & mhi, v1 & mhi, xb.z, xb.w, d[0], d[1], d[2], d[3]);
@@ -377,7 +392,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
     // ---- the 16 partial accumulators meet in shared memory --------------------------
     // red[buf][warp][act][row16]; the reader of buffer `buf` finishes before it arrives at
     // the next tile's barrier, and buffer `buf` is written again only after that barrier
-    float* myred = red + ((size_t)buf * kCW + warp) * red_stride;
+    float* myred = red + (((size_t)gi * 2 + buf) * kGW + wi) * red_stride;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       if (p.split) {
@@ -392,9 +407,9 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
         myred[(a + 1) * 16 + g + 8] = acc[nt][3];
       }
     }
-    consumer_sync();
-    if (warp == (tcount & (kCW - 1))) {
-      const float* rb = red + (size_t)buf * kCW * red_stride;
+    group_sync(gi);
+    if (wi == ((tcount / kTG) % kGW)) {
+      const float* rb = red + ((size_t)gi * 2 + buf) * kGW * red_stride;
       if (p.epilogue == QENG_EPI_QKV) {
         const qeng_qkv_epi& E = p.qkv;
         const int head = tile >> 3, i = ((tile & 7) << 3);
@@ -402,7 +417,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
           const int a = e >> 3, r = e & 7;
           float lo = 0.f, hi = 0.f;  // dims i+r and i+r+64 of this head
 #pragma unroll
-          for (int w = 0; w < kCW; ++w) {
+          for (int w = 0; w < kGW; ++w) {
             lo += rb[w * red_stride + a * 16 + r];
             hi += rb[w * red_stride + a * 16 + r + 8];
           }
@@ -443,7 +458,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
           const int a = e >> 3, r = e & 7;
           float gate = 0.f, up = 0.f;
 #pragma unroll
-          for (int w = 0; w < kCW; ++w) {
+          for (int w = 0; w < kGW; ++w) {
             gate += rb[w * red_stride + a * 16 + r];
             up += rb[w * red_stride + a * 16 + r + 8];
           }
@@ -457,7 +472,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
           const int a = e >> 4, r = e & 15;
           float v = 0.f;
 #pragma unroll
-          for (int w = 0; w < kCW; ++w) v += rb[w * red_stride + a * 16 + r];
+          for (int w = 0; w < kGW; ++w) v += rb[w * red_stride + a * 16 + r];
           v = v * 16777216.0f * oscale[a];
           const size_t o = (size_t)a * p.ldy + (size_t)tile * 16 + r;
           if (p.epilogue == QENG_EPI_ACCUM) v += p.y[o];
