@@ -14,6 +14,7 @@
 // one warp applies the fused epilogue.
 //
 // HBM-bound: algorithmic bytes = N*K*0.5625 + activations + outputs.
+#include <cstdlib>
 #include "qeng_internal.h"
 
 namespace {
@@ -24,8 +25,6 @@ constexpr int kCW = 16;                        // consumer warps
 constexpr int kCT = kCW * 32;                  // consumer threads
 constexpr int kThreadsS = kCT + 32;            // + producer warp
 constexpr int kMaxStages = 12;
-constexpr int kTG = 2;                         // tile groups: consumer warps split into independent halves
-constexpr int kGW = kCW / kTG;                 // warps per tile group
 constexpr int kGroups = 3;                     // groups of 8 k one consumer thread stages: K <= 8 * kGroups * kCT
 
 struct StreamParams {
@@ -114,7 +113,8 @@ __device__ __forceinline__ float2 lds64f(uint32_t addr) {
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(kCT) : "memory"); }
 // the warps of one tile group (named barriers 2, 3, ...)
-__device__ __forceinline__ void group_sync(int gi) { asm volatile("bar.sync %0, %1;\n" ::"r"(2 + gi), "n"(kGW * 32) : "memory"); }
+template <int GW>
+__device__ __forceinline__ void group_sync(int gi) { asm volatile("bar.sync %0, %1;\n" ::"r"(2 + gi), "n"(GW * 32) : "memory"); }
 
 __device__ __forceinline__ float act_f32(const void* x, int dtype, long long i) {
   if (dtype == QENG_F32) return reinterpret_cast<const float*>(x)[i];
@@ -127,8 +127,9 @@ __device__ __forceinline__ uint32_t h2bits(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <int NT>
+template <int NT, int kTG>
 __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const StreamParams p) {
+  constexpr int kGW = kCW / kTG;  // warps per tile group
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int Kp = p.nchunks * 64;
@@ -407,7 +408,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
         myred[(a + 1) * 16 + g + 8] = acc[nt][3];
       }
     }
-    group_sync(gi);
+    group_sync<kGW>(gi);
     if (wi == ((tcount / kTG) % kGW)) {
       const float* rb = red + ((size_t)gi * 2 + buf) * kGW * red_stride;
       if (p.epilogue == QENG_EPI_QKV) {
@@ -486,12 +487,12 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
   if (failed && lane == 0) atomicExch(p.status, 4);
 }
 
-template <int NT>
+template <int NT, int kTG>
 int32_t launch_stream(qeng_ctx* ctx, const StreamParams& p, size_t smem, cudaStream_t stream) {
   static bool configured_on[64] = {};  // the opt-in shared-memory size is set per device
   bool& configured = configured_on[ctx->device & 63];
   if (!configured) {
-    QENG_CUDA(ctx, cudaFuncSetAttribute(gemv_q4_stream_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    QENG_CUDA(ctx, cudaFuncSetAttribute(gemv_q4_stream_kernel<NT, kTG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     configured = true;
   }
   const int grid = p.ntiles < ctx->sm_count ? p.ntiles : ctx->sm_count;
@@ -507,7 +508,7 @@ int32_t launch_stream(qeng_ctx* ctx, const StreamParams& p, size_t smem, cudaStr
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = ctx->pdl ? 1 : 0;
-  QENG_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4_stream_kernel<NT>, p));
+  QENG_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4_stream_kernel<NT, kTG>, p));
   return QENG_OK;
 }
 
@@ -569,9 +570,20 @@ int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
     p.qkv = *fuse.qkv;
   }
   *handled = true;
+  // Tile groups: more groups hide more of the per-tile reduction, but a group with no tile idles,
+  // so the split follows the number of tiles a CTA owns.
+  const int grid = p.ntiles < ctx->sm_count ? p.ntiles : ctx->sm_count;
+  const int per_cta = (p.ntiles + grid - 1) / grid;
+  int tg = per_cta >= 8 ? 4 : (per_cta >= 2 ? 2 : 1);
+  static const int tg_env = [] { const char* e = getenv("QENG_STREAM_GROUPS"); return e ? atoi(e) : 0; }();
+  if (tg_env == 1 || tg_env == 2 || tg_env == 4) tg = tg_env;
+#define QENG_STREAM_CASE(NT_)                                                   \
+  (tg == 4 ? launch_stream<NT_, 4>(ctx, p, f.smem, stream)                      \
+           : (tg == 2 ? launch_stream<NT_, 2>(ctx, p, f.smem, stream) : launch_stream<NT_, 1>(ctx, p, f.smem, stream)))
   switch (f.NT) {
-    case 1: return launch_stream<1>(ctx, p, f.smem, stream);
-    case 2: return launch_stream<2>(ctx, p, f.smem, stream);
-    default: return launch_stream<4>(ctx, p, f.smem, stream);
+    case 1: return QENG_STREAM_CASE(1);
+    case 2: return QENG_STREAM_CASE(2);
+    default: return QENG_STREAM_CASE(4);
   }
+#undef QENG_STREAM_CASE
 }
