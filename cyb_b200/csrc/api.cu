@@ -37,6 +37,7 @@ int32_t qeng_create(int32_t device, qeng_ctx** out) {
   }
   ctx->sm_count = prop.multiProcessorCount;
   ctx->pdl = getenv("QENG_NO_PDL") == nullptr;
+  ctx->l2_prefetch = getenv("QENG_NO_L2_PREFETCH") == nullptr;
   if (cudaMalloc(&ctx->status, 64) != cudaSuccess || cudaMemset(ctx->status, 0, 64) != cudaSuccess) {
     delete ctx;
     return QENG_ERR_CUDA;

@@ -458,6 +458,21 @@ int32_t qeng_decoder_free(qeng_ctx* ctx, qeng_decoder* d) {
   return QENG_OK;
 }
 
+// The order of the decode loop is fixed, so every fused matrix knows its successor: the
+// streaming matmul uses it to keep HBM busy across kernel boundaries.
+static void link_weights(qeng_decoder* d) {
+  qeng_weight* prev = nullptr;
+  for (auto& L : d->layers) {
+    qeng_weight* seq[4] = {L.wqkv, L.wo, L.wgu, L.wdown};
+    for (qeng_weight* w : seq) {
+      if (!w) continue;
+      w->next = nullptr;
+      if (prev) prev->next = w;
+      prev = w;
+    }
+  }
+}
+
 int32_t qeng_decoder_load_matrix(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, int32_t which, const uint8_t* q,
                                  const uint16_t* s, int64_t N, int64_t K) {
   if (!ctx || !d || !q || !s) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_load_matrix: null argument");
@@ -536,6 +551,7 @@ int32_t qeng_decoder_load_matrix(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, 
       rc = qeng_weight_pack_q4(ctx, f.q.data(), f.s.data(), f.N, f.K, &L.wgu);
     }
   }
+  link_weights(d);
   if (d->graph) { cudaGraphExecDestroy(d->graph); d->graph = nullptr; }
   return rc;
 }

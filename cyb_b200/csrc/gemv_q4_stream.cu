@@ -28,6 +28,11 @@ constexpr int kMaxStages = 12;
 constexpr int kGroups = 3;                     // groups of 8 k one consumer thread stages: K <= 8 * kGroups * kCT
 
 struct StreamParams {
+  // the matrix multiplied next (may be null): its tiles are requested into L2 once this
+  // CTA's own loads are all issued
+  const uint4* pf_qs;
+  const uint2* pf_sc;
+  int pf_ntiles, pf_nchunks;
   const uint4* qs;
   const uint2* sc;
   int ntiles, nchunks;
@@ -111,6 +116,9 @@ __device__ __forceinline__ float2 lds64f(uint32_t addr) {
   asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(v.x), "=f"(v.y) : "r"(addr));
   return v;
 }
+__device__ __forceinline__ void l2_prefetch(const void* gptr, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(gptr), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(kCT) : "memory"); }
 // the warps of one tile group (named barriers 2, 3, ...)
 template <int GW>
@@ -162,10 +170,14 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
     // ===== producer: stream this CTA's row tiles through the ring ==================
     if (lane == 0) {
       bool failed = false;
-      int s = 0;
-      uint32_t ph = 0;
-      for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
-        for (int st = 0; st < stages_per_tile; ++st) {
+      const int NSg = NS / kTG;  // ring slots per tile group; group g owns slots [g * NSg, (g + 1) * NSg)
+      int tcount = 0;
+      for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++tcount) {
+        const int grp = tcount % kTG;
+        int use = (tcount / kTG) * stages_per_tile;  // stage uses of this group so far
+        for (int st = 0; st < stages_per_tile; ++st, ++use) {
+          const int s = grp * NSg + use % NSg;
+          const uint32_t ph = (uint32_t)(use / NSg) & 1u;
           if (!failed && !mbar_wait(smem_u32(empty + s), ph ^ 1u)) failed = true;
           const int c0 = st * kSC;
           const int nc = min(kSC, p.nchunks - c0);
@@ -175,13 +187,20 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
           mbar_expect_tx(bar, (uint32_t)nc * 576u);
           bulk_g2s(dst, p.qs + chunk * 32, (uint32_t)nc * 512u, bar);
           bulk_g2s(dst + kSC * 512, p.sc + chunk * 8, (uint32_t)nc * 64u, bar);
-          if (++s == NS) {
-            s = 0;
-            ph ^= 1u;
-          }
         }
       }
       if (failed) atomicExch(p.status, 4);
+    }
+    __syncwarp();
+    // Own loads are all in flight: ask L2 for this CTA's share of the next matrix, so that HBM
+    // does not idle while the consumers drain the ring and the next kernel starts up.
+    if (p.pf_qs != nullptr) {
+      const uint32_t qb = (uint32_t)p.pf_nchunks * 512u, sb = (uint32_t)p.pf_nchunks * 64u;
+      for (int tile = blockIdx.x + gridDim.x * lane; tile < p.pf_ntiles; tile += gridDim.x * 32) {
+        const char* q = reinterpret_cast<const char*>(p.pf_qs) + (size_t)tile * qb;
+        for (uint32_t o = 0; o < qb; o += 32768u) l2_prefetch(q + o, min(32768u, qb - o));
+        l2_prefetch(reinterpret_cast<const char*>(p.pf_sc) + (size_t)tile * sb, sb);
+      }
     }
     return;
   }
@@ -329,17 +348,13 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
   const uint32_t ring_s = smem_u32(ring) + kSC * 512u + (uint32_t)wi * 64u + (uint32_t)g * 8u;
   const int red_stride = 16 * 8 * NT;  // floats per warp per buffer
   bool failed = false;
-  int s = 0, buf = 0, tcount = 0;
+  // Each group owns NS / kTG consecutive ring slots and is the only waiter on their barriers, so a
+  // barrier's phases are seen strictly in order however far the groups drift apart.
+  const int NSg = NS / kTG, s_first = gi * NSg, s_end = s_first + NSg;
+  int s = s_first, buf = 0, tcount = 0;
   uint32_t ph = 0;
   for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++tcount) {
-    if ((tcount % kTG) != gi) {  // the other group's tile: only step over its stages
-      s += stages_per_tile;
-      while (s >= NS) {
-        s -= NS;
-        ph ^= 1u;
-      }
-      continue;
-    }
+    if ((tcount % kTG) != gi) continue;  // another group's tile
     float acc[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
@@ -384,8 +399,8 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
       // this warp is done with the stage
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(empty + s));
-      if (++s == NS) {
-        s = 0;
+      if (++s == s_end) {
+        s = s_first;
         ph ^= 1u;
       }
     }
@@ -564,6 +579,9 @@ int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
   p.y = y; p.ldy = ldy;
   p.gamma = fuse.norm_gamma; p.eps = fuse.norm_eps; p.epilogue = fuse.epilogue; p.resid = fuse.resid;
   p.nstages = f.nstages; p.status = ctx->status;
+  const qeng_weight* nx = ctx->l2_prefetch ? w->next : nullptr;
+  p.pf_qs = nx ? nx->qs : nullptr; p.pf_sc = nx ? nx->sc : nullptr;
+  p.pf_ntiles = nx ? (int)nx->ntiles : 0; p.pf_nchunks = nx ? (int)nx->nchunks : 0;
   p.qkv = qeng_qkv_epi();
   if (fuse.epilogue == QENG_EPI_QKV) {
     if (!fuse.qkv) return qeng_fail(ctx, QENG_ERR_ARG, "gemm_q4: fused q|k|v epilogue without its arguments");
@@ -575,6 +593,7 @@ int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
   const int grid = p.ntiles < ctx->sm_count ? p.ntiles : ctx->sm_count;
   const int per_cta = (p.ntiles + grid - 1) / grid;
   int tg = per_cta >= 8 ? 4 : (per_cta >= 2 ? 2 : 1);
+  while (tg > 1 && f.nstages / tg < 2) tg >>= 1;  // every group keeps at least two ring slots
   static const int tg_env = [] { const char* e = getenv("QENG_STREAM_GROUPS"); return e ? atoi(e) : 0; }();
   if (tg_env == 1 || tg_env == 2 || tg_env == 4) tg = tg_env;
 #define QENG_STREAM_CASE(NT_)                                                   \

@@ -161,6 +161,12 @@ int32_t qeng_weight_dequant_f32(qeng_ctx* ctx, const qeng_weight* w, float* out,
   return QENG_OK;
 }
 
+int32_t qeng_weight_set_next(qeng_ctx* ctx, qeng_weight* w, const qeng_weight* next) {
+  if (!ctx || !w) return qeng_fail(ctx, QENG_ERR_ARG, "weight_set_next: null argument");
+  w->next = next;
+  return QENG_OK;
+}
+
 int32_t qeng_weight_free(qeng_ctx* ctx, qeng_weight* w) {
   if (!w) return QENG_OK;
   if (ctx) cudaSetDevice(ctx->device);

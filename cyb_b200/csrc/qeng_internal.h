@@ -29,6 +29,7 @@ struct qeng_weight {
   uint4* qs;           // nibble plane, ntiles*nchunks*32 uint4
   uint2* sc;           // scale plane,  ntiles*nchunks*8 uint2
   int64_t bytes;       // device bytes held
+  const qeng_weight* next = nullptr;  // matrix the caller multiplies by after this one (L2 prefetch hint)
 };
 
 struct qeng_kv_pool {
@@ -55,6 +56,7 @@ struct qeng_ctx {
   void* p2p_peer[8] = {};
   size_t p2p_flag_off = 0, p2p_counter_off = 0;
   bool p2p_ready = false;
+  bool l2_prefetch = true;    // the streaming matmul requests the hinted next matrix into L2
   bool pdl = true;            // launch the streaming matmul with programmatic stream serialization
   // per-CTA argmax partials and the arrival counter of the fused LM head
   float* tail_val = nullptr;

@@ -78,6 +78,7 @@ _sig("qeng_weight_pack_q4", _i32, _vp, _vp, _vp, _i64, _i64, C.POINTER(_vp))
 _sig("qeng_weight_unpack_q4", _i32, _vp, _vp, _vp, _vp)
 _sig("qeng_weight_dequant_f32", _i32, _vp, _vp, _vp, _vp)
 _sig("qeng_weight_free", _i32, _vp, _vp)
+_sig("qeng_weight_set_next", _i32, _vp, _vp, _vp)
 _sig("qeng_weight_rows", _i64, _vp)
 _sig("qeng_weight_cols", _i64, _vp)
 _sig("qeng_weight_device_bytes", _i64, _vp)
@@ -321,6 +322,11 @@ class Weight:
         out = torch.empty((self.rows, self.cols), dtype=torch.float32, device="cuda:%d" % self.ctx.device)
         self.ctx.check(_lib.qeng_weight_dequant_f32(self.ctx.h, self.h, _dev_ptr(out), _cur_stream()))
         return out
+
+    def set_next(self, nxt):
+        """Hint that the matmul after one over this matrix is over `nxt` (None clears it)."""
+        self._next = nxt  # keep it alive while the hint is set
+        self.ctx.check(_lib.qeng_weight_set_next(self.ctx.h, self.h, nxt.h if nxt is not None else None))
 
     def free(self):
         if self.h:

@@ -107,6 +107,12 @@ int32_t qeng_weight_free(qeng_ctx* ctx, qeng_weight* w);
 int64_t qeng_weight_rows(const qeng_weight* w);
 int64_t qeng_weight_cols(const qeng_weight* w);
 int64_t qeng_weight_device_bytes(const qeng_weight* w);
+/* Hint: the matmul the caller runs after one over `w` is over `next` (NULL clears the hint).
+ * The decode kernel then asks L2 for `next` while it finishes `w`, so that HBM keeps
+ * streaming across the kernel boundary.  Results never depend on the hint.  `next` must stay
+ * alive while the hint is set.  The reference has no counterpart: its loop order
+ * (decide/pipeline.md:51) is what makes the next matrix known. */
+int32_t qeng_weight_set_next(qeng_ctx* ctx, qeng_weight* w, const qeng_weight* next);
 
 /* ---- quantized matmul (the "QKV / O proj / FFN" steps of decide/pipeline.md:51)
  * y[M,N] (f32, leading dimension ldy) = x[M,K] (x_dtype, leading dimension ldx)
