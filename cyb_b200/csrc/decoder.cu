@@ -103,6 +103,39 @@ __global__ void record_first_kernel(const int32_t* __restrict__ next, int32_t* o
   if ((int)threadIdx.x < B) out_tokens[threadIdx.x] = next[threadIdx.x];
 }
 
+// Sharded LM head, last step: gathered[r][m] = (max logit, its global index) of rank r.  Pick the
+// token (largest value, lowest index on ties, as the unsharded argmax does), record it, advance
+// the sequences, gather the next embedding, and clear the gather buffer for the next step.
+__global__ void __launch_bounds__(256) tp_pick_kernel(float* gathered, int world, int B, int V, int D,
+                                                      const uint16_t* __restrict__ emb, float* __restrict__ xout,
+                                                      int32_t* next, int32_t* pos, int32_t* lens, int32_t* out_tokens,
+                                                      int32_t* step, int32_t* status) {
+  __shared__ int tok[16];
+  const int tid = threadIdx.x;
+  if (tid < B) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int r = 0; r < world; ++r) {
+      const float v = gathered[2 * (r * B + tid)];
+      const float fi = gathered[2 * (r * B + tid) + 1];
+      const int i = fi >= 0.f && fi < 16777216.f ? (int)fi : 0x7fffffff;
+      if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+    if ((unsigned)bi >= (unsigned)V) { bi = 0; atomicExch(status, 3); }  // only if every logit was NaN
+    tok[tid] = bi;
+    next[tid] = bi;
+    out_tokens[(size_t)(*step + 1) * B + tid] = bi;
+    pos[tid] += 1;
+    lens[tid] += 1;
+  }
+  __syncthreads();
+  if (tid == 0) *step += 1;
+  for (int i = tid; i < 2 * world * B; i += 256) gathered[i] = 0.f;
+  for (int m = 0; m < B; ++m)
+    for (int i = tid; i < D; i += 256)
+      xout[(size_t)m * D + i] = __uint_as_float((uint32_t)emb[(size_t)tok[m] * D + i] << 16);
+}
+
 }  // namespace
 
 struct qeng_decoder {
@@ -131,6 +164,13 @@ struct qeng_decoder {
   int batch = 0;
   std::vector<int32_t> len;  // host copy of sequence lengths
   bool have_logits = false;
+  // tensor parallelism: the LM head is split by vocabulary rows [v0, v0 + vloc); every rank's
+  // (max, index) pair per sequence is summed into `tp_gath` (the other ranks' slots of `tp_pairs`
+  // stay zero, so the sum is a gather) and one small kernel picks the token
+  bool vsplit = false;
+  int v0 = 0, vloc = 0;
+  float *tp_pairs = nullptr, *tp_gath = nullptr;  // [world][max_batch][2]
+  bool logits_partial = false;  // after a sharded decode step only columns [v0, v0 + vloc) are current
   cudaStream_t stream = nullptr;
   cudaStream_t own_stream = nullptr;
   cudaGraphExec_t graph = nullptr;
@@ -314,8 +354,45 @@ int32_t run_layer(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, const int
   return row_split(ctx, d, L.wdown, d->act, d->F, rows, st);
 }
 
+// sharded LM head: every rank fills its vocabulary columns of the logits, in chunks of up to 4 rows
+int32_t tail_sharded(qeng_ctx* ctx, qeng_decoder* d, const float* x_last, int B, bool finalize, cudaStream_t st) {
+  const int dm = d->cfg.d_model, V = d->cfg.vocab, W = d->cfg.tp_world, R = d->cfg.tp_rank;
+  if (!finalize)  // the other ranks' columns must be zero for the sum below
+    QENG_CUDA(ctx, cudaMemsetAsync(d->logits, 0, (size_t)B * V * 4, st));
+  for (int m0 = 0; m0 < B; m0 += 4) {
+    qeng_lm_tail t;
+    t.table = d->lm_head; t.x = x_last + (size_t)m0 * dm; t.M = B - m0 < 4 ? B - m0 : 4; t.D = dm; t.V = d->vloc;
+    t.logits = d->logits + (size_t)m0 * V; t.v0 = d->v0; t.Vtot = V; t.ldl = V;
+    t.gamma = d->final_norm; t.eps = d->cfg.rms_eps;
+    if (finalize) { t.pairs = d->tp_pairs; t.pair_slot = R * B + m0; }
+    d->launches += 1;
+    int32_t rc = qeng_lm_head_fused(ctx, t, st);
+    if (rc != QENG_OK) return rc;
+  }
+  if (!finalize) {  // prompt end: every rank needs the full logits (zero + x = x, so the sum is exact)
+    d->logits_partial = false;
+    return qeng_tp_all_reduce_internal(ctx, d->logits, (int64_t)B * V, st);
+  }
+  const int64_t n = (int64_t)2 * W * B;  // a multiple of 4: W is even
+  int32_t rc;
+  if (qeng_tp_p2p_ready(ctx, n)) {
+    rc = qeng_tp_allreduce_add(ctx, d->tp_gath, d->tp_pairs, n, st);  // tp_gath is zero on entry
+  } else {
+    QENG_CUDA(ctx, cudaMemcpyAsync(d->tp_gath, d->tp_pairs, n * 4, cudaMemcpyDeviceToDevice, st));
+    rc = qeng_tp_all_reduce_internal(ctx, d->tp_gath, n, st);
+    d->launches += 1;
+  }
+  if (rc != QENG_OK) return rc;
+  tp_pick_kernel<<<1, 256, 0, st>>>(d->tp_gath, W, B, V, dm, d->emb, d->x, d->next, d->pos, d->lens, d->out_tokens,
+                                    d->step, ctx->status);
+  QENG_LAUNCH_CHECK(ctx);
+  d->launches += 2;
+  return QENG_OK;
+}
+
 // final norm + LM head (+ greedy finalisation: sample, record, advance, embed the next token)
 int32_t tail(qeng_ctx* ctx, qeng_decoder* d, const float* x_last, int B, bool finalize, cudaStream_t st) {
+  if (d->vsplit) return tail_sharded(ctx, d, x_last, B, finalize, st);
   if (B <= 4) {
     qeng_lm_tail t;
     t.table = d->lm_head; t.x = x_last; t.M = B; t.D = d->cfg.d_model; t.V = d->cfg.vocab; t.logits = d->logits;
@@ -393,6 +470,9 @@ int32_t qeng_decoder_create(qeng_ctx* ctx, const qeng_model_cfg* cfg, qeng_decod
   d->pages = (int64_t)d->max_pages * cfg->max_batch;
   d->layers.resize(cfg->layers);
   d->max_steps = cfg->max_seq;
+  d->vsplit = t > 1 && cfg->vocab % t == 0 && cfg->vocab <= (1 << 24);
+  d->vloc = d->vsplit ? cfg->vocab / t : cfg->vocab;
+  d->v0 = d->vsplit ? cfg->tp_rank * d->vloc : 0;
   const int64_t dm = cfg->d_model;
   const size_t pool_bytes = (size_t)cfg->layers * d->pages * d->Hkv * 2 * kPage * kHD * 2;
   cudaError_t e = cudaMalloc(&d->pool, pool_bytes);
@@ -402,6 +482,13 @@ int32_t qeng_decoder_create(qeng_ctx* ctx, const qeng_model_cfg* cfg, qeng_decod
   if (e == cudaSuccess) e = cudaMalloc(&d->xlast, (size_t)cfg->max_batch * dm * 4);
   if (e == cudaSuccess) e = cudaMalloc(&d->logits, (size_t)cfg->max_batch * cfg->vocab * 4);
   if (e == cudaSuccess) e = cudaMalloc(&d->next, 64 * 4);
+  if (e == cudaSuccess && d->vsplit) {
+    const size_t pb = (size_t)2 * t * cfg->max_batch * 4;
+    e = cudaMalloc(&d->tp_pairs, pb);
+    if (e == cudaSuccess) e = cudaMemset(d->tp_pairs, 0, pb);
+    if (e == cudaSuccess) e = cudaMalloc(&d->tp_gath, pb);
+    if (e == cudaSuccess) e = cudaMemset(d->tp_gath, 0, pb);
+  }
   if (e == cudaSuccess) e = cudaMalloc(&d->step, 4);
   if (e == cudaSuccess) e = cudaMalloc(&d->out_tokens, (size_t)(d->max_steps + 1) * cfg->max_batch * 4);
   if (e == cudaSuccess) e = cudaMalloc(&d->dec_table, (size_t)cfg->max_batch * d->max_pages * 4);
@@ -450,7 +537,7 @@ int32_t qeng_decoder_free(qeng_ctx* ctx, qeng_decoder* d) {
     if (L.norm2) cudaFree(L.norm2);
   }
   void* bufs[] = {d->emb, d->lm_head, d->final_norm, d->rope_cs, d->pool, d->x, d->qkv, d->att, d->act, d->part, d->xnr, d->gu, d->q16,
-                  d->pos, d->lens, d->table, d->xn, d->xlast, d->logits, d->next, d->out_tokens, d->step, d->dec_table};
+                  d->pos, d->lens, d->table, d->xn, d->xlast, d->logits, d->next, d->out_tokens, d->step, d->dec_table, d->tp_pairs, d->tp_gath};
   for (void* p : bufs)
     if (p) cudaFree(p);
   if (d->own_stream) cudaStreamDestroy(d->own_stream);
@@ -569,11 +656,14 @@ int32_t qeng_decoder_load_head(qeng_ctx* ctx, qeng_decoder* d, const uint16_t* e
                                const float* final_gamma) {
   if (!ctx || !d || !emb || !lm_head || !final_gamma) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_load_head: null argument");
   const size_t n = (size_t)d->cfg.vocab * d->cfg.d_model;
+  const size_t nloc = (size_t)d->vloc * d->cfg.d_model;  // this rank's vocabulary rows of the head
+  lm_head += (size_t)d->v0 * d->cfg.d_model;
+  QENG_CUDA(ctx, cudaSetDevice(ctx->device));
   if (!d->emb) QENG_CUDA(ctx, cudaMalloc(&d->emb, n * 2));
-  if (!d->lm_head) QENG_CUDA(ctx, cudaMalloc(&d->lm_head, n * 2));
+  if (!d->lm_head) QENG_CUDA(ctx, cudaMalloc(&d->lm_head, nloc * 2));
   if (!d->final_norm) QENG_CUDA(ctx, cudaMalloc(&d->final_norm, (size_t)d->cfg.d_model * 4));
   QENG_CUDA(ctx, cudaMemcpy(d->emb, emb, n * 2, cudaMemcpyHostToDevice));
-  QENG_CUDA(ctx, cudaMemcpy(d->lm_head, lm_head, n * 2, cudaMemcpyHostToDevice));
+  QENG_CUDA(ctx, cudaMemcpy(d->lm_head, lm_head, nloc * 2, cudaMemcpyHostToDevice));
   QENG_CUDA(ctx, cudaMemcpy(d->final_norm, final_gamma, (size_t)d->cfg.d_model * 4, cudaMemcpyHostToDevice));
   return QENG_OK;
 }
@@ -584,6 +674,7 @@ int32_t qeng_decoder_reset(qeng_ctx* ctx, qeng_decoder* d, int32_t batch) {
   d->batch = batch;
   d->len.assign(batch, 0);
   d->have_logits = false;
+  d->logits_partial = false;
   return QENG_OK;
 }
 
@@ -649,9 +740,13 @@ int32_t qeng_decoder_decode(qeng_ctx* ctx, qeng_decoder* d, int32_t steps, int32
   QENG_CUDA(ctx, cudaMemcpyAsync(d->pos, pos.data(), B * 4, cudaMemcpyHostToDevice, st));
   QENG_CUDA(ctx, cudaMemcpyAsync(d->lens, lens.data(), B * 4, cudaMemcpyHostToDevice, st));
   QENG_CUDA(ctx, cudaMemsetAsync(d->step, 0, 4, st));
-  {  // the token sampled from the logits at hand is fed first
-    int32_t rc = qeng_argmax(ctx, d->logits, B, d->cfg.vocab, d->next, st);
-    if (rc == QENG_OK) rc = qeng_embed(ctx, d->emb, d->next, B, d->cfg.d_model, d->cfg.vocab, d->x, st);
+  {  // the token sampled from the logits at hand is fed first; after a sharded decode step it has
+     // been picked and embedded already (only this rank's logit columns are current then)
+    int32_t rc = QENG_OK;
+    if (!d->logits_partial) {
+      rc = qeng_argmax(ctx, d->logits, B, d->cfg.vocab, d->next, st);
+      if (rc == QENG_OK) rc = qeng_embed(ctx, d->emb, d->next, B, d->cfg.d_model, d->cfg.vocab, d->x, st);
+    }
     if (rc != QENG_OK) return rc;
     record_first_kernel<<<1, 32, 0, st>>>(d->next, d->out_tokens, B);
     QENG_LAUNCH_CHECK(ctx);
@@ -677,6 +772,7 @@ int32_t qeng_decoder_decode(qeng_ctx* ctx, qeng_decoder* d, int32_t steps, int32
   QENG_CUDA(ctx, cudaMemcpyAsync(&status, ctx->status, 4, cudaMemcpyDeviceToHost, st));
   QENG_CUDA(ctx, cudaStreamSynchronize(st));
   for (int b = 0; b < B; ++b) d->len[b] += steps;
+  if (d->vsplit) d->logits_partial = true;
   if (status != 0) {
     cudaMemset(ctx->status, 0, 4);
     return qeng_fail(ctx, QENG_ERR_DEVICE_STATUS, "decoder_decode: a kernel reported status %d (1 = page id outside the pool, 2 = position outside the cache, 3 = token id outside the vocabulary)", status);
@@ -692,6 +788,17 @@ int32_t qeng_decoder_logits(qeng_ctx* ctx, qeng_decoder* d, float* out) {
   if (!ctx || !d || !out) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_logits: null argument");
   if (!d->have_logits) return qeng_fail(ctx, QENG_ERR_STATE, "decoder_logits: no logits yet");
   QENG_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (d->logits_partial) {
+    // sharded LM head: zero the other ranks' columns and sum over the ranks (every rank must make
+    // this call); the bootstrap of the next decode call keeps using the token already picked
+    const int V = d->cfg.vocab, B = d->batch;
+    if (d->v0 > 0) QENG_CUDA(ctx, cudaMemset2DAsync(d->logits, (size_t)V * 4, 0, (size_t)d->v0 * 4, B, d->stream));
+    if (d->v0 + d->vloc < V)
+      QENG_CUDA(ctx, cudaMemset2DAsync(d->logits + d->v0 + d->vloc, (size_t)V * 4, 0, (size_t)(V - d->v0 - d->vloc) * 4, B, d->stream));
+    int32_t rc = qeng_tp_all_reduce_internal(ctx, d->logits, (int64_t)B * V, d->stream);
+    if (rc != QENG_OK) return rc;
+    d->logits_partial = false;
+  }
   QENG_CUDA(ctx, cudaStreamSynchronize(d->stream));
   QENG_CUDA(ctx, cudaMemcpy(out, d->logits, (size_t)d->batch * d->cfg.vocab * 4, cudaMemcpyDeviceToHost));
   return QENG_OK;

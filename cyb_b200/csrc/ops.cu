@@ -94,6 +94,8 @@ __global__ void __launch_bounds__(256) lm_head_kernel(const qeng_lm_tail t, floa
   __shared__ int s_last;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int M = t.M, D = t.D, V = t.V;
+  const int v0 = t.v0, Vtot = t.Vtot > 0 ? t.Vtot : V;
+  const size_t ldl = t.Vtot > 0 ? (size_t)t.ldl : (size_t)V;
   for (int m = 0; m < M; ++m) {
     float rs = 1.f;
     if (t.gamma != nullptr) {
@@ -157,12 +159,12 @@ __global__ void __launch_bounds__(256) lm_head_kernel(const qeng_lm_tail t, floa
     for (int m = 0; m < kLmM; ++m) {
       if (m < M) {
         const float tot = warp_sum(acc[m]);
-        if (lane == 0) t.logits[(size_t)m * V + v] = tot;
-        if (better(tot, v, bestv[m], besti[m])) { bestv[m] = tot; besti[m] = v; }
+        if (lane == 0) t.logits[(size_t)m * ldl + v0 + v] = tot;
+        if (better(tot, v0 + v, bestv[m], besti[m])) { bestv[m] = tot; besti[m] = v0 + v; }
       }
     }
   }
-  if (t.next == nullptr) return;
+  if (t.next == nullptr && t.pairs == nullptr) return;
 
   // ---- greedy finalisation ---------------------------------------------------------------
   if (lane == 0)
@@ -203,7 +205,12 @@ __global__ void __launch_bounds__(256) lm_head_kernel(const qeng_lm_tail t, floa
     if (tid == 0) {
       for (int w = 1; w < 8; ++w)
         if (better(wv[w][0], wi[w][0], bv, bi)) { bv = wv[w][0]; bi = wi[w][0]; }
-      if ((unsigned)bi >= (unsigned)V) { bi = 0; atomicExch(status, 3); }  // only if every logit was NaN
+      if (t.pairs != nullptr) {  // a vocabulary shard: the ranks' (max, index) pairs meet in a later kernel
+        t.pairs[2 * (t.pair_slot + m)] = bv;
+        t.pairs[2 * (t.pair_slot + m) + 1] = (float)bi;  // exact: sharded vocabularies stay below 2^24
+        continue;
+      }
+      if ((unsigned)bi >= (unsigned)Vtot) { bi = 0; atomicExch(status, 3); }  // only if every logit was NaN
       tok[m] = bi;
       t.next[m] = bi;
       const int st = *t.step;
@@ -214,9 +221,10 @@ __global__ void __launch_bounds__(256) lm_head_kernel(const qeng_lm_tail t, floa
   }
   __syncthreads();
   if (tid == 0) {
-    *t.step += 1;
+    if (t.pairs == nullptr) *t.step += 1;
     *counter = 0;  // ready for the next launch
   }
+  if (t.pairs != nullptr) return;
   for (int m = 0; m < M; ++m)
     for (int i = tid; i < D; i += 256)
       t.xout[(size_t)m * D + i] = __uint_as_float((uint32_t)t.emb[(size_t)tok[m] * D + i] << 16);

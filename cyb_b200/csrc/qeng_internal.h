@@ -144,6 +144,11 @@ struct qeng_lm_tail {
   int32_t* lens = nullptr;          // [M] += 1
   int32_t* out_tokens = nullptr;    // out_tokens[(*step + 1) * M + m] = token
   int32_t* step = nullptr;          // += 1
+  // vocabulary shard (tensor parallelism): `table` holds rows [v0, v0 + V) of a Vtot-row head;
+  // logits row m starts at logits + m * ldl and this launch fills columns [v0, v0 + V)
+  int v0 = 0, Vtot = 0, ldl = 0;    // Vtot = 0 means unsharded (Vtot = ldl = V)
+  float* pairs = nullptr;           // instead of finalising: pairs[2 * (pair_slot + m)] = (max, index as f32)
+  int pair_slot = 0;
 };
 int32_t qeng_lm_head_fused(qeng_ctx* ctx, const qeng_lm_tail& t, cudaStream_t stream);
 

@@ -209,7 +209,10 @@ int32_t qeng_decoder_load_matrix(qeng_ctx* ctx, qeng_decoder* dec, int32_t layer
                                  const uint8_t* q, const uint16_t* s, int64_t N, int64_t K);
 /* RMSNorm gains of a layer (which = 0: before attention, 1: before FFN), HOST f32[d_model]. */
 int32_t qeng_decoder_load_norm(qeng_ctx* ctx, qeng_decoder* dec, int32_t layer, int32_t which, const float* gamma);
-/* Embedding table, LM head (bf16 bit patterns, HOST, [vocab,d_model]) and final norm gain. */
+/* Embedding table, LM head (bf16 bit patterns, HOST, [vocab,d_model]) and final norm gain.
+ * With tensor parallelism pass the FULL head: a rank keeps vocabulary rows
+ * [rank*vocab/world, (rank+1)*vocab/world) when vocab divides evenly (else the whole head), and
+ * a decode step exchanges one (max, index) pair per sequence and rank to pick the token. */
 int32_t qeng_decoder_load_head(qeng_ctx* ctx, qeng_decoder* dec, const uint16_t* emb, const uint16_t* lm_head,
                                const float* final_gamma);
 /* Forget all sequences (KV lengths to zero). */
@@ -221,7 +224,9 @@ int32_t qeng_decoder_prefill(qeng_ctx* ctx, qeng_decoder* dec, const int32_t* to
  * feeds the sampled token and computes the next logits.  Writes the sampled
  * tokens to HOST out_tokens [batch, steps].  Synchronous. */
 int32_t qeng_decoder_decode(qeng_ctx* ctx, qeng_decoder* dec, int32_t steps, int32_t* out_tokens);
-/* Copy the current logits [batch, vocab] (f32) to a HOST buffer. */
+/* Copy the current logits [batch, vocab] (f32) to a HOST buffer.  With a vocabulary-sharded LM
+ * head this is a collective call after a decode step (the columns are summed over the ranks):
+ * every rank must make it. */
 int32_t qeng_decoder_logits(qeng_ctx* ctx, qeng_decoder* dec, float* out);
 /* Teacher-forced single layer for parity checks: x_in DEVICE f32 [batch,d_model]
  * at positions pos (HOST int32[batch]) -> x_out DEVICE f32 [batch,d_model];
