@@ -7,7 +7,10 @@
 // index of an MMA may be permuted freely as long as both operands agree, which
 // lets every lane load contiguous 16-byte pieces), and keep an online softmax
 // (max, sum, out) per query head of the group.  Warps are merged in shared
-// memory, splits through a scratch buffer and a second small kernel.
+// memory.  Splits: the eight CTAs of a thread-block cluster take the pages of a
+// sequence round-robin and merge through distributed shared memory (no scratch,
+// no atomics); caches beyond 16K tokens fall back to fixed page ranges merged
+// through a scratch buffer by the CTA that arrives last.
 //
 // HBM-bound: algorithmic bytes = sum_b len_b * kv_heads * 2 * 128 * 2.
 #include <math.h>
@@ -19,6 +22,22 @@ namespace {
 
 constexpr int kAW = 4;  // warps per CTA
 constexpr int kHD = 128;
+constexpr int kCS = 8;  // CTAs per cluster (splits of one sequence and kv head)
+
+__device__ __forceinline__ uint32_t cluster_map(const void* smem_ptr, uint32_t cta_rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"((uint32_t)__cvta_generic_to_shared(smem_ptr)), "r"(cta_rank));
+  return r;
+}
+__device__ __forceinline__ float ld_cluster(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+// hardware barrier over all threads of the cluster (every thread of every CTA executes it)
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
 
 struct AttnParams {
   const __half* pool;
@@ -53,20 +72,30 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-__global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnParams p) {
+template <bool kCl>
+__device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
   // the output projection that follows may start streaming its weights as CTAs of this kernel retire
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   const int s = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  // Pages of this warp: first, first + stride, ... below p1.  In a cluster the CTAs interleave the
+  // pages of the sequence (page = CTA rank + 8 * (warp + 4 i)), whatever its length, so the page
+  // ids can be fetched before the length is known; otherwise a CTA owns pages [p0, p0 + pps).
+  const int p0 = kCl ? s + kCS * warp : s * p.pps + warp;
+  const int pstride = kCl ? kCS * kAW : kAW;
+  int my_pid = -1;
+  if (kCl) {  // lane i holds the id of the warp's i-th page (caches up to 8 * 4 * 32 pages)
+    const int pg = p0 + lane * pstride;
+    if (pg < p.max_pages) my_pid = p.table[(size_t)b * p.max_pages + pg];
+  }
   const int len = p.lens[b];
   const int npages = min((len + 15) >> 4, p.max_pages);
-  const int p0 = s * p.pps;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  if (p0 >= npages) {
+  if (!kCl && s * p.pps >= npages) {
     if (p.counters != nullptr && s == 0)  // empty sequence: nobody else writes its output
       for (int hh = 0; hh < p.grp; ++hh) p.out[((size_t)b * p.Hq + (size_t)h * p.grp + hh) * kHD + tid] = 0.f;
     return;
   }
-  const int p1 = min(npages, p0 + p.pps);
+  const int p1 = kCl ? npages : min(npages, s * p.pps + p.pps);
 
   __shared__ float sm_o[kAW][8][kHD];
   __shared__ float sm_m[kAW][8], sm_l[kAW][8];
@@ -92,13 +121,12 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnParams 
   // tensor cores work on the current one.
   // all page ids of this warp are fetched up front (lane i holds the id of the warp's i-th page), so a
   // tile load is one memory round trip, not a table lookup followed by a dependent load
-  int my_pid = -1;
-  {
-    const int pg = p0 + warp + lane * kAW;  // at most 64 pages per split: 16 per warp
+  if (!kCl) {
+    const int pg = p0 + lane * pstride;  // at most 64 pages per split: 16 per warp
     if (pg < p1) my_pid = p.table[(size_t)b * p.max_pages + pg];
   }
   auto load_tile = [&](int pg, uint4 (&kq)[2][4], uint4 (&vv)[4][2]) -> bool {
-    const int pid = __shfl_sync(0xffffffffu, my_pid, (pg - p0 - warp) / kAW);
+    const int pid = __shfl_sync(0xffffffffu, my_pid, (pg - p0) / pstride);
     if ((unsigned)pid >= (unsigned)p.pages) {  // malformed page table: record and skip
       if (lane == 0) atomicExch(p.status, 1);
       return false;
@@ -188,15 +216,15 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnParams 
   };
   {
     uint4 kqA[2][4], vvA[4][2], kqB[2][4], vvB[4][2];
-    int pg = p0 + warp;
+    int pg = p0;
     bool okA = false, okB = false;
     if (pg < p1) okA = load_tile(pg, kqA, vvA);
     while (pg < p1) {
-      const int pgn = pg + kAW;
+      const int pgn = pg + pstride;
       if (pgn < p1) okB = load_tile(pgn, kqB, vvB);
       if (okA) compute_tile(pg, kqA, vvA);
       if (pgn >= p1) break;
-      const int pgnn = pgn + kAW;
+      const int pgnn = pgn + pstride;
       if (pgnn < p1) okA = load_tile(pgnn, kqA, vvA);
       if (okB) compute_tile(pgn, kqB, vvB);
       pg = pgnn;
@@ -219,8 +247,9 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnParams 
     }
   }
   __syncthreads();
-  const int ns = (npages + p.pps - 1) / p.pps;
-  const bool direct = p.counters != nullptr && ns == 1;  // a single split: no partials needed
+  const int ns = kCl ? kCS : (npages + p.pps - 1) / p.pps;
+  const bool direct = !kCl && p.counters != nullptr && ns == 1;  // a single split: no partials needed
+  __shared__ float c_o[8][kHD], c_m[8], c_l[8];  // this CTA's partial per query head (cluster merge)
   for (int hh = 0; hh < p.grp; ++hh) {
     float M = -INFINITY;
 #pragma unroll
@@ -228,11 +257,17 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnParams 
     float L = 0.f, O = 0.f;
 #pragma unroll
     for (int w = 0; w < kAW; ++w) {
-      const float f = exp2f(sm_m[w][hh] - M);
+      const float f = sm_m[w][hh] == -INFINITY ? 0.f : exp2f(sm_m[w][hh] - M);  // a warp without pages
       L += sm_l[w][hh] * f;
       O += sm_o[w][hh][tid] * f;
     }
-    if (direct) {
+    if (kCl) {
+      c_o[hh][tid] = O;
+      if (tid == 0) {
+        c_m[hh] = M;
+        c_l[hh] = L;
+      }
+    } else if (direct) {
       p.out[((size_t)b * p.Hq + (size_t)h * p.grp + hh) * kHD + tid] = O / L;
     } else {
       const size_t row = ((size_t)b * p.Hq + (size_t)h * p.grp + hh) * p.S + s;
@@ -242,6 +277,34 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnParams 
         __stcg(p.part_ml + row * 2 + 1, L);
       }
     }
+  }
+  if (kCl) {
+    // ---- cluster merge: CTA `s` owns dims [16 s, 16 s + 16) of every query head and reads the
+    // eight partials through distributed shared memory
+    cluster_sync();
+    if (tid < p.grp * 16) {
+      const int hh = tid >> 4, d = 16 * s + (tid & 15);
+      float mr[kCS], lr[kCS], orr[kCS];
+#pragma unroll
+      for (int r = 0; r < kCS; ++r) {
+        mr[r] = ld_cluster(cluster_map(&c_m[hh], r));
+        lr[r] = ld_cluster(cluster_map(&c_l[hh], r));
+        orr[r] = ld_cluster(cluster_map(&c_o[hh][d], r));
+      }
+      float M = -INFINITY;
+#pragma unroll
+      for (int r = 0; r < kCS; ++r) M = fmaxf(M, mr[r]);
+      float L = 0.f, O = 0.f;
+#pragma unroll
+      for (int r = 0; r < kCS; ++r) {
+        const float f = mr[r] == -INFINITY ? 0.f : exp2f(mr[r] - M);  // a CTA without pages
+        L = fmaf(lr[r], f, L);
+        O = fmaf(orr[r], f, O);
+      }
+      p.out[((size_t)b * p.Hq + (size_t)h * p.grp + hh) * kHD + d] = L > 0.f ? O / L : 0.f;
+    }
+    cluster_sync();  // nobody leaves while a peer may still read its shared memory
+    return;
   }
   if (p.counters == nullptr || direct) return;
   // ---- the CTA that completes this (sequence, kv head) merges its splits (no waiting) ----
@@ -280,6 +343,12 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnParams 
   }
   __syncthreads();
   if (tid == 0) p.counters[b * p.Hkv + h] = 0;  // ready for the next call
+}
+
+__global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnParams p) { attn_decode_body<false>(p); }
+
+__global__ void __cluster_dims__(kCS, 1, 1) __launch_bounds__(kAW * 32) attn_decode_cluster_kernel(const AttnParams p) {
+  attn_decode_body<true>(p);
 }
 
 __global__ void __launch_bounds__(kHD) attn_combine_kernel(const AttnParams p) {
@@ -429,9 +498,20 @@ int32_t qeng_attn_decode(qeng_ctx* ctx, const qeng_kv_pool* pool, const uint16_t
   p.table = page_table; p.lens = lens; p.out = out; p.status = ctx->status;
   p.pages = (int)pool->pages; p.Hkv = (int)pool->kv_heads; p.Hq = (int)Hq; p.grp = (int)(Hq / pool->kv_heads);
   p.max_pages = (int)max_pages;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  static const bool no_cluster = getenv("QENG_ATTN_NO_CLUSTER") != nullptr;
+  // Short work (decode at small batch) is latency-bound: a cluster of 8 splits merged through distributed
+  // shared memory saves the scratch round trip.  Long caches at large batch are bandwidth-bound and run
+  // a little faster on the finer fixed splits below.
+  if (!no_cluster && max_pages <= kCS * kAW * 32 && B * pool->kv_heads * max_pages <= 16384) {
+    p.pps = 0; p.S = kCS; p.counters = nullptr; p.part_o = nullptr; p.part_ml = nullptr;
+    dim3 grid((unsigned)kCS, (unsigned)p.Hkv, (unsigned)B);
+    attn_decode_cluster_kernel<<<grid, kAW * 32, 0, (cudaStream_t)stream>>>(p);
+    QENG_LAUNCH_CHECK(ctx);
+    return QENG_OK;
+  }
   p.pps = pages_per_split(ctx, B, pool->kv_heads, max_pages);
   p.S = (int)((max_pages + p.pps - 1) / p.pps);
-  p.scale_log2 = scale * 1.4426950408889634f;
   int32_t rc = qeng_attn_reserve(ctx, B, Hq, pool->kv_heads, max_pages);
   if (rc != QENG_OK) return rc;
   p.counters = reinterpret_cast<int*>(ctx->attn_scratch);
