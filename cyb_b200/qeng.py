@@ -77,6 +77,7 @@ _sig("qeng_tp_all_reduce_f32", _i32, _vp, _vp, _i64, _vp)
 _sig("qeng_weight_pack_q4", _i32, _vp, _vp, _vp, _i64, _i64, C.POINTER(_vp))
 _sig("qeng_weight_unpack_q4", _i32, _vp, _vp, _vp, _vp)
 _sig("qeng_weight_dequant_f32", _i32, _vp, _vp, _vp, _vp)
+_sig("qeng_weight_quantize_q4", _i32, _vp, _vp, _i32, _i64, _i64, _i64, C.POINTER(_vp), _vp)
 _sig("qeng_weight_free", _i32, _vp, _vp)
 _sig("qeng_weight_set_next", _i32, _vp, _vp, _vp)
 _sig("qeng_weight_rows", _i64, _vp)
@@ -198,6 +199,16 @@ class Context:
             raise QengError(-2, "scale shape %s does not match codes %s" % (s.shape, q.shape))
         h = _vp()
         self.check(_lib.qeng_weight_pack_q4(self.h, _np_ptr(q), _np_ptr(s), n, k, C.byref(h)))
+        return Weight(self, h)
+
+    def quantize_q4(self, w):
+        """Quantise a CUDA matrix [N,K] (float32 / float16 / bfloat16) into a packed weight on the device."""
+        import torch
+        dt = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}[w.dtype]
+        assert w.is_cuda and w.dim() == 2 and w.stride(1) == 1
+        h = _vp()
+        self.check(_lib.qeng_weight_quantize_q4(self.h, _dev_ptr(w), dt, w.shape[0], w.shape[1], w.stride(0),
+                                                C.byref(h), _cur_stream()))
         return Weight(self, h)
 
     # ---- ops (torch CUDA tensors in, torch CUDA tensors out) ---------------

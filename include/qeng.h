@@ -103,6 +103,14 @@ int32_t qeng_weight_pack_q4(qeng_ctx* ctx, const uint8_t* q, const uint16_t* s,
 int32_t qeng_weight_unpack_q4(qeng_ctx* ctx, const qeng_weight* w, uint8_t* q, uint16_t* s);
 /* Device-side dequantisation to f32 [N,K] (device pointer), w = (q-8)*s. */
 int32_t qeng_weight_dequant_f32(qeng_ctx* ctx, const qeng_weight* w, float* out, void* stream);
+/* Import-time quantiser on the device ("Q4 (4-bit, 3.5x compression)" at import,
+ * decide/pipeline.md:38-40,59): w_dev is a DEVICE matrix [N,K] of x_dtype (QENG_F32 / F16 / BF16)
+ * with leading dimension ld.  Per 32-block the element of largest magnitude (first on ties) / -8
+ * becomes the f16 scale d, and code = min(15, trunc(x / d + 8.5)) computed as x * (1/d) in f32.
+ * The result is written directly in the device layout, asynchronously on `stream`; w_dev may be
+ * released once the stream has passed this call.  K % 32 == 0, N % 16 == 0. */
+int32_t qeng_weight_quantize_q4(qeng_ctx* ctx, const void* w_dev, int32_t x_dtype, int64_t N, int64_t K, int64_t ld,
+                                qeng_weight** out, void* stream);
 int32_t qeng_weight_free(qeng_ctx* ctx, qeng_weight* w);
 int64_t qeng_weight_rows(const qeng_weight* w);
 int64_t qeng_weight_cols(const qeng_weight* w);

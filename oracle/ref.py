@@ -85,6 +85,26 @@ def dequant(q, s, dtype=np.float64):
     return w.astype(dtype) * np.repeat(s.astype(dtype), BLOCK, axis=1)
 
 
+def quantize_q4(w):
+    """Import-time quantiser, F32/F16/BF16 matrix -> codes + f16 scales ("Q4 (4-bit, 3.5x
+    compression)", decide/pipeline.md:38-40,59).  Per 32-block, the published Q4_0 rule: take
+    the element of largest magnitude (the first one on ties), d = that element / -8, the
+    scale is f16(d), and code = min(15, trunc(x * (1/d) + 8.5)), all in float32 (1/d = 0 when
+    d = 0).  Integer outputs: the device quantiser must match bit for bit."""
+    w = np.asarray(w, dtype=np.float32)
+    n, k = w.shape
+    assert k % BLOCK == 0
+    b = w.reshape(n, k // BLOCK, BLOCK)
+    idx = np.argmax(np.abs(b), axis=2)  # first occurrence of the maximum
+    mx = np.take_along_axis(b, idx[..., None], axis=2)[..., 0]
+    d = (mx / np.float32(-8.0)).astype(np.float32)
+    with np.errstate(divide="ignore"):
+        inv = np.where(d != 0, np.float32(1.0) / d, np.float32(0.0)).astype(np.float32)
+    y = (b * inv[..., None]).astype(np.float32) + np.float32(8.5)
+    q = np.minimum(15, y.astype(np.float32).astype(np.int32)).astype(np.uint8)
+    return q.reshape(n, k), d.astype(np.float16)
+
+
 def dequant_bf16(q, s):
     """Dequantize, then round each weight to bf16 (what the prefill path feeds
     its tensor-core contraction)."""

@@ -170,3 +170,39 @@ def test_tensor_parallel_shard_shapes(ctx, n, k):
     y4 = ctx.gemm_q4(w, _t(x4)).cpu().numpy()
     assert ref.err_inf(y4, ref.gemm_q4_fast(x4, q, s)) < 2e-6
     w.free()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("n,k", [(16, 32), (48, 160), (4096, 4096), (1376, 4096)])
+def test_device_quantizer_bit_exact(ctx, n, k, dtype):
+    """Import-time quantiser on the device against the oracle's: codes and scale bits identical, for
+    every input type, a padded (odd) block count included; then the weight is usable as any other."""
+    import torch
+    rng = ref.rng_of(n + k)
+    x = (rng.standard_normal((n, k)) * rng.uniform(1e-3, 3.0, (n, 1))).astype(np.float32)
+    x[0, :32] = 0.0
+    x[1, 5], x[1, 9] = -7.5, 7.5
+    xt = _t(x).to(getattr(torch, dtype))
+    want_q, want_s = ref.quantize_q4(xt.float().cpu().numpy())
+    w = ctx.quantize_q4(xt)
+    q, s = w.unpack()
+    assert np.array_equal(q, want_q)
+    assert np.array_equal(s.view(np.uint16), want_s.view(np.uint16))
+    a = ref.rng_of(5).standard_normal((1, k), dtype=np.float32)
+    y = ctx.gemm_q4(w, _t(a)).cpu().numpy()
+    assert ref.err_inf(y, ref.gemm_q4(a, want_q, want_s)) < TOL
+    w.free()
+
+
+def test_device_quantizer_strided_input_and_errors(ctx):
+    import torch
+    from cyb_b200 import qeng
+    x = torch.randn(32, 200, device="cuda")
+    view = x[:, :160]  # leading dimension 200
+    w = ctx.quantize_q4(view)
+    q, s = w.unpack()
+    want_q, want_s = ref.quantize_q4(view.cpu().numpy())
+    assert np.array_equal(q, want_q) and np.array_equal(s.view(np.uint16), want_s.view(np.uint16))
+    with pytest.raises(qeng.QengError) as e:
+        ctx.quantize_q4(x[:, :100])  # K % 32 != 0
+    assert e.value.code == -2

@@ -122,3 +122,42 @@ def test_c_decoder_matches_numpy_decoder(oracle_c):
         logits, nxt = dec.step(nxt, np.full(B, P + s, np.int32), table)
     assert np.array_equal(np.stack(toks, 1), g["dec_tokens"][:, :3])
     dec.close()
+
+
+def _quantizer_cases():
+    rng = ref.rng_of(31)
+    x = (rng.standard_normal((48, 160)) * rng.uniform(1e-3, 3.0, (48, 1))).astype(np.float32)
+    x[0, :32] = 0.0                     # an all-zero block: scale 0, every code 8
+    x[1, 5], x[1, 9] = -7.5, 7.5        # a tie in magnitude: the first element decides the sign of d
+    x[2, 32:64] = np.arange(-16, 16)    # the largest magnitude is negative: code 15 is reached
+    return x
+
+
+def test_quantizer_known_answers():
+    x = _quantizer_cases()
+    q, s = ref.quantize_q4(x)
+    assert q.dtype == np.uint8 and q.max() <= 15 and s.dtype == np.float16
+    assert np.all(q[0, :32] == 8) and s[0, 0] == 0
+    assert s[1, 0] == np.float16(7.5 / 8) and q[1, 5] == 0 and q[1, 9] == 15  # d = -7.5 / -8 > 0
+    assert s[2, 1] == np.float16(2.0) and q[2, 32] == 0 and q[2, 63] == 15
+    # the reconstruction error stays within half a step of the block's scale (one step at the clamped end)
+    err = np.abs(ref.dequant(q, s, np.float32) - x)
+    step = np.repeat(np.abs(s.astype(np.float32)), 32, axis=1)
+    assert np.all(err <= step * 1.001 + 1e-6)
+
+
+def test_quantizer_matches_the_gguf_package_if_present():
+    """Independent pin: the third-party `gguf` package implements the same published rule for the
+    type it calls Q4_0 (18-byte blocks: f16 scale, then low nibbles = elements 0..15, high nibbles
+    = elements 16..31).  Codes and scale bits must agree exactly; nibble ORDER is a layout matter."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    x = _quantizer_cases()
+    q, s = ref.quantize_q4(x)
+    n, k = x.shape
+    b = quants.quantize(x, gguf.GGMLQuantizationType.Q4_0).reshape(n, k // 32, 18)
+    d = b[..., :2].copy().view(np.float16)[..., 0]
+    codes = np.concatenate([b[..., 2:] & 15, b[..., 2:] >> 4], axis=-1).reshape(n, k)
+    assert np.array_equal(d.view(np.uint16), s.view(np.uint16))
+    assert np.array_equal(codes, q)
+    assert np.allclose(quants.dequantize(b.reshape(n, -1), gguf.GGMLQuantizationType.Q4_0), ref.dequant(q, s, np.float32))
