@@ -34,16 +34,21 @@ struct Layer {
   qeng_weight* wdown = nullptr;
   float* norm1 = nullptr;
   float* norm2 = nullptr;
+  float *qnorm = nullptr, *knorm = nullptr;  // optional per-head gains [128] (QK-norm)
   HostMat pend[7];  // host shards waiting for their fusion partners
 };
 
 // rows of q|k|v (f32, straight from the QKV matmul) -> rotated q as f16, rotated k and v
-// as f16 into the page pool at token index pos[row].
+// as f16 into the page pool at token index pos[row].  One warp per head; with per-head gains
+// (qg, kg: the "QK-norm" of the Qwen3 family, decide/model-lifecycle.md:173-176) every q and k
+// head is RMS-normalised over its 128 dims before the rotation.
 __global__ void __launch_bounds__(256) rope_append_kernel(const float* __restrict__ qkv, const float* __restrict__ cs,
                                                           const int32_t* __restrict__ pos,
                                                           const int32_t* __restrict__ table, int max_pages, int pages,
                                                           int Hq, int Hkv, int max_seq, __half* __restrict__ q16,
-                                                          __half* __restrict__ pool, int32_t* status) {
+                                                          __half* __restrict__ pool, int32_t* status,
+                                                          const float* __restrict__ qg, const float* __restrict__ kg,
+                                                          float eps) {
   const int row = blockIdx.x;
   const int ps = pos[row];
   if (ps < 0 || ps >= max_seq || (ps >> 4) >= max_pages) {
@@ -58,21 +63,44 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const float* __restric
   const int nq = Hq * kHD, nkv = Hkv * kHD;
   const float* src = qkv + (size_t)row * (nq + 2 * nkv);
   const float* cosr = cs + (size_t)ps * kHD;  // [64 cos | 64 sin]
-  // rotated heads: Hq query heads then Hkv key heads, 64 pairs each
-  for (int idx = threadIdx.x; idx < (Hq + Hkv) * 64; idx += blockDim.x) {
-    const int h = idx >> 6, i = idx & 63;
-    const float c = cosr[i], s = cosr[64 + i];
-    // the q|k|v rows of a head are stored permuted: dim i sits at 16*((i&63)>>3) + (i&7) + 8*(i>>6)
-    const int pi = ((i >> 3) << 4) + (i & 7);
-    const float a = src[h * kHD + pi], b = src[h * kHD + pi + 8];
-    const __half lo = __float2half_rn(a * c - b * s), hi = __float2half_rn(b * c + a * s);
-    if (h < Hq) {
-      q16[(size_t)row * nq + h * kHD + i] = lo;
-      q16[(size_t)row * nq + h * kHD + i + 64] = hi;
-    } else {
-      __half* kd = pool + ((size_t)pid * Hkv + (h - Hq)) * (2 * kPage * kHD) + (ps & 15) * kHD;
-      kd[i] = lo;
-      kd[i + 64] = hi;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // rotated heads: Hq query heads then Hkv key heads; a lane owns the pairs (i, i+64), i = lane, lane+32
+  for (int h = warp; h < Hq + Hkv; h += 8) {
+    const float* gain = h < Hq ? qg : kg;
+    float a[2], b[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int i = lane + 32 * u;
+      // the q|k|v rows of a head are stored permuted: dim i sits at 16*((i&63)>>3) + (i&7) + 8*(i>>6)
+      const int pi = ((i >> 3) << 4) + (i & 7);
+      a[u] = src[h * kHD + pi];
+      b[u] = src[h * kHD + pi + 8];
+    }
+    if (gain != nullptr) {
+      float ss = a[0] * a[0] + b[0] * b[0] + a[1] * a[1] + b[1] * b[1];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float r = rsqrtf(ss / (float)kHD + eps);
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int i = lane + 32 * u;
+        a[u] = a[u] * r * gain[i];
+        b[u] = b[u] * r * gain[i + 64];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int i = lane + 32 * u;
+      const float c = cosr[i], s = cosr[64 + i];
+      const __half lo = __float2half_rn(a[u] * c - b[u] * s), hi = __float2half_rn(b[u] * c + a[u] * s);
+      if (h < Hq) {
+        q16[(size_t)row * nq + h * kHD + i] = lo;
+        q16[(size_t)row * nq + h * kHD + i + 64] = hi;
+      } else {
+        __half* kd = pool + ((size_t)pid * Hkv + (h - Hq)) * (2 * kPage * kHD) + (ps & 15) * kHD;
+        kd[i] = lo;
+        kd[i + 64] = hi;
+      }
     }
   }
   for (int idx = threadIdx.x; idx < nkv; idx += blockDim.x) {
@@ -288,7 +316,7 @@ int32_t run_layer_prefill(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, c
   if (rc == QENG_OK) rc = qeng_gemm_q4_prefill(ctx, L.wqkv, d->xnr, QENG_F32, rows, dm, d->qkv, d->nqkv, 0, st);
   if (rc != QENG_OK) return rc;
   rope_append_kernel<<<(unsigned)rows, 256, 0, st>>>(d->qkv, d->rope_cs, d->pos, table, d->max_pages, (int)d->pages,
-                                                     d->Hq, d->Hkv, d->cfg.max_seq, d->q16, pool, ctx->status);
+                                                     d->Hq, d->Hkv, d->cfg.max_seq, d->q16, pool, ctx->status, L.qnorm, L.knorm, d->cfg.rms_eps);
   QENG_LAUNCH_CHECK(ctx);
   d->view.pages = d->pages; d->view.kv_heads = d->Hkv; d->view.hd = kHD; d->view.data = pool;
   rc = qeng_attn_decode(ctx, &d->view, reinterpret_cast<const uint16_t*>(d->q16), table, d->max_pages, d->lens, rows,
@@ -324,7 +352,9 @@ int32_t run_layer(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, const int
   qeng_gemm_fuse f;
   f.norm_gamma = L.norm1; f.norm_eps = d->cfg.rms_eps; f.epilogue = QENG_EPI_STORE;
   int32_t rc;
-  if (qeng_gemm_q4_stream_fits(L.wqkv, 1, true)) {
+  if ((L.qnorm == nullptr) != (L.knorm == nullptr))
+    return qeng_fail(ctx, QENG_ERR_STATE, "decoder: layer %d has only one of the q / k head gains", l);
+  if (L.qnorm == nullptr && qeng_gemm_q4_stream_fits(L.wqkv, 1, true)) {
     // q|k|v projection with rotary embedding, f16 rounding and KV append in its epilogue
     qeng_qkv_epi E;
     E.pos = d->pos; E.table = table; E.cs = d->rope_cs; E.q16 = d->q16; E.pool = pool;
@@ -336,7 +366,7 @@ int32_t run_layer(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, const int
     rc = mm(ctx, d, L.wqkv, d->x, dm, rows, d->qkv, d->nqkv, f, st);
     if (rc != QENG_OK) return rc;
     rope_append_kernel<<<(unsigned)rows, 256, 0, st>>>(d->qkv, d->rope_cs, d->pos, table, d->max_pages, (int)d->pages,
-                                                       d->Hq, d->Hkv, d->cfg.max_seq, d->q16, pool, ctx->status);
+                                                       d->Hq, d->Hkv, d->cfg.max_seq, d->q16, pool, ctx->status, L.qnorm, L.knorm, d->cfg.rms_eps);
     QENG_LAUNCH_CHECK(ctx);
     d->launches++;
   }
@@ -535,6 +565,8 @@ int32_t qeng_decoder_free(qeng_ctx* ctx, qeng_decoder* d) {
     qeng_weight_free(ctx, L.wqkv); qeng_weight_free(ctx, L.wo); qeng_weight_free(ctx, L.wgu); qeng_weight_free(ctx, L.wdown);
     if (L.norm1) cudaFree(L.norm1);
     if (L.norm2) cudaFree(L.norm2);
+    if (L.qnorm) cudaFree(L.qnorm);
+    if (L.knorm) cudaFree(L.knorm);
   }
   void* bufs[] = {d->emb, d->lm_head, d->final_norm, d->rope_cs, d->pool, d->x, d->qkv, d->att, d->act, d->part, d->xnr, d->gu, d->q16,
                   d->pos, d->lens, d->table, d->xn, d->xlast, d->logits, d->next, d->out_tokens, d->step, d->dec_table, d->tp_pairs, d->tp_gath};
@@ -645,10 +677,14 @@ int32_t qeng_decoder_load_matrix(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, 
 
 int32_t qeng_decoder_load_norm(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, int32_t which, const float* gamma) {
   if (!ctx || !d || !gamma) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_load_norm: null argument");
-  if (layer < 0 || layer >= d->cfg.layers || which < 0 || which > 1) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_load_norm: bad layer/which");
-  float** dst = which == 0 ? &d->layers[layer].norm1 : &d->layers[layer].norm2;
-  if (!*dst) QENG_CUDA(ctx, cudaMalloc(dst, (size_t)d->cfg.d_model * 4));
-  QENG_CUDA(ctx, cudaMemcpy(*dst, gamma, (size_t)d->cfg.d_model * 4, cudaMemcpyHostToDevice));
+  if (layer < 0 || layer >= d->cfg.layers || which < 0 || which > 3) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_load_norm: bad layer/which");
+  QENG_CUDA(ctx, cudaSetDevice(ctx->device));
+  Layer& L = d->layers[layer];
+  float** dst = which == 0 ? &L.norm1 : which == 1 ? &L.norm2 : which == 2 ? &L.qnorm : &L.knorm;
+  const size_t n = which < 2 ? (size_t)d->cfg.d_model : (size_t)kHD;  // 2, 3: per-head gains of q and k
+  if (!*dst) QENG_CUDA(ctx, cudaMalloc(dst, n * 4));
+  QENG_CUDA(ctx, cudaMemcpy(*dst, gamma, n * 4, cudaMemcpyHostToDevice));
+  if (which >= 2 && d->graph) { cudaGraphExecDestroy(d->graph); d->graph = nullptr; }  // the step takes another path
   return QENG_OK;
 }
 

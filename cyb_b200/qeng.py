@@ -476,6 +476,9 @@ def load_decoder_weights(dec, W, cfg):
             dec.load_matrix(l, i, *lw[nm])
         dec.load_norm(l, 0, lw["norm1"])
         dec.load_norm(l, 1, lw["norm2"])
+        if "qnorm" in lw:  # optional per-head gains of q and k
+            dec.load_norm(l, 2, lw["qnorm"])
+            dec.load_norm(l, 3, lw["knorm"])
 
     def bits(x):
         return (np.ascontiguousarray(x, dtype=np.float32).view(np.uint32) >> 16).astype(np.uint16)

@@ -215,7 +215,10 @@ int32_t qeng_decoder_free(qeng_ctx* ctx, qeng_decoder* dec);
  * (unsharded) matrix [N,K]; the decoder keeps this rank's shard only. */
 int32_t qeng_decoder_load_matrix(qeng_ctx* ctx, qeng_decoder* dec, int32_t layer, int32_t which,
                                  const uint8_t* q, const uint16_t* s, int64_t N, int64_t K);
-/* RMSNorm gains of a layer (which = 0: before attention, 1: before FFN), HOST f32[d_model]. */
+/* RMSNorm gains of a layer (which = 0: before attention, 1: before FFN), HOST f32[d_model].
+ * which = 2 / 3: optional per-head gains of q / k, HOST f32[head_dim] ("QK-norm", named as a
+ * blocker for the catalog's Qwen3 models in decide/model-lifecycle.md:173-176): every q and k head
+ * is RMS-normalised over its head_dim values before the rotary embedding; load both or neither. */
 int32_t qeng_decoder_load_norm(qeng_ctx* ctx, qeng_decoder* dec, int32_t layer, int32_t which, const float* gamma);
 /* Embedding table, LM head (bf16 bit patterns, HOST, [vocab,d_model]) and final norm gain.
  * With tensor parallelism pass the FULL head: a rank keeps vocabulary rows

@@ -295,6 +295,9 @@ class Decoder:
         qp = self.mm(n1, *lw["wq"]).reshape(B, T, cfg.heads, cfg.hd)
         kp = self.mm(n1, *lw["wk"]).reshape(B, T, cfg.kv_heads, cfg.hd)
         vp = self.mm(n1, *lw["wv"]).reshape(B, T, cfg.kv_heads, cfg.hd)
+        if "qnorm" in lw:  # per-head RMS norm of q and k before the rotation (Qwen3 family)
+            qp = rmsnorm(qp, lw["qnorm"], cfg.eps)
+            kp = rmsnorm(kp, lw["knorm"], cfg.eps)
         qr = f16_round(rope(qp, pos, cfg.hd, cfg.rope_base))
         kr = f16_round(rope(kp, pos, cfg.hd, cfg.rope_base))
         vr = f16_round(vp)

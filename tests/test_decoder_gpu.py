@@ -120,3 +120,54 @@ def test_full_size_layer_teacher_forced(ctx):
     assert e1 < 5e-4, e1
     ctx.device_status()
     dec.free()
+
+
+def test_qk_norm_layers_and_greedy_decode(ctx):
+    """Per-head RMS norm of q and k before the rotation (the Qwen3-family delta): teacher-forced
+    layers and free-running greedy tokens against the float64 teacher with the same gains."""
+    import torch
+    from cyb_b200 import qeng
+    cfg = ref.DecoderConfig(**CFG)
+    W = ref.make_decoder_weights(cfg, seed=5)
+    rng = ref.rng_of(91)
+    for lw in W["layers"]:
+        lw["qnorm"] = rng.uniform(0.5, 1.5, cfg.hd).astype(np.float32)
+        lw["knorm"] = rng.uniform(0.5, 1.5, cfg.hd).astype(np.float32)
+    dec = ctx.decoder(layers=cfg.layers, d_model=cfg.d, ffn=cfg.ffn, heads=cfg.heads, kv_heads=cfg.kv_heads,
+                      vocab=cfg.vocab, max_batch=2, max_seq=64)
+    qeng.load_decoder_weights(dec, W, cfg)
+    teacher = ref.Decoder(cfg, W)
+    teacher.reset(1)
+    T = 9
+    x = rng.standard_normal((1, T, cfg.d), dtype=np.float32) * 3
+    for l in range(cfg.layers):
+        want = teacher.layer(l, x.astype(np.float64), np.arange(T)[None])
+        got = dec.layer(l, torch.from_numpy(x[0]).cuda(), np.arange(T)).cpu().numpy()
+        assert ref.err_inf(got, want[0]) < 5e-5
+    # the gains matter: without them the same input gives another result
+    plain = ref.Decoder(cfg, {**W, "layers": [{k: v for k, v in lw.items() if k not in ("qnorm", "knorm")} for lw in W["layers"]]})
+    plain.reset(1)
+    assert ref.err_inf(plain.layer(0, x.astype(np.float64), np.arange(T)[None])[0], teacher_layer0(cfg, W, x, T)) > 1e-3
+    prompt = GOLD["dec_prompt"]
+    dec.reset(prompt.shape[0])
+    dec.prefill(prompt)
+    toks = dec.decode(6)
+    want, logs = ref.Decoder(cfg, W).generate(prompt, 6)
+    assert np.array_equal(toks, want)
+    # only one of the two gains is a state error
+    dec2 = ctx.decoder(layers=cfg.layers, d_model=cfg.d, ffn=cfg.ffn, heads=cfg.heads, kv_heads=cfg.kv_heads,
+                       vocab=cfg.vocab, max_batch=1, max_seq=64)
+    W2 = ref.make_decoder_weights(cfg, seed=5)
+    qeng.load_decoder_weights(dec2, W2, cfg)
+    dec2.load_norm(0, 2, np.ones(cfg.hd, np.float32))
+    with pytest.raises(qeng.QengError) as e:
+        dec2.layer(0, torch.zeros(1, cfg.d, device="cuda"), np.array([0]))
+    assert e.value.code == -8
+    dec.free()
+    dec2.free()
+
+
+def teacher_layer0(cfg, W, x, T):
+    t = ref.Decoder(cfg, W)
+    t.reset(1)
+    return t.layer(0, x.astype(np.float64), np.arange(T)[None])[0]

@@ -49,10 +49,20 @@ def _rank_main(rank, world, port, out):
     n2 = ref.rmsnorm(h, lw["norm2"], cfg.eps)
     act = ref.swiglu(ref.gemm_q4(n2, *sh["wgate"]), ref.gemm_q4(n2, *sh["wup"]))
     y = h + allreduce(ref.gemm_q4(act, *sh["wdown"]))
+    # LM head split by vocabulary rows: every rank contributes its (max, global index) pair in its own
+    # slot of a zeroed vector; the all-reduce (a sum with zeros) is the gather; every rank picks the token
+    v0, v1 = tp.vocab_shard(cfg.vocab, rank, world)
+    xn = ref.rmsnorm(y[-1:], W["final_norm"], cfg.eps)
+    logits = xn @ W["lm_head"][v0:v1].astype(np.float64).T
+    pairs = np.zeros((world, 1, 2), np.float32)
+    pairs[rank, 0] = (np.float32(logits[0].max()), np.float32(v0 + int(logits[0].argmax())))
+    token = tp.pick_token(allreduce(pairs))[0]
     if rank == 0:
         teacher = ref.Decoder(cfg, W)
         teacher.reset(1)
         want = teacher.layer(0, x, pos)[0]
+        full = ref.rmsnorm(want[-1:], W["final_norm"], cfg.eps) @ W["lm_head"].astype(np.float64).T
+        assert token == int(full[0].argmax()), (token, int(full[0].argmax()))
         out.put(float(np.abs(y - want).max() / np.abs(want).max()))
     dist.barrier()
     dist.destroy_process_group()
@@ -82,3 +92,15 @@ def test_shard_bounds_cover_and_reject():
         assert cols[0][2] == 0 and cols[-1][3] == 11008 and all(c[2] % 32 == 0 for c in cols)
     with pytest.raises(ValueError):
         tp.shard_bounds("wdown", 4096, 11008, 0, 16)  # 688 is not a whole number of 32-blocks
+
+
+def test_vocab_shard_and_token_pick():
+    from cyb_b200 import tp
+    for world in (2, 4, 8):
+        b = [tp.vocab_shard(32000, r, world) for r in range(world)]
+        assert b[0][0] == 0 and b[-1][1] == 32000 and all(x[1] == y[0] for x, y in zip(b, b[1:]))
+    assert tp.vocab_shard(32001, 1, 2) == (0, 32001)   # does not divide: replicated
+    assert tp.vocab_shard(32000, 0, 1) == (0, 32000)
+    # ties go to the lowest global index, whichever rank holds it
+    pairs = np.array([[[1.5, 7.0]], [[2.5, 16003.0]], [[2.5, 9001.0]], [[-1.0, 30000.0]]], np.float32)
+    assert tp.pick_token(pairs) == [9001]
