@@ -224,6 +224,17 @@ int32_t qeng_tp_p2p_open(qeng_ctx* ctx, const uint8_t* handles) {
   return QENG_OK;
 }
 
+int32_t qeng_tp_p2p_reset(qeng_ctx* ctx) {
+  if (!ctx) return QENG_ERR_ARG;
+  if (!ctx->p2p_local) return qeng_fail(ctx, QENG_ERR_STATE, "tp_p2p_reset: no inbox (tp_p2p_handle first)");
+  QENG_CUDA(ctx, cudaSetDevice(ctx->device));
+  QENG_CUDA(ctx, cudaDeviceSynchronize());
+  const size_t inbox = (size_t)2 * ctx->tp_world * kP2pMaxElems * sizeof(uint2);
+  QENG_CUDA(ctx, cudaMemset(ctx->p2p_local, 0, inbox + 256));  // tags and the call counter start over
+  QENG_CUDA(ctx, cudaMemset(ctx->status, 0, 4));
+  return QENG_OK;
+}
+
 __global__ void tp_add_kernel(float* __restrict__ x, const float* __restrict__ p, int64_t n) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) x[i] += p[i];

@@ -72,6 +72,7 @@ _sig("qeng_tp_unique_id", _i32, _vp)
 _sig("qeng_tp_init", _i32, _vp, _i32, _i32, _vp)
 _sig("qeng_tp_p2p_handle", _i32, _vp, _vp)
 _sig("qeng_tp_p2p_open", _i32, _vp, _vp)
+_sig("qeng_tp_p2p_reset", _i32, _vp)
 _sig("qeng_tp_all_reduce_add_f32", _i32, _vp, _vp, _vp, _i64, _vp)
 _sig("qeng_tp_all_reduce_f32", _i32, _vp, _vp, _i64, _vp)
 _sig("qeng_weight_pack_q4", _i32, _vp, _vp, _vp, _i64, _i64, C.POINTER(_vp))
@@ -177,6 +178,10 @@ class Context:
             parts = allgather(bytes(hb))
             allb = (C.c_uint8 * (64 * world)).from_buffer_copy(b"".join(parts))
             self.check(_lib.qeng_tp_p2p_open(self.h, allb))
+
+    def tp_p2p_reset(self):
+        """After a failed collective: clear this rank's inbox, call counter and status (all ranks, then a host barrier)."""
+        self.check(_lib.qeng_tp_p2p_reset(self.h))
 
     def all_reduce_add_(self, dst, part):
         self.check(_lib.qeng_tp_all_reduce_add_f32(self.h, _dev_ptr(dst), _dev_ptr(part), part.numel(), _cur_stream()))

@@ -83,6 +83,11 @@ int32_t qeng_tp_init(qeng_ctx* ctx, int32_t rank, int32_t world, const uint8_t* 
  * bytes (rank order) and gives them to qeng_tp_p2p_open on every rank. */
 int32_t qeng_tp_p2p_handle(qeng_ctx* ctx, uint8_t* out64);
 int32_t qeng_tp_p2p_open(qeng_ctx* ctx, const uint8_t* handles);
+/* Recovery after a peer failed to join (device status 5): the ranks' call counters no longer
+ * agree.  With no collective in flight anywhere, every surviving rank calls this (it clears its
+ * own inbox, call counter and status word), the host program makes sure all have returned (a
+ * barrier on its own channel), and the one-shot all-reduce works again. */
+int32_t qeng_tp_p2p_reset(qeng_ctx* ctx);
 /* dst[n] += sum over ranks of part[n] (f32, device): the collective after a row-split projection
  * fused with the residual add.  Uses the one-shot peer-memory kernel when the peers are mapped
  * and n <= 65536 (n % 4 == 0), else NCCL followed by an add. */

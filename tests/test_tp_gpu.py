@@ -121,7 +121,20 @@ def _lonely_rank_main(rank, world, port, out):
         w = ctx.pack_q4(q, s)
         y = ctx.gemm_q4(w, torch.from_numpy(x).cuda()).cpu().numpy()
         res = res + (ref.err_inf(y, ref.gemm_q4(x, q, s)) < 2e-6,) if isinstance(res, tuple) else res
-    dist.barrier()  # rank 1 only leaves after rank 0 is done, with nothing in flight
+    dist.barrier()  # rank 0 is done, nothing is in flight
+    # recovery: the call counters disagree now; both ranks clear their inboxes, meet on the host,
+    # and the next all-reduce (joined by both) must work
+    ctx.tp_p2p_reset()
+    dist.barrier()
+    dst = torch.full((4096,), 10.0, device="cuda")
+    part = torch.full((4096,), float(rank + 1), device="cuda")
+    ctx.all_reduce_add_(dst, part)
+    torch.cuda.synchronize()
+    ctx.device_status()
+    ok = bool((dst == 13.0).all())
+    if rank == 0:
+        res = res + (ok,) if isinstance(res, tuple) else res
+    dist.barrier()  # nobody leaves with a collective in flight
     out.put((rank, res))
     dist.destroy_process_group()
 
@@ -141,4 +154,4 @@ def test_missing_peer_is_reported_not_hung(built_lib):
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    assert res[0] == (-7, True, True), res
+    assert res[0] == (-7, True, True, True), res
