@@ -22,7 +22,7 @@ namespace {
 
 constexpr int kAW = 4;  // warps per CTA
 constexpr int kHD = 128;
-constexpr int kCS = 8;  // CTAs per cluster (splits of one sequence and kv head)
+constexpr int kCS = 8;  // largest cluster: CTAs (splits) per sequence and kv head; the launch picks 1, 2, 4 or 8
 
 __device__ __forceinline__ uint32_t cluster_map(const void* smem_ptr, uint32_t cta_rank) {
   uint32_t r;
@@ -81,10 +81,11 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
   // Pages of this warp: first, first + stride, ... below p1.  In a cluster the CTAs interleave the
   // pages of the sequence (page = CTA rank + 8 * (warp + 4 i)), whatever its length, so the page
   // ids can be fetched before the length is known; otherwise a CTA owns pages [p0, p0 + pps).
-  const int p0 = kCl ? s + kCS * warp : s * p.pps + warp;
-  const int pstride = kCl ? kCS * kAW : kAW;
+  const int cs = p.S;  // cluster path: CTAs in the cluster (= gridDim.x)
+  const int p0 = kCl ? s + cs * warp : s * p.pps + warp;
+  const int pstride = kCl ? cs * kAW : kAW;
   int my_pid = -1;
-  if (kCl) {  // lane i holds the id of the warp's i-th page (caches up to 8 * 4 * 32 pages)
+  if (kCl) {  // lane i holds the id of the warp's i-th page (caches up to cs * 4 * 32 pages)
     const int pg = p0 + lane * pstride;
     if (pg < p.max_pages) my_pid = p.table[(size_t)b * p.max_pages + pg];
   }
@@ -126,7 +127,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
     if (pg < p1) my_pid = p.table[(size_t)b * p.max_pages + pg];
   }
   auto load_tile = [&](int pg, uint4 (&kq)[2][4], uint4 (&vv)[4][2]) -> bool {
-    const int pid = __shfl_sync(0xffffffffu, my_pid, (pg - p0) / pstride);
+    const int pid = __shfl_sync(0xffffffffu, my_pid, kCl ? ((pg - p0) / kAW) / cs : (pg - p0) / kAW);
     if ((unsigned)pid >= (unsigned)p.pages) {  // malformed page table: record and skip
       if (lane == 0) atomicExch(p.status, 1);
       return false;
@@ -247,7 +248,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
     }
   }
   __syncthreads();
-  const int ns = kCl ? kCS : (npages + p.pps - 1) / p.pps;
+  const int ns = kCl ? cs : (npages + p.pps - 1) / p.pps;
   const bool direct = !kCl && p.counters != nullptr && ns == 1;  // a single split: no partials needed
   __shared__ float c_o[8][kHD], c_m[8], c_l[8];  // this CTA's partial per query head (cluster merge)
   for (int hh = 0; hh < p.grp; ++hh) {
@@ -279,17 +280,23 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
     }
   }
   if (kCl) {
-    // ---- cluster merge: CTA `s` owns dims [16 s, 16 s + 16) of every query head and reads the
-    // eight partials through distributed shared memory
-    cluster_sync();
-    if (tid < p.grp * 16) {
-      const int hh = tid >> 4, d = 16 * s + (tid & 15);
+    // ---- cluster merge: CTA `s` owns 128 / cs dims of every query head and reads the partials of
+    // all CTAs of the cluster through distributed shared memory
+    if (cs > 1) cluster_sync();
+    else __syncthreads();
+    const int dper = kHD / cs;
+    for (int e = tid; e < p.grp * dper; e += kAW * 32) {
+      const int hh = e / dper, d = s * dper + e % dper;
       float mr[kCS], lr[kCS], orr[kCS];
 #pragma unroll
       for (int r = 0; r < kCS; ++r) {
-        mr[r] = ld_cluster(cluster_map(&c_m[hh], r));
-        lr[r] = ld_cluster(cluster_map(&c_l[hh], r));
-        orr[r] = ld_cluster(cluster_map(&c_o[hh][d], r));
+        mr[r] = -INFINITY;
+        lr[r] = orr[r] = 0.f;
+        if (r < cs) {
+          mr[r] = ld_cluster(cluster_map(&c_m[hh], r));
+          lr[r] = ld_cluster(cluster_map(&c_l[hh], r));
+          orr[r] = ld_cluster(cluster_map(&c_o[hh][d], r));
+        }
       }
       float M = -INFINITY;
 #pragma unroll
@@ -303,7 +310,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
       }
       p.out[((size_t)b * p.Hq + (size_t)h * p.grp + hh) * kHD + d] = L > 0.f ? O / L : 0.f;
     }
-    cluster_sync();  // nobody leaves while a peer may still read its shared memory
+    if (cs > 1) cluster_sync();  // nobody leaves while a peer may still read its shared memory
     return;
   }
   if (p.counters == nullptr || direct) return;
@@ -347,7 +354,8 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
 
 __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnParams p) { attn_decode_body<false>(p); }
 
-__global__ void __cluster_dims__(kCS, 1, 1) __launch_bounds__(kAW * 32) attn_decode_cluster_kernel(const AttnParams p) {
+// launched with a cluster dimension of (p.S, 1, 1) = (gridDim.x, 1, 1)
+__global__ void __launch_bounds__(kAW * 32) attn_decode_cluster_kernel(const AttnParams p) {
   attn_decode_body<true>(p);
 }
 
@@ -500,14 +508,27 @@ int32_t qeng_attn_decode(qeng_ctx* ctx, const qeng_kv_pool* pool, const uint16_t
   p.max_pages = (int)max_pages;
   p.scale_log2 = scale * 1.4426950408889634f;
   static const bool no_cluster = getenv("QENG_ATTN_NO_CLUSTER") != nullptr;
-  // Short work (decode at small batch) is latency-bound: a cluster of 8 splits merged through distributed
-  // shared memory saves the scratch round trip.  Long caches at large batch are bandwidth-bound and run
-  // a little faster on the finer fixed splits below.
-  if (!no_cluster && max_pages <= kCS * kAW * 32 && B * pool->kv_heads * max_pages <= 16384) {
-    p.pps = 0; p.S = kCS; p.counters = nullptr; p.part_o = nullptr; p.part_ml = nullptr;
-    dim3 grid((unsigned)kCS, (unsigned)p.Hkv, (unsigned)B);
-    attn_decode_cluster_kernel<<<grid, kAW * 32, 0, (cudaStream_t)stream>>>(p);
-    QENG_LAUNCH_CHECK(ctx);
+  // Cluster path: 1, 2, 4 or 8 CTAs per (sequence, kv head), as many as keep the grid within about one
+  // wave (two CTAs per SM), merged through distributed shared memory.  A lane holds one page id per
+  // tile of its warp, which caps the cache at cs * 4 * 32 pages; beyond that the fixed splits below.
+  int cs = kCS;
+  while (cs > 1 && B * pool->kv_heads * cs > 2 * (int64_t)ctx->sm_count) cs >>= 1;
+  while (cs < kCS && max_pages > cs * kAW * 32) cs <<= 1;
+  // (long caches at large batch are bandwidth-bound and measured a little faster on the fixed splits)
+  if (!no_cluster && max_pages <= cs * kAW * 32 && B * pool->kv_heads * max_pages <= 16384) {
+    p.pps = 0; p.S = cs; p.counters = nullptr; p.part_o = nullptr; p.part_ml = nullptr;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)cs, (unsigned)p.Hkv, (unsigned)B);
+    cfg.blockDim = dim3(kAW * 32);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cs;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    QENG_CUDA(ctx, cudaLaunchKernelEx(&cfg, attn_decode_cluster_kernel, p));
     return QENG_OK;
   }
   p.pps = pages_per_split(ctx, B, pool->kv_heads, max_pages);

@@ -293,11 +293,12 @@ class Context:
         self.check(_lib.qeng_kv_append(self.h, pool.h, _dev_ptr(k), _dev_ptr(v), _dev_ptr(table), table.shape[1],
                                        _dev_ptr(pos), pos.numel(), _cur_stream()))
 
-    def attn_decode(self, pool, q, table, lens, scale=None):
+    def attn_decode(self, pool, q, table, lens, scale=None, out=None):
         import torch
         b, hq, hd = q.shape
         assert q.dtype == torch.float16 and q.is_contiguous()
-        out = torch.empty((b, hq, hd), dtype=torch.float32, device=q.device)
+        if out is None:
+            out = torch.empty((b, hq, hd), dtype=torch.float32, device=q.device)
         scale = float(hd) ** -0.5 if scale is None else scale
         self.check(_lib.qeng_attn_decode(self.h, pool.h, _dev_ptr(q), _dev_ptr(table), table.shape[1], _dev_ptr(lens),
                                          b, hq, scale, _dev_ptr(out), _cur_stream()))
