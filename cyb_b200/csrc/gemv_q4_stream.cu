@@ -219,25 +219,42 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
   const int ngroups = Kp / 8;
   const bool vec_ok = p.x_dtype == QENG_F32 && ((reinterpret_cast<uintptr_t>(p.x) | (uintptr_t)(p.ldx * 4)) & 15) == 0 &&
                       (p.gamma == nullptr || (reinterpret_cast<uintptr_t>(p.gamma) & 15) == 0) && (p.K & 7) == 0;
-  for (int m = 0; m < p.M; ++m) {
-    float v[kGroups][8];
-    float ss = 0.f, amax = 0.f;
+  // The raw values of row m + 1 are requested before row m is reduced and converted, so with
+  // several activation rows only the first one waits for memory.
+  auto load_row = [&](int m, float (&dst)[kGroups][8]) {
 #pragma unroll
     for (int j = 0; j < kGroups; ++j) {
       const int k0 = (tid + j * kCT) * 8;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[j][i] = 0.f;
+      for (int i = 0; i < 8; ++i) dst[j][i] = 0.f;
       if (k0 < p.K) {
         if (vec_ok) {
           const float4* xp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x) + (long long)m * p.ldx + k0);
           const float4 a = xp[0], b = xp[1];
-          v[j][0] = a.x; v[j][1] = a.y; v[j][2] = a.z; v[j][3] = a.w;
-          v[j][4] = b.x; v[j][5] = b.y; v[j][6] = b.z; v[j][7] = b.w;
+          dst[j][0] = a.x; dst[j][1] = a.y; dst[j][2] = a.z; dst[j][3] = a.w;
+          dst[j][4] = b.x; dst[j][5] = b.y; dst[j][6] = b.z; dst[j][7] = b.w;
         } else {
 #pragma unroll
           for (int i = 0; i < 8; ++i)
-            if (k0 + i < p.K) v[j][i] = act_f32(p.x, p.x_dtype, (long long)m * p.ldx + k0 + i);
+            if (k0 + i < p.K) dst[j][i] = act_f32(p.x, p.x_dtype, (long long)m * p.ldx + k0 + i);
         }
+      }
+    }
+  };
+  float nv[kGroups][8];
+  load_row(0, nv);
+  for (int m = 0; m < p.M; ++m) {
+    float v[kGroups][8];
+#pragma unroll
+    for (int j = 0; j < kGroups; ++j)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[j][i] = nv[j][i];
+    if (m + 1 < p.M) load_row(m + 1, nv);
+    float ss = 0.f, amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < kGroups; ++j) {
+      const int k0 = (tid + j * kCT) * 8;
+      if (k0 < p.K) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) ss = fmaf(v[j][i], v[j][i], ss);
         if (p.gamma != nullptr) {
