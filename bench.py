@@ -331,7 +331,7 @@ def main():
         achieved = algo / len(ws) / per_launch_s / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": (NCU_TRAFFIC_PER_ALGO_BYTE * algo / len(ws)) if NCU_TRAFFIC_PER_ALGO_BYTE else None,
-                "kernel": "gemv_q4_stream_kernel (M=1, f32 activations)", "bytes_per_launch": algo / len(ws),
+                "kernel": "gemv_q4_stream_kernel<NT=1,TG> (M=1, f32 activations)", "bytes_per_launch": algo / len(ws),
                 "us_per_launch": per_launch_s * 1e6,
                 "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback",
                 "step_frac": algo_bytes_per_step(m, B, ctx_mid, world) / (ms * 1e-3 / K) / 1e9 / peak}
