@@ -198,6 +198,7 @@ struct qeng_decoder {
   bool vsplit = false;
   int v0 = 0, vloc = 0;
   float *tp_pairs = nullptr, *tp_gath = nullptr;  // [world][max_batch][2]
+  bool next_ready = false;      // the last operation was a decode step: `next` holds the sampled token, `x` its embedding
   bool logits_partial = false;  // after a sharded decode step only columns [v0, v0 + vloc) are current
   cudaStream_t stream = nullptr;
   cudaStream_t own_stream = nullptr;
@@ -711,6 +712,7 @@ int32_t qeng_decoder_reset(qeng_ctx* ctx, qeng_decoder* d, int32_t batch) {
   d->len.assign(batch, 0);
   d->have_logits = false;
   d->logits_partial = false;
+  d->next_ready = false;
   return QENG_OK;
 }
 
@@ -755,6 +757,7 @@ int32_t qeng_decoder_prefill(qeng_ctx* ctx, qeng_decoder* d, const int32_t* toke
   if (e != cudaSuccess) return qeng_fail(ctx, QENG_ERR_CUDA, "decoder_prefill: %s", cudaGetErrorString(e));
   for (int b = 0; b < batch; ++b) d->len[b] += T;
   d->have_logits = true;
+  d->next_ready = false;
   return QENG_OK;
 }
 
@@ -773,13 +776,15 @@ int32_t qeng_decoder_decode(qeng_ctx* ctx, qeng_decoder* d, int32_t steps, int32
   }
   std::vector<int32_t> pos(B), lens(B);
   for (int b = 0; b < B; ++b) { pos[b] = d->len[b]; lens[b] = d->len[b] + 1; }
-  QENG_CUDA(ctx, cudaMemcpyAsync(d->pos, pos.data(), B * 4, cudaMemcpyHostToDevice, st));
-  QENG_CUDA(ctx, cudaMemcpyAsync(d->lens, lens.data(), B * 4, cudaMemcpyHostToDevice, st));
+  if (!d->next_ready) {  // right after a decode step the device copies are already one token on
+    QENG_CUDA(ctx, cudaMemcpyAsync(d->pos, pos.data(), B * 4, cudaMemcpyHostToDevice, st));
+    QENG_CUDA(ctx, cudaMemcpyAsync(d->lens, lens.data(), B * 4, cudaMemcpyHostToDevice, st));
+  }
   QENG_CUDA(ctx, cudaMemsetAsync(d->step, 0, 4, st));
-  {  // the token sampled from the logits at hand is fed first; after a sharded decode step it has
-     // been picked and embedded already (only this rank's logit columns are current then)
+  {  // the token sampled from the logits at hand is fed first; right after a decode step it has
+     // been picked and embedded already by that step's last kernel
     int32_t rc = QENG_OK;
-    if (!d->logits_partial) {
+    if (!d->next_ready) {
       rc = qeng_argmax(ctx, d->logits, B, d->cfg.vocab, d->next, st);
       if (rc == QENG_OK) rc = qeng_embed(ctx, d->emb, d->next, B, d->cfg.d_model, d->cfg.vocab, d->x, st);
     }
@@ -787,8 +792,9 @@ int32_t qeng_decoder_decode(qeng_ctx* ctx, qeng_decoder* d, int32_t steps, int32
     record_first_kernel<<<1, 32, 0, st>>>(d->next, d->out_tokens, B);
     QENG_LAUNCH_CHECK(ctx);
   }
-  QENG_CUDA(ctx, cudaStreamSynchronize(st));
+  d->next_ready = false;  // until this call's steps have run to the end
   if (!d->graph || d->graph_batch != B) {
+    QENG_CUDA(ctx, cudaStreamSynchronize(st));
     if (d->graph) { cudaGraphExecDestroy(d->graph); d->graph = nullptr; }
     cudaGraph_t g = nullptr;
     QENG_CUDA(ctx, cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
@@ -809,6 +815,7 @@ int32_t qeng_decoder_decode(qeng_ctx* ctx, qeng_decoder* d, int32_t steps, int32
   QENG_CUDA(ctx, cudaStreamSynchronize(st));
   for (int b = 0; b < B; ++b) d->len[b] += steps;
   if (d->vsplit) d->logits_partial = true;
+  d->next_ready = status == 0;
   if (status != 0) {
     cudaMemset(ctx->status, 0, 4);
     return qeng_fail(ctx, QENG_ERR_DEVICE_STATUS, "decoder_decode: a kernel reported status %d (1 = page id outside the pool, 2 = position outside the cache, 3 = token id outside the vocabulary)", status);
@@ -859,6 +866,7 @@ int32_t qeng_decoder_layer(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, const 
   QENG_CUDA(ctx, cudaMemcpyAsync(d->pos, pos, rows * 4, cudaMemcpyHostToDevice, st));
   QENG_CUDA(ctx, cudaMemcpyAsync(d->lens, lens.data(), rows * 4, cudaMemcpyHostToDevice, st));
   QENG_CUDA(ctx, cudaMemcpyAsync(d->table, table.data(), table.size() * 4, cudaMemcpyHostToDevice, st));
+  d->next_ready = false;  // the activation buffer is reused
   QENG_CUDA(ctx, cudaMemcpyAsync(d->x, x_in, (size_t)rows * d->cfg.d_model * 4, cudaMemcpyDeviceToDevice, st));
   rc = run_layer(ctx, d, layer, rows, d->table, st);
   if (rc != QENG_OK) return rc;
