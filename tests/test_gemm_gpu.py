@@ -206,3 +206,25 @@ def test_device_quantizer_strided_input_and_errors(ctx):
     with pytest.raises(qeng.QengError) as e:
         ctx.quantize_q4(x[:, :100])  # K % 32 != 0
     assert e.value.code == -2
+
+
+def test_next_matrix_hint_never_changes_results(ctx):
+    """qeng_weight_set_next is a pure performance hint (an L2 prefetch of the matrix used next):
+    outputs are bit-identical with, without, and after clearing it."""
+    rng = ref.rng_of(77)
+    q1, s1 = ref.make_q4(rng, 4096, 4096)
+    q2, s2 = ref.make_q4(rng, 1376, 4096)
+    w1, w2 = ctx.pack_q4(q1, s1), ctx.pack_q4(q2, s2)
+    x = _t(rng.standard_normal((1, 4096), dtype=np.float32))
+    base1, base2 = ctx.gemm_q4(w1, x).clone(), ctx.gemm_q4(w2, x).clone()
+    w1.set_next(w2)
+    w2.set_next(w1)
+    for _ in range(3):
+        assert bool((ctx.gemm_q4(w1, x) == base1).all())
+        assert bool((ctx.gemm_q4(w2, x) == base2).all())
+    w1.set_next(None)
+    w2.set_next(None)
+    assert bool((ctx.gemm_q4(w1, x) == base1).all())
+    ctx.device_status()
+    w1.free()
+    w2.free()
