@@ -58,6 +58,22 @@ def main():
     toks, logs = dec.generate(prompt, 6)
     out["dec_prompt"], out["dec_tokens"] = prompt, toks.astype(np.int32)
     out["dec_logits"] = np.stack(logs, 0)  # [steps, batch, vocab]
+    # import-time quantiser: zero block, a tie in magnitude, a negative extreme, ragged scales
+    rng = ref.rng_of(17)
+    xq = (rng.standard_normal((32, 96)) * rng.uniform(1e-3, 3.0, (32, 1))).astype(np.float32)
+    xq[0, :32] = 0.0
+    xq[1, 5], xq[1, 9] = -7.5, 7.5
+    xq[2, 32:64] = np.arange(-16, 16)
+    out["quant_x"] = xq
+    out["quant_q"], out["quant_s"] = ref.quantize_q4(xq)
+    # the same tiny decoder with per-head q / k gains (QK-norm): greedy tokens and first logits
+    rng = ref.rng_of(18)
+    gains = rng.uniform(0.5, 1.5, (cfg.layers, 2, cfg.hd)).astype(np.float32)
+    Wn = ref.make_decoder_weights(cfg, seed=5)
+    for l, lw in enumerate(Wn["layers"]):
+        lw["qnorm"], lw["knorm"] = gains[l, 0], gains[l, 1]
+    toks_n, logs_n = ref.Decoder(cfg, Wn).generate(prompt, 6)
+    out["qkn_gains"], out["qkn_tokens"], out["qkn_logits0"] = gains, toks_n.astype(np.int32), logs_n[0]
     np.savez_compressed(os.path.join(HERE, "golden.npz"), **out)
     print("wrote", os.path.join(HERE, "golden.npz"), sum(v.nbytes for v in out.values()), "bytes raw")
 

@@ -171,3 +171,20 @@ def teacher_layer0(cfg, W, x, T):
     t = ref.Decoder(cfg, W)
     t.reset(1)
     return t.layer(0, x.astype(np.float64), np.arange(T)[None])[0]
+
+
+def test_qk_norm_decode_matches_the_golden_fixture(ctx):
+    from cyb_b200 import qeng
+    cfg = ref.DecoderConfig(**CFG)
+    W = ref.make_decoder_weights(cfg, seed=5)
+    for l, lw in enumerate(W["layers"]):
+        lw["qnorm"], lw["knorm"] = GOLD["qkn_gains"][l, 0], GOLD["qkn_gains"][l, 1]
+    dec = ctx.decoder(layers=cfg.layers, d_model=cfg.d, ffn=cfg.ffn, heads=cfg.heads, kv_heads=cfg.kv_heads,
+                      vocab=cfg.vocab, max_batch=2, max_seq=64)
+    qeng.load_decoder_weights(dec, W, cfg)
+    prompt = GOLD["dec_prompt"]
+    dec.reset(prompt.shape[0])
+    dec.prefill(prompt)
+    assert ref.err_inf(dec.logits(), GOLD["qkn_logits0"]) < 2e-3
+    assert np.array_equal(dec.decode(GOLD["qkn_tokens"].shape[1]), GOLD["qkn_tokens"])
+    dec.free()

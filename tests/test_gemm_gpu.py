@@ -228,3 +228,11 @@ def test_next_matrix_hint_never_changes_results(ctx):
     ctx.device_status()
     w1.free()
     w2.free()
+
+
+def test_device_quantizer_matches_the_golden_fixture(ctx):
+    w = ctx.quantize_q4(_t(GOLD["quant_x"]))
+    q, s = w.unpack()
+    assert np.array_equal(q, GOLD["quant_q"])
+    assert np.array_equal(s.view(np.uint16), GOLD["quant_s"].view(np.uint16))
+    w.free()

@@ -100,6 +100,8 @@ def test_golden_fixtures_reproduce():
         assert ref.err_inf(y, g[name + "_y"]) < 1e-14
     assert ref.err_inf(ref.rmsnorm(g["rms_x"], g["rms_g"], 1e-5), g["rms_y"]) < 1e-14
     assert ref.err_inf(ref.rope(g["rope_x"], g["rope_pos"]), g["rope_y"]) < 1e-14
+    q, s = ref.quantize_q4(g["quant_x"])
+    assert np.array_equal(q, g["quant_q"]) and np.array_equal(s.view(np.uint16), g["quant_s"].view(np.uint16))
 
 
 def test_c_decoder_matches_numpy_decoder(oracle_c):
