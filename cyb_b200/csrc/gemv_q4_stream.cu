@@ -610,7 +610,10 @@ int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
   const int grid = p.ntiles < ctx->sm_count ? p.ntiles : ctx->sm_count;
   const int per_cta = (p.ntiles + grid - 1) / grid;
   int tg = per_cta >= 8 ? 4 : (per_cta >= 2 ? 2 : 1);
-  while (tg > 1 && f.nstages / tg < 2) tg >>= 1;  // every group keeps at least two ring slots
+  // every group keeps at least two ring slots, and no fewer than one row tile needs (K > 4096: a tile
+  // spans several stages, and a group whose ring is shorter than its tile stalls the producer)
+  const int spt = (p.nchunks + kSC - 1) / kSC;
+  while (tg > 1 && f.nstages / tg < (spt > 2 ? spt : 2)) tg >>= 1;
   static const int tg_env = [] { const char* e = getenv("QENG_STREAM_GROUPS"); return e ? atoi(e) : 0; }();
   if (tg_env == 1 || tg_env == 2 || tg_env == 4) tg = tg_env;
 #define QENG_STREAM_CASE(NT_)                                                   \
