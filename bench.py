@@ -1,7 +1,9 @@
 #!/usr/bin/env python
 """Headline benchmark: greedy decode tokens/s of a 7B-shaped 4-bit Llama-style
 decoder (32 layers, d 4096, FFN 11008, 32/8 heads, vocab 32000) on N B200s,
-and the HBM roofline of its dominant kernel, the 4-bit decode GEMV.
+the HBM roofline of its dominant kernel, and the kernel-level figures of the
+other configurations (single GEMV, decode-batch GEMM sweep, prefill GEMM,
+decode attention, LM head, batch-16 decode).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
 
@@ -19,6 +21,7 @@ import subprocess
 import sys
 import threading
 import time
+import zlib
 
 import numpy as np
 
@@ -29,10 +32,11 @@ if ROOT not in sys.path:
 MODEL = dict(layers=32, d=4096, ffn=11008, heads=32, kv_heads=8, hd=128, vocab=32000)
 PROMPT = 512
 METRIC = "decode tokens/s (7B 4-bit, 1/2/4/8 B200); quant GEMV HBM GB/s vs peak"
-# (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of one launch of the decode
-# matmul, from the ncu capture summarised in profiles/gemv_q4_stream_22016x4096_m1.md
-# (50.80 MB read + 9.5 KB written against 50.83 MB algorithmic); traffic grows with N*K.
+# DRAM bytes (read + written) per algorithmic byte of the decode matmul, from one ncu capture of
+# the gate|up shape (50.80 MB read + 9.5 KB written against 50.83 MB algorithmic); the traffic
+# grows in proportion to N*K, so the bench line scales this constant instead of measuring it.
 NCU_TRAFFIC_PER_ALGO_BYTE = 0.9996
+GOLDEN = os.path.join(ROOT, "tests", "golden")
 
 
 def parse():
@@ -44,6 +48,8 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=MODEL["layers"], help="for quick checks only; the bench config is 32")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-kernels", action="store_true", help="skip the kernel-level legs")
+    ap.add_argument("--save-tokens", default=None, help="write the generated tokens (JSON) to this path")
     return ap.parse_args()
 
 
@@ -79,56 +85,106 @@ def algo_bytes_per_step(m, batch, ctx_len, tp=1):
 
 
 # --------------------------------------------------------------------------
-# clocks
+# clocks: read-only NVML polling from a thread, fast enough to land samples inside a timed
+# region of a few tens of milliseconds (nvidia-smi's own loop is too slow to start for that)
 # --------------------------------------------------------------------------
 class ClockSampler:
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
-    def __init__(self, index=0):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index=0, period_s=0.002):
+        self.index, self.period, self.rows, self.marks = index, period_s, [], []
+        self.stop = threading.Event()
+        self.h = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            dev = self._physical(index)
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(dev) if isinstance(dev, int) else pynvml.nvmlDeviceGetHandleByUUID(dev)
+            self.max_sm = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.h = None
+
+    @staticmethod
+    def _physical(index):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip() != ""]
+            if index < len(ids):
+                return int(ids[index]) if ids[index].isdigit() else ids[index]
+        return index
+
+    def _run(self):
+        nv = self.nv
+        while not self.stop.is_set():
+            try:
+                sm = float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    rs = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+                except Exception:
+                    rs = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                self.rows.append((time.perf_counter(), sm, rs))
+            except Exception:
+                pass
+            time.sleep(self.period)
 
     def __enter__(self):
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.t = threading.Thread(target=self._read, daemon=True)
+        if self.h is not None:
+            self.t = threading.Thread(target=self._run, daemon=True)
             self.t.start()
-        except OSError:
-            self.proc = None
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
-
     def __exit__(self, *a):
-        if self.proc:
-            self.proc.terminate()
-            try:
-                self.proc.wait(timeout=2)
-            except Exception:
-                self.proc.kill()
+        self.stop.set()
+        if self.h is not None:
+            self.t.join(timeout=1)
+
+    def region(self):
+        """Context manager marking a timed region: only samples taken inside regions count."""
+        sampler = self
+
+        class _R:
+            def __enter__(self):
+                self.t0 = time.perf_counter()
+
+            def __exit__(self, *a):
+                sampler.marks.append((self.t0, time.perf_counter()))
+        return _R()
 
     def summary(self):
-        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
-        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) >= 9 and r[5 + i].lower().startswith("active") for r in self.rows)]
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(sm)}
+        inside = [r for r in self.rows if any(a <= r[0] <= b for a, b in self.marks)]
+        sm = [r[1] for r in inside]
+        bits = 0
+        for r in inside:
+            bits |= r[2]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": getattr(self, "max_sm", None),
+                "reasons": [n for n, b in self.REASONS.items() if bits & b], "samples": len(sm),
+                "how": "NVML polled every %.0f ms from a thread; samples inside the timed regions only" % (self.period * 1e3)}
 
 
 # --------------------------------------------------------------------------
 # CPU baseline (the oracle's C port on the host cores) — rank 0 only
 # --------------------------------------------------------------------------
-def cpu_decode_rate(m, batch, ctx_len, budget_s, steps=None):
+def _host_cores():
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def _cpu_env():
+    """All host cores, threads pinned: must run before the oracle's OpenMP runtime loads
+    (torch.distributed.run exports OMP_NUM_THREADS=1 to its workers)."""
+    os.environ["OMP_NUM_THREADS"] = str(_host_cores())
+    os.environ.setdefault("OMP_PROC_BIND", "close")
+    os.environ.setdefault("OMP_PLACES", "cores")
+
+
+def cpu_decode_rate(m, batch, ctx_len, budget_s=None, steps=None, warmup=3):
     """Times CPU decode steps on a bounded sample: `sample_layers` of the model's
     layers (per-layer cost is identical; the LM head is timed in full) with a
-    synthetic KV cache of ctx_len tokens.  Returns (tokens/s extrapolated to
-    the full depth, cores, description, seconds per full step)."""
+    synthetic KV cache of ctx_len tokens.  Returns a dict: tokens/s extrapolated to
+    the full depth (from the median step), its min/max over the timed steps, cores, description."""
     from oracle import cport, ref
     cores = cport.threads()
     sample_layers = min(m["layers"], 2)
@@ -150,16 +206,18 @@ def cpu_decode_rate(m, batch, ctx_len, budget_s, steps=None):
     pool[:] = rng.standard_normal(pool.shape[0], dtype=np.float32).astype(np.float16)
     table = np.arange(batch * max_pages, dtype=np.int32).reshape(batch, max_pages)
     toks = rng.integers(0, m["vocab"], batch).astype(np.int32)
-    # time layers and head separately: t_layers from the 2-layer model minus head, head from a direct call
+    # layers and head are timed separately: the slice's step holds the whole head
     x = rng.standard_normal((batch, m["d"]), dtype=np.float32)
-    cport.gemm_bf16(x, dec.lm)  # warm (first touch of the table)
+    for _ in range(warmup):
+        cport.gemm_bf16(x, dec.lm)
     th = []
-    for _ in range(3):
+    for _ in range(7):
         t0 = time.perf_counter()
         cport.gemm_bf16(x, dec.lm)
         th.append(time.perf_counter() - t0)
     t_head = statistics.median(th)
-    dec.step(toks, np.full(batch, ctx_len, np.int32), table)  # warm
+    for i in range(warmup):
+        dec.step(toks, np.full(batch, ctx_len + i, np.int32), table)
     times = []
     t_start = time.perf_counter()
     n = 0
@@ -171,15 +229,18 @@ def cpu_decode_rate(m, batch, ctx_len, budget_s, steps=None):
         if steps is not None:
             if n >= steps:
                 break
-        elif time.perf_counter() - t_start > budget_s or n >= 64:
+        elif time.perf_counter() - t_start > budget_s or n >= 256:
             break
-    t_step = statistics.median(times)
-    t_head = min(t_head, 0.9 * t_step)  # the slice's step contains the head: never extrapolate a negative layer time
-    per_full = (t_step - t_head) / sample_layers * m["layers"] + t_head
     dec.close()
-    desc = ("%d decode steps of a %d-layer slice (+ full LM head) at context %d, batch %d, extrapolated x%d/%d layers"
-            % (n, sample_layers, ctx_len, batch, m["layers"], sample_layers))
-    return batch / per_full, cores, desc, per_full
+
+    def full(t_step):
+        th_ = min(t_head, 0.9 * t_step)  # never extrapolate a negative layer time
+        return (t_step - th_) / sample_layers * m["layers"] + th_
+    per_full = full(statistics.median(times))
+    desc = ("%d decode steps (after %d warm-up) of a %d-layer slice (+ full LM head) at context %d, batch %d, "
+            "extrapolated x%d/%d layers; median step" % (n, warmup, sample_layers, ctx_len, batch, m["layers"], sample_layers))
+    return {"value": batch / per_full, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc,
+            "min": batch / full(max(times)), "max": batch / full(min(times)), "s_per_step": per_full}
 
 
 def run_reference(args):
@@ -188,18 +249,129 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    _cpu_env()
     m = dict(MODEL)
-    total = args.warmup + args.steps
     t0 = time.perf_counter()
-    rate, cores, desc, per_full = cpu_decode_rate(m, args.batch, PROMPT, budget_s=None, steps=max(total, 1))
-    line = {"impl": "reference", "metric": METRIC, "value": rate, "unit": "tokens/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_full * 1e3, "higher_is_better": True,
+    r = cpu_decode_rate(m, args.batch, PROMPT, steps=max(args.steps, 1), warmup=max(args.warmup, 3))
+    line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": r["s_per_step"] * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "configs[4]: 32-layer d4096 ffn11008 32/8-head 4-bit decoder, greedy decode at context %d, batch %d" % (PROMPT, args.batch)},
-            "cpu_baseline": {"value": rate, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc},
-            "e2e": {"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample", "min", "max")},
+            "e2e": {"value": r["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "wall_s": time.perf_counter() - t0}
     print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------
+# kernel-level legs (1 GPU): device-resident inputs, graph replay over a pool of distinct
+# buffers larger than L2, CUDA events on the replaying stream
+# --------------------------------------------------------------------------
+def _time_graph(torch, calls, iters=10):
+    """calls: list of zero-argument launchers.  Returns microseconds per call."""
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for c in calls:
+            c()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        for c in calls:
+            c()
+    for _ in range(3):
+        g.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(iters):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (iters * len(calls))
+
+
+def kernel_legs(ctx, torch, peaks):
+    hbm = float(peaks.get("hbm_gbs", 6650.0))
+    tf = float(peaks.get("bf16_tflops", 1590.0))
+    out = []
+    L2 = 160e6  # a pool at least this large never fits the 126 MB L2
+
+    def wpool(n, k, count):
+        return [ctx.quantize_q4(torch.randn(n, k, device="cuda") * 0.05) for _ in range(count)]
+
+    def gemm_leg(name, m, n, k, dt):
+        wb = n * k * 0.5625
+        ws = wpool(n, k, max(2, int(L2 // wb) + 1))
+        x = torch.randn(m, k, device="cuda").to(dt)
+        y = torch.empty(m, n, device="cuda")
+        us = _time_graph(torch, [lambda w=w: ctx.gemm_q4(w, x, out=y) for w in ws])
+        algo = wb + m * k * x.element_size() + m * n * 4
+        out.append({"name": name, "m": m, "n": n, "k": k, "x": str(dt).split(".")[-1], "algo_bytes": algo, "us": us,
+                    "achieved": algo / us / 1e3, "unit": "GB/s", "frac": algo / us / 1e3 / hbm,
+                    "l2_policy": "pool of %d distinct weights (%.0f MB) replayed from a graph" % (len(ws), len(ws) * wb / 1e6)})
+        for w in ws:
+            w.free()
+
+    gemm_leg("configs[0] gemv", 1, 4096, 4096, torch.float32)
+    for (n, k) in [(4096, 4096), (11008, 4096), (4096, 11008)]:
+        for m in (1, 8, 32):
+            gemm_leg("configs[1] decode-batch gemm", m, n, k, torch.bfloat16)
+    # prefill: tensor-bound
+    for (n, k) in [(11008, 4096), (4096, 11008)]:
+        w0 = wpool(n, k, 1)[0]
+        for m in (512, 2048, 8192):
+            per = n * k * 0.5625 + m * k * 2 + m * n * 4
+            cnt = max(1, int(L2 // per) + 1)
+            xs = [torch.randn(m, k, device="cuda").bfloat16() for _ in range(cnt)]
+            ys = [torch.empty(m, n, device="cuda") for _ in range(cnt)]
+            ws = [w0] + (wpool(n, k, cnt - 1) if cnt > 1 else [])
+            us = _time_graph(torch, [lambda i=i: ctx.gemm_q4(ws[i], xs[i], out=ys[i]) for i in range(cnt)], iters=5)
+            fl = 2.0 * m * n * k
+            out.append({"name": "configs[2] prefill gemm", "m": m, "n": n, "k": k, "flops": fl, "us": us,
+                        "achieved": fl / us / 1e6, "unit": "TFLOP/s", "frac": fl / us / 1e6 / tf,
+                        "l2_policy": "%d distinct (weight, activation, output) sets, %.0f MB per call" % (cnt, per / 1e6)})
+            for w in ws[1:]:
+                w.free()
+            del xs, ys
+        w0.free()
+    # decode attention, configs[3]
+    rng = np.random.Generator(np.random.PCG64(4))
+    B, Hq, Hkv = 16, 32, 8
+    lens = rng.integers(512, 4097, B).astype(np.int32)
+    npages = (lens + 15) // 16
+    total = int(npages.sum())
+    pools = []
+    for _ in range(2):
+        p = ctx.kv_pool(total, Hkv)
+        p.tensor().normal_()
+        pools.append(p)
+    order = rng.permutation(total).astype(np.int32)
+    table = np.zeros((B, int(npages.max())), np.int32)
+    off = 0
+    for b in range(B):
+        table[b, :npages[b]] = order[off:off + npages[b]]
+        off += npages[b]
+    q = torch.randn(B, Hq, 128, device="cuda").half()
+    tb, ln = torch.from_numpy(table).cuda(), torch.from_numpy(lens).cuda()
+    o = torch.empty(B, Hq, 128, device="cuda")
+    us = _time_graph(torch, [lambda p=p: ctx.attn_decode(p, q, tb, ln, out=o) for p in pools] * 4)
+    algo = float(lens.sum()) * Hkv * 2 * 128 * 2 + 2 * B * Hq * 128 * 2
+    out.append({"name": "configs[3] decode attention", "batch": B, "tokens": int(lens.sum()), "algo_bytes": algo, "us": us,
+                "achieved": algo / us / 1e3, "unit": "GB/s", "frac": algo / us / 1e3 / hbm,
+                "l2_policy": "2 distinct KV pools (%.0f MB) replayed from a graph" % (2 * algo / 1e6)})
+    for p in pools:
+        p.free()
+    # LM head (bf16 [32000, 4096]), M = 1
+    V, D = MODEL["vocab"], MODEL["d"]
+    tbs = [(torch.randn(V, D, device="cuda") * 0.02).bfloat16().view(torch.int16) for _ in range(2)]
+    x = torch.randn(1, D, device="cuda")
+    lo = torch.empty(1, V, device="cuda")
+
+    us = _time_graph(torch, [lambda t=t: ctx.lm_head(t, x, out=lo) for t in tbs] * 2)
+    algo = V * D * 2 + (D + V) * 4
+    out.append({"name": "lm head", "m": 1, "algo_bytes": algo, "us": us, "achieved": algo / us / 1e3, "unit": "GB/s",
+                "frac": algo / us / 1e3 / hbm, "l2_policy": "2 distinct tables (524 MB) replayed from a graph"})
+    return out
 
 
 def main():
@@ -220,11 +392,15 @@ def main():
 
     # the weight import (re-tiling on the host) is OpenMP-parallel; torch.distributed.run pins
     # OMP_NUM_THREADS to 1, so give every rank its share of the cores before the library loads
-    os.environ["OMP_NUM_THREADS"] = str(max(1, (os.cpu_count() or 1) // max(world, 1)))
+    if world == 1:
+        _cpu_env()  # also the CPU-baseline leg's settings: OpenMP reads them once, when it loads
+    else:
+        os.environ["OMP_NUM_THREADS"] = str(max(1, _host_cores() // world))
     from cyb_b200 import qeng
     m = dict(MODEL)
     m["layers"] = args.layers
     B, K, Wm = args.batch, args.steps, max(args.warmup, 3)
+    B16 = 16  # the second half of configs[4]
     ctx = qeng.Context(local)
     if world > 1:
         def exchange(b):
@@ -238,7 +414,7 @@ def main():
         ctx.tp_init(rank, world, exchange, allgather)
     max_seq = PROMPT + Wm + 2 * K + 64
     dec = ctx.decoder(layers=m["layers"], d_model=m["d"], ffn=m["ffn"], heads=m["heads"], kv_heads=m["kv_heads"],
-                      vocab=m["vocab"], max_batch=B, max_seq=max_seq, tp_rank=rank, tp_world=world)
+                      vocab=m["vocab"], max_batch=max(B, B16), max_seq=max_seq, tp_rank=rank, tp_world=world)
     t_load = time.perf_counter()
     for l in range(m["layers"]):
         for j, (nm, n, k) in enumerate(layer_shapes(m)):
@@ -248,94 +424,129 @@ def main():
     dec.load_head(gen_table(1, m["vocab"], m["d"]), gen_table(2, m["vocab"], m["d"]), np.ones(m["d"], np.float32))
     t_load = time.perf_counter() - t_load
 
-    prompt = np.random.Generator(np.random.PCG64(7)).integers(0, m["vocab"], (B, PROMPT)).astype(np.int32)
-    dec.use_current_stream()
-    dec.reset(B)
-    dec.prefill(prompt)  # first call: buffers grow, kernels load
-    dec.reset(B)
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    dec.prefill(prompt)
-    torch.cuda.synchronize()
-    t_prefill = time.perf_counter() - t0
-
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-timed decode: K steps replayed from the captured graph ------
-    dec.decode(Wm)
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clk:
-        barrier()
-        ev0.record()
-        dec.decode(K)
-        ev1.record()
-        barrier()
-    ms = ev0.elapsed_time(ev1)
-    t = torch.tensor([ms], device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    value = B * K / (ms * 1e-3)
-    launches = dec.launches_per_step * K
-    ctx_mid = PROMPT + Wm + K // 2
+    def maxr(v):
+        t = torch.tensor([v], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
-    # ---- end to end: one call per token, every token read back to the host ---
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(K):
-        dec.decode(1)
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    t = torch.tensor([e2e_s], device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e = B * K / float(t.item())
+    dec.use_current_stream()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def run_batch(Bn, Kn, clk=None):
+        """prompt of PROMPT tokens then Wm warm-up and Kn timed decode steps at batch Bn."""
+        prompt = np.random.Generator(np.random.PCG64(7)).integers(0, m["vocab"], (Bn, PROMPT)).astype(np.int32)
+        dec.reset(Bn)
+        dec.prefill(prompt)  # first call: buffers grow, kernels load
+        dec.reset(Bn)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        dec.prefill(prompt)
+        torch.cuda.synchronize()
+        t_prefill = time.perf_counter() - t0
+        logits0 = dec.logits()
+        warm = dec.decode(Wm)
+        barrier()
+        if clk is not None:
+            with clk.region():
+                ev0.record()
+                toks = dec.decode(Kn)
+                ev1.record()
+                barrier()
+        else:
+            ev0.record()
+            toks = dec.decode(Kn)
+            ev1.record()
+            barrier()
+        ms = maxr(ev0.elapsed_time(ev1))
+        return ms, t_prefill, np.concatenate([warm, toks], 1), logits0
+
+    with ClockSampler(local) as clk:
+        ms, t_prefill, tokens, logits0 = run_batch(B, K, clk)
+        value = B * K / (ms * 1e-3)
+        launches = dec.launches_per_step * K
+        ctx_mid = PROMPT + Wm + K // 2
+        # ---- end to end: one call per token, every token read back to the host ---
+        barrier()
+        with clk.region():
+            t0 = time.perf_counter()
+            for _ in range(K):
+                dec.decode(1)
+            torch.cuda.synchronize()
+            e2e_s = time.perf_counter() - t0
+        e2e = B * K / maxr(e2e_s)
+
+    # ---- what was computed: tokens against the float64 teacher and against the 1-GPU run ------
+    check = {"tokens_crc32": "%08x" % zlib.crc32(np.ascontiguousarray(tokens, np.int32).tobytes()), "tokens_checked": 0}
+    if B == 1 and m["layers"] == MODEL["layers"]:
+        seq = tokens[0]
+        tpath = os.path.join(GOLDEN, "config5_teacher.npz")
+        if os.path.exists(tpath):
+            t = np.load(tpath)
+            n = min(len(seq), len(t["tokens"]))
+            agree = 0
+            while agree < n and seq[agree] == t["tokens"][agree]:
+                agree += 1
+            li = t["top_idx"][0]
+            check.update({"teacher_tokens": n, "teacher_prefix": agree,
+                          "teacher_logits_err_step0": float(np.abs(logits0[0, li] - t["top_val"][0]).max() / t["absmax"][0]),
+                          "teacher": "float64 oracle, free-running greedy decode of the same seeded model (fixture)"})
+        ppath = os.path.join(GOLDEN, "bench_tokens_tp1.json")
+        if os.path.exists(ppath):
+            ref1 = json.load(open(ppath))["tokens"]
+            n = min(len(seq), len(ref1))
+            agree = 0
+            while agree < n and int(seq[agree]) == ref1[agree]:
+                agree += 1
+            check.update({"tokens_checked": n, "tokens_match_tp1": agree == n, "tokens_common_prefix_tp1": agree})
+    if args.save_tokens and rank == 0:
+        json.dump({"tokens": [int(v) for v in tokens[0]], "batch": B, "warmup": Wm, "steps": K, "world": world},
+                  open(args.save_tokens, "w"))
 
     # ---- roofline of the dominant kernel: the 4-bit GEMV over this decoder's own
     # weights (32 layers x 4 fused matrices = distinct buffers >> L2), timed with events
-    roof = None
-    if True:
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except Exception:
-            pass
-        peak = float(peaks.get("hbm_gbs", 6650.0))
-        ws = [dec.weight(l, i) for l in range(m["layers"]) for i in range(4)]
-        xs = {k: torch.randn(k, device="cuda") for k in {w.cols for w in ws}}
-        ys = {w.rows: torch.empty(w.rows, device="cuda") for w in ws}
-        algo = sum(w.rows * w.cols * 0.5625 + w.cols * 4 + w.rows * 4 for w in ws)
-        # replayed from a CUDA graph so that the host launch rate does not bound the figure
-        side = torch.cuda.Stream()
-        with torch.cuda.stream(side):
-            for w in ws:
-                ctx.gemv_q4(w, xs[w.cols], out=ys[w.rows])
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=side):
-            for w in ws:
-                ctx.gemv_q4(w, xs[w.cols], out=ys[w.rows])
-        for _ in range(3):
-            graph.replay()
-        reps = 10
-        torch.cuda.synchronize()
-        ev0.record()
-        for _ in range(reps):
-            graph.replay()
-        ev1.record()
-        torch.cuda.synchronize()
-        per_launch_s = ev0.elapsed_time(ev1) * 1e-3 / (reps * len(ws))
-        achieved = algo / len(ws) / per_launch_s / 1e9
-        roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": (NCU_TRAFFIC_PER_ALGO_BYTE * algo / len(ws)) if NCU_TRAFFIC_PER_ALGO_BYTE else None,
-                "kernel": "gemv_q4_stream_kernel<NT=1,TG> (M=1, f32 activations)", "bytes_per_launch": algo / len(ws),
-                "us_per_launch": per_launch_s * 1e6,
-                "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback",
-                "step_frac": algo_bytes_per_step(m, B, ctx_mid, world) / (ms * 1e-3 / K) / 1e9 / peak}
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    ws = [dec.weight(l, i) for l in range(m["layers"]) for i in range(4)]
+    xs = {k: torch.randn(k, device="cuda") for k in {w.cols for w in ws}}
+    ys = {w.rows: torch.empty(w.rows, device="cuda") for w in ws}
+    algo = sum(w.rows * w.cols * 0.5625 + w.cols * 4 + w.rows * 4 for w in ws)
+    per_launch_us = _time_graph(torch, [lambda w=w: ctx.gemv_q4(w, xs[w.cols], out=ys[w.rows]) for w in ws])
+    achieved = algo / len(ws) / per_launch_us / 1e3
+    roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+            "traffic": NCU_TRAFFIC_PER_ALGO_BYTE * algo / len(ws),
+            "traffic_how": "one ncu capture of the gate|up shape (DRAM bytes = 0.9996 x algorithmic), scaled by N*K; not measured in this run",
+            "kernel": "gemv_q4_stream_kernel (M=1, f32 activations), the decoder's own 4 x %d layer matrices in loop order" % m["layers"],
+            "bytes_per_launch": algo / len(ws), "us_per_launch": per_launch_us,
+            "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback",
+            "frac_of_nominal_8tbs": achieved / 8000.0,
+            "step_frac": algo_bytes_per_step(m, B, ctx_mid, world) / (ms * 1e-3 / K) / 1e9 / peak}
+
+    # ---- batch 16 (the other half of configs[4]) and the kernel-level legs -----------------
+    kernels = []
+    b16 = None
+    if not args.no_kernels and B != B16:
+        K16 = min(K, 32)
+        ms16, tp16, _, _ = run_batch(B16, K16)
+        ctx16 = PROMPT + Wm + K16 // 2
+        b16 = {"name": "configs[4] batch 16 decode", "value": B16 * K16 / (ms16 * 1e-3), "unit": "tokens/s",
+               "ms_per_step": ms16 / K16, "steps": K16,
+               "step_frac": algo_bytes_per_step(m, B16, ctx16, world) / (ms16 * 1e-3 / K16) / 1e9 / peak,
+               "prefill_tokens_per_s": B16 * PROMPT / tp16}
     ctx.device_status()
+    dec.free()
+    if not args.no_kernels and world == 1:
+        kernels = kernel_legs(ctx, torch, peaks)
+        ctx.device_status()
 
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": Wm,
@@ -348,13 +559,16 @@ def main():
                 "clocks": clk.summary(), "gpu_launches": launches,
                 "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 8 * B, "d2h_bytes_per_step": 4 * B + 4,
                         "how": "one qeng_decoder_decode(1) call per token, sampled token copied to the host every step"},
-                "roofline": roof, "prefill_s": t_prefill, "prefill_tokens_per_s": B * PROMPT / t_prefill,
+                "roofline": roof, "check": check, "prefill_s": t_prefill, "prefill_tokens_per_s": B * PROMPT / t_prefill,
                 "load_s": t_load}
+        if b16 is not None:
+            line["batch16"] = b16
+        if kernels:
+            line["kernels"] = kernels
         if not args.no_cpu_baseline and world == 1:
-            rate, cores, desc, _ = cpu_decode_rate(m, B, PROMPT, budget_s=15.0)
-            line["cpu_baseline"] = {"value": rate, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc}
+            r = cpu_decode_rate(m, B, PROMPT, budget_s=12.0)
+            line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample", "min", "max")}
         print(json.dumps(line))
-    dec.free()
     if world > 1:
         dist.destroy_process_group()
 

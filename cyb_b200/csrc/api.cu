@@ -1,6 +1,7 @@
 // Context and error plumbing of libqeng.
 #include <stdarg.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include "qeng_internal.h"
 
@@ -18,9 +19,18 @@ extern "C" {
 
 int32_t qeng_version(void) { return 100; }
 
-int32_t qeng_create(int32_t device, qeng_ctx** out) {
+int32_t qeng_create(int32_t device, qeng_ctx** out) { return qeng_create_opts(device, nullptr, out); }
+
+int32_t qeng_create_opts(int32_t device, const qeng_options* opts, qeng_ctx** out) {
   if (!out) return QENG_ERR_ARG;
   *out = nullptr;
+  qeng_options o = {};
+  if (opts) {  // an older caller's (shorter) struct leaves the newer fields at their defaults
+    if (opts->struct_size < (int32_t)sizeof(int32_t) || opts->struct_size > 4096) return QENG_ERR_ARG;
+    memcpy(&o, opts, (size_t)opts->struct_size < sizeof o ? (size_t)opts->struct_size : sizeof o);
+  }
+  if (o.attn_ctas_per_sm < 0 || o.attn_ctas_per_sm > 64) return QENG_ERR_ARG;
+  if (o.stream_groups != 0 && o.stream_groups != 1 && o.stream_groups != 2 && o.stream_groups != 4) return QENG_ERR_ARG;
   int count = 0;
   if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) return QENG_ERR_CUDA;  // no CPU fallback
   if (device < 0 || device >= count) return QENG_ERR_ARG;
@@ -36,8 +46,13 @@ int32_t qeng_create(int32_t device, qeng_ctx** out) {
     return QENG_ERR_CUDA;
   }
   ctx->sm_count = prop.multiProcessorCount;
-  ctx->pdl = getenv("QENG_NO_PDL") == nullptr;
-  ctx->l2_prefetch = getenv("QENG_NO_L2_PREFETCH") == nullptr;
+  ctx->pdl = !o.no_pdl;
+  ctx->l2_prefetch = !o.no_l2_prefetch;
+  ctx->p2p_allowed = !o.no_p2p_allreduce;
+  ctx->attn_cluster = !o.no_attn_cluster;
+  ctx->step_kernel = !o.no_step_kernel;
+  ctx->attn_ctas_per_sm = o.attn_ctas_per_sm > 0 ? o.attn_ctas_per_sm : 8;
+  ctx->stream_groups = o.stream_groups;
   if (cudaMalloc(&ctx->status, 64) != cudaSuccess || cudaMemset(ctx->status, 0, 64) != cudaSuccess) {
     delete ctx;
     return QENG_ERR_CUDA;

@@ -415,8 +415,7 @@ constexpr int kMaxAttnCounters = 1 << 16;  // (sequence, kv head) pairs per call
 
 // Splits: enough CTAs to fill the machine several times over, at least one page per warp.
 static int pages_per_split(const qeng_ctx* ctx, int64_t B, int64_t Hkv, int64_t max_pages) {
-  static const int mult = getenv("QENG_ATTN_CTAS_PER_SM") ? atoi(getenv("QENG_ATTN_CTAS_PER_SM")) : 8;
-  int64_t target = (int64_t)ctx->sm_count * mult;
+  int64_t target = (int64_t)ctx->sm_count * (ctx->attn_ctas_per_sm > 0 ? ctx->attn_ctas_per_sm : 8);
   int64_t pps = (B * Hkv * max_pages + target - 1) / target;
   pps = (pps + kAW - 1) / kAW * kAW;
   if (pps < kAW) pps = kAW;
@@ -439,6 +438,7 @@ int32_t qeng_attn_reserve(qeng_ctx* ctx, int64_t B, int64_t Hq, int64_t Hkv, int
   if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);
   ctx->attn_scratch = nullptr;
   ctx->attn_scratch_bytes = 0;
+  ctx->scratch_gen++;
   QENG_CUDA(ctx, cudaMalloc(&ctx->attn_scratch, need));
   QENG_CUDA(ctx, cudaMemset(ctx->attn_scratch, 0, need));  // the arrival counters start at zero and return to it
   ctx->attn_scratch_bytes = need;
@@ -507,7 +507,7 @@ int32_t qeng_attn_decode(qeng_ctx* ctx, const qeng_kv_pool* pool, const uint16_t
   p.pages = (int)pool->pages; p.Hkv = (int)pool->kv_heads; p.Hq = (int)Hq; p.grp = (int)(Hq / pool->kv_heads);
   p.max_pages = (int)max_pages;
   p.scale_log2 = scale * 1.4426950408889634f;
-  static const bool no_cluster = getenv("QENG_ATTN_NO_CLUSTER") != nullptr;
+  const bool no_cluster = !ctx->attn_cluster;
   // Cluster path: 1, 2, 4 or 8 CTAs per (sequence, kv head), as many as keep the grid within about one
   // wave (two CTAs per SM), merged through distributed shared memory.  A lane holds one page id per
   // tile of its warp, which caps the cache at cs * 4 * 32 pages; beyond that the fixed splits below.

@@ -184,7 +184,7 @@ struct qeng_decoder {
   float *x = nullptr, *qkv = nullptr, *att = nullptr, *act = nullptr, *part = nullptr;
   float *xnr = nullptr, *gu = nullptr;  // prefill only: normalised rows, gate|up before SwiGLU
   __half* q16 = nullptr;
-  int32_t *pos = nullptr, *lens = nullptr, *table = nullptr;  // per row
+  int32_t *pos = nullptr, *lens = nullptr, *table = nullptr, *tok = nullptr;  // per row
   // decode state
   float *xn = nullptr, *xlast = nullptr, *logits = nullptr;
   int32_t *next = nullptr, *out_tokens = nullptr, *step = nullptr, *dec_table = nullptr;
@@ -204,19 +204,27 @@ struct qeng_decoder {
   cudaStream_t own_stream = nullptr;
   cudaGraphExec_t graph = nullptr;
   int graph_batch = 0;
+  uint64_t graph_scratch_gen = 0;  // ctx->scratch_gen at capture time
   int launches = 0;
 };
 
 namespace {
 
+// Prompt rows go through the decode attention kernel one "sequence" per row, at most this many
+// per launch (bounds its grid, its arrival counters and its split scratch).
+constexpr int64_t kAttnRowsPerCall = 2048;
+
+// Grow the per-row buffers.  A captured decode step holds their addresses, so it is dropped here
+// and captured again by the next decode call.
 int32_t ensure_rows(qeng_ctx* ctx, qeng_decoder* d, int64_t rows) {
   if (rows <= d->rows_cap) return QENG_OK;
   QENG_CUDA(ctx, cudaDeviceSynchronize());
+  if (d->graph) { cudaGraphExecDestroy(d->graph); d->graph = nullptr; }
   float** fb[] = {&d->x, &d->qkv, &d->att, &d->act, &d->part, &d->xnr, &d->gu};
   for (auto p : fb)
     if (*p) { cudaFree(*p); *p = nullptr; }
   if (d->q16) { cudaFree(d->q16); d->q16 = nullptr; }
-  int32_t** ib[] = {&d->pos, &d->lens, &d->table};
+  int32_t** ib[] = {&d->pos, &d->lens, &d->table, &d->tok};
   for (auto p : ib)
     if (*p) { cudaFree(*p); *p = nullptr; }
   d->rows_cap = 0;
@@ -234,8 +242,9 @@ int32_t ensure_rows(qeng_ctx* ctx, qeng_decoder* d, int64_t rows) {
   QENG_CUDA(ctx, cudaMalloc(&d->pos, rows * 4));
   QENG_CUDA(ctx, cudaMalloc(&d->lens, rows * 4));
   QENG_CUDA(ctx, cudaMalloc(&d->table, rows * d->max_pages * 4));
+  QENG_CUDA(ctx, cudaMalloc(&d->tok, rows * 4));
   d->rows_cap = rows;
-  return qeng_attn_reserve(ctx, rows, d->Hq, d->Hkv, d->max_pages);
+  return qeng_attn_reserve(ctx, rows < kAttnRowsPerCall ? rows : kAttnRowsPerCall, d->Hq, d->Hkv, d->max_pages);
 }
 
 // matmul over `rows` activation rows in chunks the decode kernels accept: the largest row count
@@ -320,9 +329,12 @@ int32_t run_layer_prefill(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, c
                                                      d->Hq, d->Hkv, d->cfg.max_seq, d->q16, pool, ctx->status, L.qnorm, L.knorm, d->cfg.rms_eps);
   QENG_LAUNCH_CHECK(ctx);
   d->view.pages = d->pages; d->view.kv_heads = d->Hkv; d->view.hd = kHD; d->view.data = pool;
-  rc = qeng_attn_decode(ctx, &d->view, reinterpret_cast<const uint16_t*>(d->q16), table, d->max_pages, d->lens, rows,
-                        d->Hq, 1.0f / sqrtf((float)kHD), d->att, st);
-  if (rc != QENG_OK) return rc;
+  for (int64_t r0 = 0; r0 < rows; r0 += kAttnRowsPerCall) {
+    const int64_t nr = rows - r0 < kAttnRowsPerCall ? rows - r0 : kAttnRowsPerCall;
+    rc = qeng_attn_decode(ctx, &d->view, reinterpret_cast<const uint16_t*>(d->q16 + r0 * nq), table + r0 * d->max_pages,
+                          d->max_pages, d->lens + r0, nr, d->Hq, 1.0f / sqrtf((float)kHD), d->att + r0 * nq, st);
+    if (rc != QENG_OK) return rc;
+  }
   const int64_t n = rows * dm;
   auto row_split_tc = [&](const qeng_weight* w, const float* in, int64_t ldin) -> int32_t {
     if (!tp) return qeng_gemm_q4_prefill(ctx, w, in, QENG_F32, rows, ldin, d->x, dm, 1, st);
@@ -570,7 +582,7 @@ int32_t qeng_decoder_free(qeng_ctx* ctx, qeng_decoder* d) {
     if (L.knorm) cudaFree(L.knorm);
   }
   void* bufs[] = {d->emb, d->lm_head, d->final_norm, d->rope_cs, d->pool, d->x, d->qkv, d->att, d->act, d->part, d->xnr, d->gu, d->q16,
-                  d->pos, d->lens, d->table, d->xn, d->xlast, d->logits, d->next, d->out_tokens, d->step, d->dec_table, d->tp_pairs, d->tp_gath};
+                  d->pos, d->lens, d->table, d->tok, d->xn, d->xlast, d->logits, d->next, d->out_tokens, d->step, d->dec_table, d->tp_pairs, d->tp_gath};
   for (void* p : bufs)
     if (p) cudaFree(p);
   if (d->own_stream) cudaStreamDestroy(d->own_stream);
@@ -736,8 +748,7 @@ int32_t qeng_decoder_prefill(qeng_ctx* ctx, qeng_decoder* d, const int32_t* toke
       lens[r] = pos[r] + 1;
       for (int p = 0; p < d->max_pages; ++p) table[(size_t)r * d->max_pages + p] = p * d->cfg.max_batch + b;
     }
-  int32_t* dtok = nullptr;
-  QENG_CUDA(ctx, cudaMalloc(&dtok, rows * 4));
+  int32_t* dtok = d->tok;
   cudaMemcpyAsync(dtok, tokens, rows * 4, cudaMemcpyHostToDevice, st);
   cudaMemcpyAsync(d->pos, pos.data(), rows * 4, cudaMemcpyHostToDevice, st);
   cudaMemcpyAsync(d->lens, lens.data(), rows * 4, cudaMemcpyHostToDevice, st);
@@ -752,7 +763,6 @@ int32_t qeng_decoder_prefill(qeng_ctx* ctx, qeng_decoder* d, const int32_t* toke
     rc = tail(ctx, d, d->xlast, batch, false, st);
   }
   cudaError_t e = cudaStreamSynchronize(st);
-  cudaFree(dtok);
   if (rc != QENG_OK) return rc;
   if (e != cudaSuccess) return qeng_fail(ctx, QENG_ERR_CUDA, "decoder_prefill: %s", cudaGetErrorString(e));
   for (int b = 0; b < batch; ++b) d->len[b] += T;
@@ -793,7 +803,7 @@ int32_t qeng_decoder_decode(qeng_ctx* ctx, qeng_decoder* d, int32_t steps, int32
     QENG_LAUNCH_CHECK(ctx);
   }
   d->next_ready = false;  // until this call's steps have run to the end
-  if (!d->graph || d->graph_batch != B) {
+  if (!d->graph || d->graph_batch != B || d->graph_scratch_gen != ctx->scratch_gen) {
     QENG_CUDA(ctx, cudaStreamSynchronize(st));
     if (d->graph) { cudaGraphExecDestroy(d->graph); d->graph = nullptr; }
     cudaGraph_t g = nullptr;
@@ -807,6 +817,7 @@ int32_t qeng_decoder_decode(qeng_ctx* ctx, qeng_decoder* d, int32_t steps, int32
     cudaGraphDestroy(g);
     if (e != cudaSuccess) return qeng_fail(ctx, QENG_ERR_CUDA, "decoder_decode: instantiate failed: %s", cudaGetErrorString(e));
     d->graph_batch = B;
+    d->graph_scratch_gen = ctx->scratch_gen;
   }
   for (int s = 0; s < steps; ++s) QENG_CUDA(ctx, cudaGraphLaunch(d->graph, st));
   QENG_CUDA(ctx, cudaMemcpyAsync(out_tokens, d->out_tokens, (size_t)steps * B * 4, cudaMemcpyDeviceToHost, st));

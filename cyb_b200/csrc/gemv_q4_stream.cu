@@ -614,8 +614,7 @@ int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
   // spans several stages, and a group whose ring is shorter than its tile stalls the producer)
   const int spt = (p.nchunks + kSC - 1) / kSC;
   while (tg > 1 && f.nstages / tg < (spt > 2 ? spt : 2)) tg >>= 1;
-  static const int tg_env = [] { const char* e = getenv("QENG_STREAM_GROUPS"); return e ? atoi(e) : 0; }();
-  if (tg_env == 1 || tg_env == 2 || tg_env == 4) tg = tg_env;
+  if (ctx->stream_groups == 1 || ctx->stream_groups == 2 || ctx->stream_groups == 4) tg = ctx->stream_groups;
 #define QENG_STREAM_CASE(NT_)                                                   \
   (tg == 4 ? launch_stream<NT_, 4>(ctx, p, f.smem, stream)                      \
            : (tg == 2 ? launch_stream<NT_, 2>(ctx, p, f.smem, stream) : launch_stream<NT_, 1>(ctx, p, f.smem, stream)))

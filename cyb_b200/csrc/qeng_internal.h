@@ -58,6 +58,11 @@ struct qeng_ctx {
   bool p2p_ready = false;
   bool l2_prefetch = true;    // the streaming matmul requests the hinted next matrix into L2
   bool pdl = true;            // launch the streaming matmul with programmatic stream serialization
+  // remaining switches of qeng_options
+  bool p2p_allowed = true, attn_cluster = true, step_kernel = true;
+  int attn_ctas_per_sm = 8, stream_groups = 0;
+  // bumped whenever attn_scratch moves: a captured graph that holds the old address is stale
+  uint64_t scratch_gen = 0;
   // per-CTA argmax partials and the arrival counter of the fused LM head
   float* tail_val = nullptr;
   int32_t* tail_idx = nullptr;

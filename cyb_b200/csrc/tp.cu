@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(kP2pThreads) p2p_allreduce_add_kernel(const P2
     for (int r = 0; r < p.world && !failed; ++r) {
       const uint2* in = p.inbox[p.rank] + ((size_t)slot * p.world + r) * kP2pMaxElems + i0;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
+      for (int e = 0; e < 4 && !failed; ++e) {
         uint32_t val, tag;
         unsigned long long t0 = 0;
         for (int spin = 0;; ++spin) {
@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(kP2pThreads) p2p_allreduce_add_kernel(const P2
             }
           }
         }
-        a[e] += __uint_as_float(val);
+        if (!failed) a[e] += __uint_as_float(val);
       }
     }
     if (!failed) *reinterpret_cast<float4*>(p.dst + i0) = acc;
@@ -220,7 +220,7 @@ int32_t qeng_tp_p2p_open(qeng_ctx* ctx, const uint8_t* handles) {
     if (e != cudaSuccess) return qeng_fail(ctx, QENG_ERR_CUDA, "tp_p2p_open: rank %d: %s", r, cudaGetErrorString(e));
     ctx->p2p_peer[r] = ptr;
   }
-  ctx->p2p_ready = getenv("QENG_NO_P2P") == nullptr;
+  ctx->p2p_ready = ctx->p2p_allowed;
   return QENG_OK;
 }
 

@@ -49,6 +49,13 @@ _lib = load_library()
 _vp, _i32, _i64, _f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float
 
 
+class Options(C.Structure):
+    """qeng_options: tuning switches fixed when a context is created (0 keeps the default)."""
+    _fields_ = [("struct_size", C.c_int32), ("no_pdl", C.c_int32), ("no_l2_prefetch", C.c_int32),
+                ("no_p2p_allreduce", C.c_int32), ("no_attn_cluster", C.c_int32), ("attn_ctas_per_sm", C.c_int32),
+                ("stream_groups", C.c_int32), ("no_step_kernel", C.c_int32)]
+
+
 class ModelCfg(C.Structure):
     _fields_ = [("layers", _i32), ("d_model", _i32), ("ffn", _i32), ("heads", _i32), ("kv_heads", _i32),
                 ("head_dim", _i32), ("vocab", _i32), ("rms_eps", _f32), ("rope_base", _f32),
@@ -64,6 +71,7 @@ def _sig(name, res, *args):
 
 _sig("qeng_version", _i32)
 _sig("qeng_create", _i32, _i32, C.POINTER(_vp))
+_sig("qeng_create_opts", _i32, _i32, C.POINTER(Options), C.POINTER(_vp))
 _sig("qeng_destroy", _i32, _vp)
 _sig("qeng_last_error", C.c_char_p, _vp)
 _sig("qeng_device_status", _i32, _vp)
@@ -131,9 +139,15 @@ def _cur_stream():
 class Context:
     """One engine context on one CUDA device."""
 
-    def __init__(self, device=0):
+    def __init__(self, device=0, **options):
+        """`options`: fields of qeng_options (no_pdl, no_l2_prefetch, no_p2p_allreduce, no_attn_cluster,
+        attn_ctas_per_sm, stream_groups, no_step_kernel)."""
         h = _vp()
-        rc = _lib.qeng_create(device, C.byref(h))
+        if options:
+            o = Options(struct_size=C.sizeof(Options), **{k: int(v) for k, v in options.items()})
+            rc = _lib.qeng_create_opts(device, C.byref(o), C.byref(h))
+        else:
+            rc = _lib.qeng_create(device, C.byref(h))
         if rc != 0:
             raise QengError(rc, "qeng_create failed (no B200 visible, or device index out of range)")
         self.h = h
@@ -268,10 +282,11 @@ class Context:
                                    _cur_stream()))
         return x
 
-    def lm_head(self, table_bf16, x):
+    def lm_head(self, table_bf16, x, out=None):
         import torch
         v, d = table_bf16.shape
-        out = torch.empty((x.shape[0], v), dtype=torch.float32, device=x.device)
+        if out is None:
+            out = torch.empty((x.shape[0], v), dtype=torch.float32, device=x.device)
         self.check(_lib.qeng_lm_head(self.h, _dev_ptr(table_bf16), _dev_ptr(x), x.shape[0], d, v, _dev_ptr(out),
                                      _cur_stream()))
         return out

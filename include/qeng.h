@@ -61,6 +61,21 @@ typedef struct qeng_decoder qeng_decoder;
  *      named "cpu . wgpu . honeycrisp" in decide/model-lifecycle.md:25) ------- */
 int32_t qeng_version(void);
 int32_t qeng_create(int32_t device, qeng_ctx** out);
+/* Tuning switches of a context: a plain struct, fixed at creation (the library reads no
+ * environment variable).  Zero-initialise, set struct_size = sizeof(qeng_options), then change
+ * what you need; a field left at 0 keeps its default.  Results never depend on any of them
+ * beyond f32 summation order. */
+typedef struct qeng_options {
+  int32_t struct_size;       /* sizeof(qeng_options) of the caller's header */
+  int32_t no_pdl;            /* 1: launch the decode matmuls without programmatic dependent launch */
+  int32_t no_l2_prefetch;    /* 1: ignore qeng_weight_set_next hints */
+  int32_t no_p2p_allreduce;  /* 1: small all-reduces go through NCCL instead of the peer-store kernel */
+  int32_t no_attn_cluster;   /* 1: decode attention always uses fixed splits + scratch */
+  int32_t attn_ctas_per_sm;  /* CTAs per SM the split-KV attention aims for (default 8) */
+  int32_t stream_groups;     /* tile groups of the streaming matmul: 1, 2 or 4 (default: by shape) */
+  int32_t no_step_kernel;    /* 1: a decode step is the per-operator kernel chain, never the fused step kernel */
+} qeng_options;
+int32_t qeng_create_opts(int32_t device, const qeng_options* opts, qeng_ctx** out);
 int32_t qeng_destroy(qeng_ctx* ctx);
 const char* qeng_last_error(const qeng_ctx* ctx);
 /* Drain the device, read and clear the status word kernels write when they meet a

@@ -156,6 +156,41 @@ def test_prefill_tensor_core_path(ctx, m, n, k):
     w.free()
 
 
+def _sample_rows(m):
+    """Rows that hit every position of a 256-row tile and both ends of the matrix."""
+    r = np.concatenate([np.arange(0, m, 13), [0, 127, 128, 255, 256, 257, m - 258, m - 257, m - 129, m - 2, m - 1]])
+    return np.unique(r[(r >= 0) & (r < m)])
+
+
+@pytest.mark.parametrize("m,n,k", [(2048, 11008, 4096), (8192, 11008, 4096), (8192, 4096, 11008), (2049, 11024, 4096)])
+def test_prefill_wide_tile_kernel(ctx, m, n, k):
+    """The M = 2048 and 8192 cases of the prefill sweep select the 256-wide output tile (all 512
+    tensor-memory columns); (2049, 11024) adds a partial last row tile and a partial last column
+    tile.  The device computes every row; the oracle checks a sample of rows that covers every
+    position inside a tile (the float64 product of the full matrix would take minutes)."""
+    import torch
+    rng = ref.rng_of(2000 + m + n + k)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    q, s = ref.make_q4(rng, n, k)
+    w = ctx.pack_q4(q, s)
+    y = ctx.gemm_q4(w, _t(x))
+    ctx.device_status()
+    rows = _sample_rows(m)
+    ys = y[torch.from_numpy(rows).cuda()].cpu().numpy()
+    xb = ref.to_bf16(x[rows])
+    same = xb.astype(np.float64) @ ref.dequant_bf16(q, s).T
+    assert ref.err_inf(ys, same) < 2e-5, ref.err_inf(ys, same)
+    assert ref.err_inf(ys, x[rows].astype(np.float64) @ ref.dequant(q, s).T) < 5e-3
+    # every row, through a size-independent property: the column sums of y equal (sum of rows of bf16(x)) . W^T
+    colsum = y.double().sum(0).cpu().numpy()
+    want = ref.to_bf16(x).astype(np.float64).sum(0)[None] @ ref.dequant_bf16(q, s).T
+    assert ref.err_inf(colsum, want[0]) < 1e-4
+    # accumulate form on bf16 activations
+    y2 = ctx.gemm_q4(w, _t(ref.to_bf16(x)).to(torch.bfloat16), out=y.clone(), flags=1)
+    assert float((y2 - 2 * y).abs().max()) <= 1e-5 * float(y.abs().max())
+    w.free()
+
+
 @pytest.mark.parametrize("n,k", [(768, 4096), (4096, 512), (2752, 4096), (4096, 1376), (1536, 4096), (4096, 2752)])
 def test_tensor_parallel_shard_shapes(ctx, n, k):
     """The per-rank matrices of the 2/4/8-way sharded decoder (K = 1376 has an odd number of

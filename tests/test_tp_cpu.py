@@ -1,5 +1,5 @@
 """The tensor-parallel path on CPU: two gloo ranks shard one decoder layer by the engine's rules
-(cyb_b200.tp), compute their parts with the oracle, sum the row-split partials with an
+(tests/tp_rules.py), compute their parts with the oracle, sum the row-split partials with an
 all-reduce, and must reproduce the unsharded layer."""
 import os
 import socket
@@ -21,7 +21,7 @@ def _free_port():
 def _rank_main(rank, world, port, out):
     import torch
     import torch.distributed as dist
-    from cyb_b200 import tp
+    import tp_rules as tp
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -84,7 +84,7 @@ def test_two_rank_layer_matches_unsharded():
 
 
 def test_shard_bounds_cover_and_reject():
-    from cyb_b200 import tp
+    import tp_rules as tp
     for world in (1, 2, 4, 8):
         rows = [tp.shard_bounds("wgate", 11008, 4096, r, world) for r in range(world)]
         assert rows[0][0] == 0 and rows[-1][1] == 11008 and all(a[1] == b[0] for a, b in zip(rows, rows[1:]))
@@ -95,7 +95,7 @@ def test_shard_bounds_cover_and_reject():
 
 
 def test_vocab_shard_and_token_pick():
-    from cyb_b200 import tp
+    import tp_rules as tp
     for world in (2, 4, 8):
         b = [tp.vocab_shard(32000, r, world) for r in range(world)]
         assert b[0][0] == 0 and b[-1][1] == 32000 and all(x[1] == y[0] for x, y in zip(b, b[1:]))

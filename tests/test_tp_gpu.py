@@ -1,5 +1,6 @@
-"""Tensor parallelism on real GPUs (needs >= 2): two ranks, NCCL all-reduce after the row-split
-projections; tokens and logits must match the unsharded oracle decoder."""
+"""Tensor parallelism on real GPUs (needs >= 2): 2, 4 or 8 ranks, one process per GPU, the sum
+after the row-split projections over NVLink; tokens, logits and teacher-forced layers must match
+the unsharded oracle decoder."""
 import os
 import socket
 
@@ -155,3 +156,92 @@ def test_missing_peer_is_reported_not_hung(built_lib):
         p.join(timeout=60)
         assert p.exitcode == 0
     assert res[0] == (-7, True, True, True), res
+
+
+def _wide_rank_main(rank, world, port, out):
+    """A decoder whose 8 kv heads split down to one per GPU at 8 ranks: greedy tokens and logits
+    against the float64 teacher; then ONE layer at the full widths (d 4096, FFN 11008: per-rank
+    shards 11008/world wide, 1376 at 8 ranks, an odd number of 32-blocks) teacher-forced."""
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from cyb_b200 import qeng
+    ctx = qeng.Context(rank)
+
+    def exchange(b):
+        obj = [b]
+        dist.broadcast_object_list(obj, src=0)
+        return obj[0]
+
+    def allgather(b):
+        outl = [None] * world
+        dist.all_gather_object(outl, b)
+        return outl
+    ctx.tp_init(rank, world, exchange, allgather)
+    cfg = ref.DecoderConfig(layers=2, d=256, ffn=512, heads=8, kv_heads=8, vocab=320)
+    W = ref.make_decoder_weights(cfg, seed=6)
+    dec = ctx.decoder(layers=2, d_model=256, ffn=512, heads=8, kv_heads=8, vocab=320, max_batch=2, max_seq=64,
+                      tp_rank=rank, tp_world=world)
+    qeng.load_decoder_weights(dec, W, cfg)
+    prompt = ref.rng_of(17).integers(0, 320, (2, 9)).astype(np.int32)
+    want, logs = ref.Decoder(cfg, W).generate(prompt, 6)
+    dec.reset(2)
+    dec.prefill(prompt)
+    e_log = ref.err_inf(dec.logits(), logs[0])
+    toks = dec.decode(6)
+    ctx.device_status()
+    dec.free()
+    # one full-width layer, 5 prompt rows then a decode row
+    cfgw = ref.DecoderConfig(layers=1, d=4096, ffn=11008, heads=32, kv_heads=8, vocab=256)
+    Ww = ref.make_decoder_weights(cfgw, seed=77)
+    decw = ctx.decoder(layers=1, d_model=4096, ffn=11008, heads=32, kv_heads=8, vocab=256, max_batch=1, max_seq=32,
+                       tp_rank=rank, tp_world=world)
+    qeng.load_decoder_weights(decw, Ww, cfgw)
+    teacher = ref.Decoder(cfgw, Ww)
+    teacher.reset(1)
+    rng = ref.rng_of(78)
+    x = rng.standard_normal((1, 5, cfgw.d), dtype=np.float32) * 2
+    wantl = teacher.layer(0, x.astype(np.float64), np.arange(5)[None])
+    gotl = decw.layer(0, torch.from_numpy(x[0]).cuda(), np.arange(5))
+    e_l = ref.err_inf(gotl.cpu().numpy(), wantl[0])
+    x1 = rng.standard_normal((1, 1, cfgw.d), dtype=np.float32) * 2
+    want1 = teacher.layer(0, x1.astype(np.float64), np.array([[5]]))
+    got1 = decw.layer(0, torch.from_numpy(x1[0]).cuda(), np.array([5]))
+    e_1 = ref.err_inf(got1.cpu().numpy(), want1[0])
+    ctx.device_status()
+    # the rank-ordered sum makes the residual stream bit-identical on every rank
+    mine = got1.cpu().numpy().view(np.uint32)
+    allb = [None] * world
+    dist.all_gather_object(allb, mine.tobytes())
+    same = all(b == allb[0] for b in allb)
+    out.put((rank, e_log, toks.tolist(), want.tolist(), e_l, e_1, same))
+    dist.barrier()
+    decw.free()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sharded_decoder_against_the_teacher(built_lib, world):
+    import torch
+    if not torch.cuda.is_available() or torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_wide_rank_main, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [out.get(timeout=600) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank, e_log, toks, want, e_l, e_1, same in res:
+        assert e_log < 2e-3, (rank, e_log)
+        assert toks == want, rank
+        assert e_l < 5e-4 and e_1 < 5e-4, (rank, e_l, e_1)
+        assert same, rank
