@@ -254,7 +254,7 @@ int32_t mm(qeng_ctx* ctx, qeng_decoder* d, const qeng_weight* w, const float* x,
            int64_t ldy, const qeng_gemm_fuse& fuse, cudaStream_t st) {
   int64_t chunk = 16;
   for (int64_t c = 16; c >= 1; c >>= 1)
-    if (qeng_gemm_q4_stream_fits(w, c, true)) { chunk = c; break; }
+    if (qeng_gemm_q4_stream_fits(ctx, w, c)) { chunk = c; break; }
   for (int64_t m0 = 0; m0 < rows; m0 += chunk) {
     const int64_t mm_ = rows - m0 < chunk ? rows - m0 : chunk;
     qeng_gemm_fuse f = fuse;
@@ -285,6 +285,7 @@ int32_t row_split(qeng_ctx* ctx, qeng_decoder* d, const qeng_weight* w, const fl
                   cudaStream_t st) {
   const int64_t dm = d->cfg.d_model;
   qeng_gemm_fuse f;
+  f.two_limbs = true;  // 15-bit activations: only the q|k|v projection, which feeds the softmax, keeps 22
   if (d->cfg.tp_world == 1) {
     f.epilogue = QENG_EPI_ACCUM;
     return mm(ctx, d, w, in, ldin, rows, d->x, dm, f, st);
@@ -367,7 +368,7 @@ int32_t run_layer(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, const int
   int32_t rc;
   if ((L.qnorm == nullptr) != (L.knorm == nullptr))
     return qeng_fail(ctx, QENG_ERR_STATE, "decoder: layer %d has only one of the q / k head gains", l);
-  if (L.qnorm == nullptr && qeng_gemm_q4_stream_fits(L.wqkv, 1, true)) {
+  if (L.qnorm == nullptr && qeng_gemm_q4_stream_fits(ctx, L.wqkv, 1)) {
     // q|k|v projection with rotary embedding, f16 rounding and KV append in its epilogue
     qeng_qkv_epi E;
     E.pos = d->pos; E.table = table; E.cs = d->rope_cs; E.q16 = d->q16; E.pool = pool;
@@ -391,7 +392,7 @@ int32_t run_layer(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, const int
   rc = row_split(ctx, d, L.wo, d->att, (int64_t)d->Hq * kHD, rows, st);
   if (rc != QENG_OK) return rc;
   qeng_gemm_fuse fg;
-  fg.norm_gamma = L.norm2; fg.norm_eps = d->cfg.rms_eps; fg.epilogue = QENG_EPI_SWIGLU;
+  fg.norm_gamma = L.norm2; fg.norm_eps = d->cfg.rms_eps; fg.epilogue = QENG_EPI_SWIGLU; fg.two_limbs = true;
   rc = mm(ctx, d, L.wgu, d->x, dm, rows, d->act, d->F, fg, st);
   if (rc != QENG_OK) return rc;
   return row_split(ctx, d, L.wdown, d->act, d->F, rows, st);

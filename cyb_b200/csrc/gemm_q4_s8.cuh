@@ -1,0 +1,391 @@
+// Device-side building blocks of the decode matmul over 4-bit block weights, shared by the
+// standalone streaming kernel (gemv_q4_stream.cu) and the fused decode-step kernel
+// (decode_step.cu).
+//
+// Arithmetic.  Weights stay 4-bit codes c in 0..15 with one f16 scale s per 32-block:
+// w = (c - 8) s.  Activations are quantised per (row, 32-block) to 15-bit fixed point with a
+// power-of-two step: e = floor(log2(max|x| over the block)) - 13, q = clamp(rint(x 2^-e),
+// -16384, 16383), split into two signed bytes q = 128 hi + lo (hi = q >> 7 in -128..127,
+// lo = q & 127).  The contraction runs on the tensor pipe as integer MMAs
+// (mma.sync.m16n8k32, u8 codes x s8 activation bytes, exact s32 accumulation): the weight
+// words need one AND per four codes, and the block's zero point enters through the
+// accumulator's initial value -8 sum(hi) / -8 sum(lo).  Per block the exact integer result is
+// scaled in f32: y += s 2^e (128 D_hi + D_lo), f32 accumulation over the blocks.
+// Error: the rounding of x to 15 bits relative to its block's largest magnitude (<= 2^-14 of
+// it), ~5e-5 of max|y| for Gaussian activations; everything else is exact up to the f32
+// accumulation.  One-hot or power-of-two activations are exact.
+//
+// Column use of the 8-wide MMA tile.  An activation row takes two columns (hi, lo).  With one
+// activation row, the 8 columns hold (limb, block) for FOUR consecutive blocks: the MMA of
+// block j gets activation bytes only in the two columns of block j (the other lanes read a
+// zero region), so four blocks share one accumulator fragment and the f32 post-processing (scale
+// conversion, 4 FMAs) is paid once per four blocks instead of once per block.  Two rows: two
+// blocks per fragment.  Three or four rows: one block per fragment, columns = (row, limb).
+// More rows: several such 8-column tiles.
+#pragma once
+#include "qeng_internal.h"
+
+namespace q4s8 {
+
+constexpr int kCW = 16;               // consumer warps
+constexpr int kCT = kCW * 32;         // consumer threads
+constexpr int kThreads = kCT + 32;    // + producer warp
+constexpr int kMaxStages = 24;
+constexpr uint32_t kBias = 0x4B400000u;   // float 12582912: bits kBias + d read as a float are 12582912 + d for |d| < 2^22
+constexpr float kBiasF = 12582912.0f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+// One attempt: the hardware may park the thread until the phase completes or the hinted time passes.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(1000u)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
+  return t;
+}
+// Bounded wait: gives up (false) two seconds after the first failed attempt; a healthy wait ends
+// in microseconds.  The clock is read once per 64 attempts.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (globaltimer() - t0 > 2000000000ull) return false;
+  }
+}
+// 1-D bulk copy global -> shared, completion counted in bytes on the mbarrier
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void l2_prefetch(const void* gptr, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(gptr), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
+  asm volatile("st.shared.v2.u32 [%0], {%1,%2};\n" ::"r"(addr), "r"(a), "r"(b) : "memory");
+}
+// d += a.b : 16 rows x 32 k of u8 codes (a) times 32 k x 8 columns of s8 activation bytes (b), s32
+__device__ __forceinline__ void imma(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                     uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// one 32-block of 16 weight rows: lane (g, t) holds w0 = codes of row g, w1 = codes of row g+8, each
+// the 8 codes of k = 8t + j in nibble j.  The even nibbles (j = 0,2,4,6) land in the MMA's k slots
+// 4t..4t+3, the odd ones in 16+4t..16+4t+3; the staged activation bytes use the same order.
+__device__ __forceinline__ void block_mma(int (&d)[4], uint32_t w0, uint32_t w1, uint32_t b0, uint32_t b1) {
+  const uint32_t m = 0x0f0f0f0fu;
+  imma(d, w0 & m, w1 & m, (w0 >> 4) & m, (w1 >> 4) & m, b0, b1);
+}
+__device__ __forceinline__ float unbias(int d) { return __int_as_float(d) - kBiasF; }
+
+__device__ __forceinline__ float act_f32(const void* x, int dtype, long long i) {
+  if (dtype == QENG_F32) return reinterpret_cast<const float*>(x)[i];
+  if (dtype == QENG_F16) return __half2float(reinterpret_cast<const __half*>(x)[i]);
+  return __uint_as_float((uint32_t)reinterpret_cast<const uint16_t*>(x)[i] << 16);
+}
+
+// Shared-memory geometry of the staged activations of one K slice (bytes, relative to `base`).
+//   xq   : [cols][col_stride]  s8 bytes; column c = 2 * row + limb; inside a column the 32 bytes of
+//          block b start at 32 b: [t 0..3][k = 8t + 0,2,4,6,1,3,5,7]
+//   zero : col_stride bytes of zeros (only when several blocks share a fragment)
+//   zin  : [cols][nblk] int32   kBias - 8 * (sum of the column's bytes in the block)
+//   fex  : [cols][nblk] float   2^e (x 128 for the hi limb), 0 for blocks beyond K
+struct XLayout {
+  uint32_t col_stride, xq, zero, zin, fex, bytes;
+  uint32_t zs;  // bytes per column of zin / fex (padded so that the columns read together fall in different banks)
+  int nblk;
+};
+// zeroed = true when several blocks share an accumulator fragment (the lanes of the other blocks
+// read zeros); chunks = 64-wide K chunks of the slice
+__host__ __device__ inline XLayout x_layout(int cols, int chunks, bool zeroed) {
+  XLayout L;
+  L.nblk = chunks * 2;
+  const uint32_t raw = ((uint32_t)chunks * 64u + 127u) / 128u * 128u;
+  // Bank rule for the 64-bit activation loads: a half-warp (lane groups g = 0..3 or 4..7) reads at
+  // most two different columns plus the zero region, 32 bytes each.  Columns sit 32 bytes apart
+  // (mod 128); the zero region starts 64 bytes off (mod 128) and the upper half-warp enters it
+  // another 64 bytes further on.
+  L.col_stride = raw + 32u;
+  L.xq = 0;
+  L.zero = ((uint32_t)cols * L.col_stride + 127u) / 128u * 128u + 64u;
+  const uint32_t after = zeroed ? L.zero + raw + 128u : (uint32_t)cols * L.col_stride;
+  L.zin = (after + 127u) & ~127u;
+  L.zs = ((uint32_t)L.nblk * 4u + 127u) / 128u * 128u + 16u;
+  L.fex = L.zin + (uint32_t)cols * L.zs;
+  L.bytes = L.fex + (uint32_t)cols * L.zs;
+  return L;
+}
+// bytes of the zero region (to be cleared once per kernel)
+__host__ __device__ inline uint32_t x_zero_bytes(const XLayout& L) { return L.col_stride - 32u + 128u; }
+
+// Quantise 8 consecutive activations (one (block, t) group of a row) and store its limbs.
+// `v` are the final f32 values (norm applied).  The four lanes of a quad hold one 32-block.
+// Every lane of the warp must call this (shuffles); `valid` gates the stores.
+// LIMBS = 2: 15-bit values, q = 128 hi + lo.  LIMBS = 3: 22-bit values, q = 16384 h + 128 m + l
+// (h = q >> 14 in -128..127, m and l in 0..127).  Columns xq0, xq0 + col_stride, ... hold the limbs
+// from the most significant down; zin0 / fex0 likewise with stride zs.
+template <int LIMBS>
+__device__ __forceinline__ void quantise_group(const float (&v)[8], bool valid, uint32_t xq0, uint32_t col_stride,
+                                               uint32_t zin0, uint32_t fex0, uint32_t zs, int blk_off32, int t) {
+  constexpr int kBits = LIMBS == 3 ? 20 : 13;          // the block's largest magnitude lands in [2^kBits, 2^(kBits+1))
+  constexpr int kMaxQ = LIMBS == 3 ? 2097151 : 16383;
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  // 2^-e with e = exponent(amax) - kBits; a zero, denormal-tiny or non-finite block quantises to zeros
+  const int ex = (int)((__float_as_uint(amax) >> 23) & 0xffu);
+  const bool ok = ex >= 32 && ex <= 230;
+  const float inv = ok ? __uint_as_float((uint32_t)(254 + kBits - ex) << 23) : 0.f;  // 2^(kBits - (ex - 127))
+  const float step = ok ? __uint_as_float((uint32_t)(ex - kBits) << 23) : 0.f;      // 2^(ex - 127 - kBits)
+  int sum[LIMBS];
+  uint32_t w0[LIMBS], w1[LIMBS];  // bytes of k = 0,2,4,6 and of k = 1,3,5,7, per limb
+#pragma unroll
+  for (int l = 0; l < LIMBS; ++l) { sum[l] = 0; w0[l] = 0u; w1[l] = 0u; }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    int q = __float2int_rn(v[i] * inv);
+    q = max(-kMaxQ - 1, min(kMaxQ, q));
+#pragma unroll
+    for (int l = 0; l < LIMBS; ++l) {
+      const int sh = 7 * (LIMBS - 1 - l);
+      const int d = l == 0 ? (q >> sh) : ((q >> sh) & 127);
+      sum[l] += d;
+      const uint32_t byte = ((uint32_t)d & 0xffu) << (8 * (i >> 1));
+      if (i & 1) w1[l] |= byte; else w0[l] |= byte;
+    }
+  }
+#pragma unroll
+  for (int l = 0; l < LIMBS; ++l) {
+    sum[l] += __shfl_xor_sync(0xffffffffu, sum[l], 1);
+    sum[l] += __shfl_xor_sync(0xffffffffu, sum[l], 2);
+  }
+  if (valid) {
+    const int b4 = blk_off32 >> 3;  // block index * 4 bytes
+#pragma unroll
+    for (int l = 0; l < LIMBS; ++l) {
+      sts64(xq0 + (uint32_t)l * col_stride + blk_off32 + t * 8, w0[l], w1[l]);
+      if (t == 0) {
+        const float f = step * (float)(1 << (7 * (LIMBS - 1 - l)));
+        asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(zin0 + (uint32_t)l * zs + b4), "r"(kBias - 8u * (uint32_t)sum[l]) : "memory");
+        asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(fex0 + (uint32_t)l * zs + b4), "f"(f) : "memory");
+      }
+    }
+  }
+}
+
+// ---- the per-stage contraction ------------------------------------------------------------
+// One call processes this warp's share of a stage: `nc` chunks of 64 k of one 16-row tile, already
+// in shared memory at `wbase` (nibbles, 512 B per chunk) and `sbase` (scales, 64 B per chunk).
+// blk0 = index (inside the staged slice) of the stage's first block.  Warp `wi` of `NW` takes the
+// work items wi, wi + NW, ...; an item is max(G/2, 1) chunks.
+
+// G = 4: one activation row.  acc[0] += row g, acc[1] += row g+8 (partial over this lane's columns).
+template <int NW>
+__device__ __forceinline__ void consume_g4(float (&acc)[2], uint32_t wbase, uint32_t sbase, int nc, int blk0,
+                                           const XLayout& L, uint32_t xbase, int wi, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  const int limb = t >> 1;      // this lane's output columns: limb, blocks 2(t&1), 2(t&1)+1 of the item
+  const int myblk = g & 3;      // this lane's B column: limb g>>2, block g&3 of the item
+  const uint32_t xcol = xbase + L.xq + (uint32_t)(g >> 2) * L.col_stride + (uint32_t)t * 8u;
+  const uint32_t zcol = xbase + L.zero + (uint32_t)(g >> 2) * 64u + (uint32_t)t * 8u;
+  uint32_t xa[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) xa[j] = (myblk == j ? xcol : zcol) + (uint32_t)(blk0 + j) * 32u;
+  const uint32_t zin = xbase + L.zin + (uint32_t)limb * L.zs + (uint32_t)(blk0 + 2 * (t & 1)) * 4u;
+  const uint32_t fex = xbase + L.fex + (uint32_t)limb * L.zs + (uint32_t)(blk0 + 2 * (t & 1)) * 4u;
+  const int nitems = (nc + 1) >> 1;
+#pragma unroll 2
+  for (int it = wi; it < nitems; it += NW) {
+    const uint32_t wo = wbase + (uint32_t)it * 1024u + (uint32_t)lane * 16u;
+    const uint4 wA = lds128(wo);
+    const uint4 wB = lds128(wo + 512u);
+    const int ch = 2 * it + (t & 1);
+    uint2 s2 = lds64(sbase + (uint32_t)ch * 64u + (uint32_t)g * 8u);
+    if (ch >= nc) s2 = make_uint2(0u, 0u);  // a chunk past the stage's data: whatever the slot holds must not count
+    const uint2 z2 = lds64(zin + (uint32_t)it * 16u);
+    const uint2 f2 = lds64(fex + (uint32_t)it * 16u);
+    int d[4] = {(int)z2.x, (int)z2.y, (int)z2.x, (int)z2.y};
+    const uint32_t xo = (uint32_t)it * 128u;
+    uint2 b;
+    b = lds64(xa[0] + xo);
+    block_mma(d, wA.x, wA.y, b.x, b.y);
+    b = lds64(xa[1] + xo);
+    block_mma(d, wA.z, wA.w, b.x, b.y);
+    b = lds64(xa[2] + xo);
+    block_mma(d, wB.x, wB.y, b.x, b.y);
+    b = lds64(xa[3] + xo);
+    block_mma(d, wB.z, wB.w, b.x, b.y);
+    const float2 se = __half22float2(*reinterpret_cast<const __half2*>(&s2.x));  // (row g, row g+8) of the even block
+    const float2 so = __half22float2(*reinterpret_cast<const __half2*>(&s2.y));  // ... of the odd block
+    const float fe = __uint_as_float(f2.x), fo = __uint_as_float(f2.y);
+    acc[0] = fmaf(se.x * fe, unbias(d[0]), acc[0]);
+    acc[0] = fmaf(so.x * fo, unbias(d[1]), acc[0]);
+    acc[1] = fmaf(se.y * fe, unbias(d[2]), acc[1]);
+    acc[1] = fmaf(so.y * fo, unbias(d[3]), acc[1]);
+  }
+}
+
+// One activation row in three limbs (22 bits): the 8 columns hold (limb, block) for the TWO blocks of
+// a chunk (6 used); lane t < 3 owns limb t of both blocks, lane t = 3 idles.  acc[0] += row g,
+// acc[1] += row g+8.
+template <int NW>
+__device__ __forceinline__ void consume_m1l3(float (&acc)[2], uint32_t wbase, uint32_t sbase, int nc, int blk0,
+                                             const XLayout& L, uint32_t xbase, int wi, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  const int limb = min(t, 2);
+  const uint32_t xcol = xbase + L.xq + (uint32_t)(g >> 1) * L.col_stride + (uint32_t)t * 8u;  // B column g: limb g>>1, block g&1
+  const uint32_t zcol = xbase + L.zero + (uint32_t)(g >> 2) * 64u + (uint32_t)t * 8u;
+  uint32_t xa[2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) xa[j] = ((g < 6 && (g & 1) == j) ? xcol : zcol) + (uint32_t)(blk0 + j) * 32u;
+  const uint32_t zin = xbase + L.zin + (uint32_t)limb * L.zs + (uint32_t)blk0 * 4u;
+  const uint32_t fex = xbase + L.fex + (uint32_t)limb * L.zs + (uint32_t)blk0 * 4u;
+  const float live = t < 3 ? 1.f : 0.f;
+#pragma unroll 2
+  for (int it = wi; it < nc; it += NW) {
+    const uint4 w = lds128(wbase + (uint32_t)it * 512u + (uint32_t)lane * 16u);
+    const uint2 s2 = lds64(sbase + (uint32_t)it * 64u + (uint32_t)g * 8u);
+    const uint2 z2 = lds64(zin + (uint32_t)it * 8u);
+    const uint2 f2 = lds64(fex + (uint32_t)it * 8u);
+    int d[4] = {(int)z2.x, (int)z2.y, (int)z2.x, (int)z2.y};
+    const uint32_t xo = (uint32_t)it * 64u;
+    uint2 b;
+    b = lds64(xa[0] + xo);
+    block_mma(d, w.x, w.y, b.x, b.y);
+    b = lds64(xa[1] + xo);
+    block_mma(d, w.z, w.w, b.x, b.y);
+    const float2 se = __half22float2(*reinterpret_cast<const __half2*>(&s2.x));
+    const float2 so = __half22float2(*reinterpret_cast<const __half2*>(&s2.y));
+    const float fe = __uint_as_float(f2.x) * live, fo = __uint_as_float(f2.y) * live;
+    acc[0] = fmaf(se.x * fe, unbias(d[0]), acc[0]);
+    acc[0] = fmaf(so.x * fo, unbias(d[1]), acc[0]);
+    acc[1] = fmaf(se.y * fe, unbias(d[2]), acc[1]);
+    acc[1] = fmaf(so.y * fo, unbias(d[3]), acc[1]);
+  }
+}
+
+// G = 2: two activation rows; columns = (row, limb) x 2 blocks; an item is one chunk.
+// This lane's output columns: column pair t = (row t>>1, limb t&1), blocks 0 and 1 of the chunk.
+template <int NW>
+__device__ __forceinline__ void consume_g2(float (&acc)[2], uint32_t wbase, uint32_t sbase, int nc, int blk0,
+                                           const XLayout& L, uint32_t xbase, int wi, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  const int myblk = g & 1;
+  const uint32_t xcol = xbase + L.xq + (uint32_t)(g >> 1) * L.col_stride + (uint32_t)t * 8u;
+  const uint32_t zcol = xbase + L.zero + (uint32_t)(g >> 2) * 64u + (uint32_t)t * 8u;
+  uint32_t xa[2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) xa[j] = (myblk == j ? xcol : zcol) + (uint32_t)(blk0 + j) * 32u;
+  const uint32_t zin = xbase + L.zin + (uint32_t)t * L.zs + (uint32_t)blk0 * 4u;
+  const uint32_t fex = xbase + L.fex + (uint32_t)t * L.zs + (uint32_t)blk0 * 4u;
+#pragma unroll 2
+  for (int it = wi; it < nc; it += NW) {
+    const uint4 w = lds128(wbase + (uint32_t)it * 512u + (uint32_t)lane * 16u);
+    const uint2 s2 = lds64(sbase + (uint32_t)it * 64u + (uint32_t)g * 8u);
+    const uint2 z2 = lds64(zin + (uint32_t)it * 8u);
+    const uint2 f2 = lds64(fex + (uint32_t)it * 8u);
+    int d[4] = {(int)z2.x, (int)z2.y, (int)z2.x, (int)z2.y};
+    const uint32_t xo = (uint32_t)it * 64u;
+    uint2 b;
+    b = lds64(xa[0] + xo);
+    block_mma(d, w.x, w.y, b.x, b.y);
+    b = lds64(xa[1] + xo);
+    block_mma(d, w.z, w.w, b.x, b.y);
+    const float2 se = __half22float2(*reinterpret_cast<const __half2*>(&s2.x));
+    const float2 so = __half22float2(*reinterpret_cast<const __half2*>(&s2.y));
+    const float fe = __uint_as_float(f2.x), fo = __uint_as_float(f2.y);
+    acc[0] = fmaf(se.x * fe, unbias(d[0]), acc[0]);
+    acc[0] = fmaf(so.x * fo, unbias(d[1]), acc[0]);
+    acc[1] = fmaf(se.y * fe, unbias(d[2]), acc[1]);
+    acc[1] = fmaf(so.y * fo, unbias(d[3]), acc[1]);
+  }
+}
+
+// G = 1: NT tiles of 8 columns = 4 activation rows each; lane t of tile nt owns row 4 nt + t, both
+// limbs.  acc[nt][0] += row g of the weights, acc[nt][1] += row g+8.  An item is one chunk.
+template <int NW, int NT>
+__device__ __forceinline__ void consume_g1(float (&acc)[NT][2], uint32_t wbase, uint32_t sbase, int nc, int blk0,
+                                           const XLayout& L, uint32_t xbase, int cols, int wi, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  uint32_t xa[NT], za[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    // lanes whose B column lies beyond the activations read an existing column: their outputs are never used
+    const int col = min(nt * 8 + g, cols - 1);
+    xa[nt] = xbase + L.xq + (uint32_t)col * L.col_stride + (uint32_t)t * 8u + (uint32_t)blk0 * 32u;
+    const int oc = min(nt * 8 + 2 * t, cols - 2);  // this lane's output columns (hi, lo) of row 4 nt + t
+    za[nt] = (uint32_t)oc * L.zs + (uint32_t)blk0 * 4u;
+  }
+  const uint32_t zin = xbase + L.zin, fex = xbase + L.fex;
+  const uint32_t lo_off = L.zs;  // column + 1
+#pragma unroll 2
+  for (int it = wi; it < nc; it += NW) {
+    const uint4 w = lds128(wbase + (uint32_t)it * 512u + (uint32_t)lane * 16u);
+    const uint2 s2 = lds64(sbase + (uint32_t)it * 64u + (uint32_t)g * 8u);
+    const float2 se = __half22float2(*reinterpret_cast<const __half2*>(&s2.x));
+    const float2 so = __half22float2(*reinterpret_cast<const __half2*>(&s2.y));
+    const uint32_t m = 0x0f0f0f0fu;
+    const uint32_t e0 = w.x & m, e1 = w.y & m, e2 = (w.x >> 4) & m, e3 = (w.y >> 4) & m;
+    const uint32_t o0 = w.z & m, o1 = w.w & m, o2 = (w.z >> 4) & m, o3 = (w.w >> 4) & m;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const uint32_t zo = za[nt] + (uint32_t)it * 8u;
+      const uint2 zh = lds64(zin + zo), zl = lds64(zin + zo + lo_off);  // (even block, odd block) of hi / lo
+      const uint2 fh = lds64(fex + zo);                                  // 2^e * 128 of (even, odd); lo factor = / 128
+      const uint2 be = lds64(xa[nt] + (uint32_t)it * 64u);
+      const uint2 bo = lds64(xa[nt] + (uint32_t)it * 64u + 32u);
+      int de[4] = {(int)zh.x, (int)zl.x, (int)zh.x, (int)zl.x};
+      int dd[4] = {(int)zh.y, (int)zl.y, (int)zh.y, (int)zl.y};
+      imma(de, e0, e1, e2, e3, be.x, be.y);
+      imma(dd, o0, o1, o2, o3, bo.x, bo.y);
+      const float fe = __uint_as_float(fh.x), fo = __uint_as_float(fh.y);
+      // 128 hi + lo, in units of 2^e / 128 ... fe already carries the 128: v = fe * (hi + lo / 128)
+      const float ve0 = fmaf(unbias(de[1]), 0.0078125f, unbias(de[0])), ve1 = fmaf(unbias(de[3]), 0.0078125f, unbias(de[2]));
+      const float vo0 = fmaf(unbias(dd[1]), 0.0078125f, unbias(dd[0])), vo1 = fmaf(unbias(dd[3]), 0.0078125f, unbias(dd[2]));
+      acc[nt][0] = fmaf(se.x * fe, ve0, acc[nt][0]);
+      acc[nt][0] = fmaf(so.x * fo, vo0, acc[nt][0]);
+      acc[nt][1] = fmaf(se.y * fe, ve1, acc[nt][1]);
+      acc[nt][1] = fmaf(so.y * fo, vo1, acc[nt][1]);
+    }
+  }
+}
+
+}  // namespace q4s8

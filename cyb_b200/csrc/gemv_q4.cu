@@ -302,7 +302,7 @@ int32_t qeng_gemm_q4_decode(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
                             cudaStream_t stream) {
   {
     bool handled = false;
-    int32_t rc = qeng_gemm_q4_stream(ctx, w, x, x_dtype, M, ldx, y, ldy, split_f32, fuse, stream, &handled);
+    int32_t rc = qeng_gemm_q4_stream(ctx, w, x, x_dtype, M, ldx, y, ldy, fuse, stream, &handled);
     if (handled || rc != QENG_OK) return rc;
   }
   const int split = (x_dtype == QENG_F32 && split_f32) ? 1 : 0;
@@ -350,8 +350,9 @@ int32_t qeng_gemm_q4(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t
     return qeng_gemm_q4_prefill(ctx, w, x, x_dtype, M, ldx, y, ldy, (flags & QENG_GEMM_ACCUMULATE) ? 1 : 0, (cudaStream_t)stream);
   qeng_gemm_fuse fuse;
   fuse.epilogue = (flags & QENG_GEMM_ACCUMULATE) ? QENG_EPI_ACCUM : QENG_EPI_STORE;
+  fuse.two_limbs = (flags & QENG_GEMM_FAST_F16) != 0;
   const bool split = x_dtype == QENG_F32 && !(flags & QENG_GEMM_FAST_F16);
-  const int64_t step = split ? 16 : 32;
+  const int64_t step = 16;  // rows per pass over the weights
   const size_t esz = x_dtype == QENG_F32 ? 4 : 2;
   for (int64_t m0 = 0; m0 < M; m0 += step) {
     int64_t mm = M - m0 < step ? M - m0 : step;

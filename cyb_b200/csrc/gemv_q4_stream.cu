@@ -3,29 +3,30 @@
 // One persistent CTA per SM: a producer warp and 16 consumer warps around a
 // ring of shared-memory stages.  The producer walks this CTA's row tiles
 // (16 rows x K, contiguous in the packed layout) and copies them stage by
-// stage (64 chunks: 32 KB of nibbles + 4 KB of scales) with bulk asynchronous
-// copies (cp.async.bulk, completion counted on an mbarrier), so ~170 KB per SM
-// are in flight without holding registers and independent of what the
-// consumers are doing.  Consumers take the chunks of a stage round-robin, read
-// them with conflict-free 128-bit shared loads, unpack in registers and
-// contract on the tensor pipe (mma.sync.m16n8k16, weights = A, activations = B;
-// arithmetic as in gemv_q4.cu).  At the end of a row tile the 16 partial
-// accumulators meet in shared memory (one named barrier, double-buffered) and
-// one warp applies the fused epilogue.
+// stage (up to 64 chunks: 32 KB of nibbles + 4 KB of scales) with bulk
+// asynchronous copies (cp.async.bulk, completion counted on an mbarrier), so
+// ~170 KB per SM are in flight without holding registers and independent of
+// what the consumers are doing.  Consumers take the chunks of a stage
+// round-robin, read them with conflict-free 128-bit shared loads, unpack in
+// registers and contract on the tensor pipe with integer MMAs against the
+// activations quantised to two signed bytes per value (gemm_q4_s8.cuh has the
+// arithmetic).  At the end of a row tile the 16 partial accumulators meet in
+// shared memory (one named barrier, double-buffered) and one warp applies the
+// fused epilogue.
+//
+// Up to 4 activation rows keep the whole K range staged; more rows (up to 16
+// per launch) are staged in K slices, the weights of a slice streamed for all
+// of the CTA's tiles and the partial sums kept in shared memory between
+// slices, so the weights still cross HBM once per launch.
 //
 // HBM-bound: algorithmic bytes = N*K*0.5625 + activations + outputs.
 #include <cstdlib>
-#include "qeng_internal.h"
+#include "gemm_q4_s8.cuh"
 
 namespace {
+using namespace q4s8;
 
-constexpr int kSC = 64;                        // chunks (of 64 k) per stage
-constexpr int kStageBytes = kSC * (512 + 64);  // nibbles then scales: 36864
-constexpr int kCW = 16;                        // consumer warps
-constexpr int kCT = kCW * 32;                  // consumer threads
-constexpr int kThreadsS = kCT + 32;            // + producer warp
-constexpr int kMaxStages = 12;
-constexpr int kGroups = 3;                     // groups of 8 k one consumer thread stages: K <= 8 * kGroups * kCT
+constexpr int kGroups = 3;  // groups of 8 k one consumer thread stages in the single-slice mode: K <= 8 * kGroups * kCT
 
 struct StreamParams {
   // the matrix multiplied next (may be null): its tiles are requested into L2 once this
@@ -40,119 +41,57 @@ struct StreamParams {
   const void* x;
   int x_dtype;
   long long ldx;
-  int M, cols, split;
+  int M, cols;
   float* y;
   long long ldy;
   const float* gamma;
   float eps;
   int epilogue;
   const float* resid;
-  int nstages;
+  int nstages;        // ring slots
+  int stage_chunks;   // chunks per ring slot
+  int slice_chunks;   // chunks of K staged at once (= all of them in single-slice mode)
+  int nslices;
   int32_t* status;
   qeng_qkv_epi qkv;
 };
 
-// d = a.b + c (m16n8k16, f16 operands, f32 accumulate)
-__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1, float c0, float c1, float c2, float c3) {
-  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};\n"
-      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(c2), "f"(c3));
-}
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-// One attempt: the hardware may park the thread until the phase completes or the hinted time passes.
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(1000u)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: gives up (false) two seconds after the first failed attempt; a healthy wait ends
-// in microseconds.  The clock is read once per 64 attempts.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
-  unsigned long long t0;
-  asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t0));
-  for (;;) {
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    unsigned long long t1;
-    asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t1));
-    if (t1 - t0 > 2000000000ull) return false;
-  }
-}
-// 1-D bulk copy global -> shared, completion counted in bytes on the mbarrier
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ uint2 lds64(uint32_t addr) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ float2 lds64f(uint32_t addr) {
-  float2 v;
-  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(v.x), "=f"(v.y) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ void l2_prefetch(const void* gptr, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(gptr), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(kCT) : "memory"); }
 // the warps of one tile group (named barriers 2, 3, ...)
 template <int GW>
 __device__ __forceinline__ void group_sync(int gi) { asm volatile("bar.sync %0, %1;\n" ::"r"(2 + gi), "n"(GW * 32) : "memory"); }
 
-__device__ __forceinline__ float act_f32(const void* x, int dtype, long long i) {
-  if (dtype == QENG_F32) return reinterpret_cast<const float*>(x)[i];
-  if (dtype == QENG_F16) return __half2float(reinterpret_cast<const __half*>(x)[i]);
-  return __uint_as_float((uint32_t)reinterpret_cast<const uint16_t*>(x)[i] << 16);
-}
-
-__device__ __forceinline__ uint32_t h2bits(float a, float b) {
-  __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
-
-template <int NT, int kTG>
-__global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const StreamParams p) {
-  constexpr int kGW = kCW / kTG;  // warps per tile group
+// MODE: how the 8 MMA columns are used (gemm_q4_s8.cuh)
+//   kM1L3: one activation row in three limbs (22 bits), two blocks per accumulator fragment
+//   kM1L2: one row in two limbs (15 bits), four blocks per fragment
+//   kM2L2: two rows in two limbs, two blocks per fragment
+//   kMN  : NT tiles of four rows in two limbs, one block per fragment
+enum { kM1L3 = 0, kM1L2 = 1, kM2L2 = 2, kMN = 3 };
+template <int MODE, int NT, int kTG>
+__global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const StreamParams p) {
+  constexpr int kGW = kCW / kTG;        // warps per tile group
+  constexpr int kMR = MODE == kMN ? 4 * NT : (MODE == kM2L2 ? 2 : 1);  // activation rows the fragment layout holds
+  constexpr int kLimbs = MODE == kM1L3 ? 3 : 2;
+  constexpr bool kZeroed = MODE != kMN;
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  const int Kp = p.nchunks * 64;
-  const int CS = Kp + 32;  // halves per staged activation column (64-byte skew)
-  const int nblk = p.nchunks * 2;
   const int NS = p.nstages;
-  // carve: ring | barriers | activations | block sums | reduction buffers
+  const uint32_t stage_bytes = (uint32_t)p.stage_chunks * 576u;
+  const int sl_alloc = MODE == kM1L2 ? (p.slice_chunks + 1) & ~1 : p.slice_chunks;
+  const XLayout L = x_layout(p.cols, sl_alloc, kZeroed);
+  // carve: ring | activations (128-byte aligned) | reduction buffers | slice accumulators | barriers
   unsigned char* ring = smem;
-  unsigned char* after_ring = smem + (size_t)NS * kStageBytes;
-  uint64_t* full = reinterpret_cast<uint64_t*>(after_ring);
+  unsigned char* xreg = smem + (((size_t)NS * stage_bytes + 127) & ~(size_t)127);
+  float* red = reinterpret_cast<float*>(xreg + L.bytes);          // [kTG][2][kGW][kMR * 16]
+  constexpr int red_stride = kMR * 16;
+  float* accsm = red + kTG * 2 * kGW * red_stride;                 // [tiles of this CTA][kMR * 16] (several slices only)
+  const int my_tiles = p.ntiles > (int)blockIdx.x ? (p.ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  const int max_tiles = (p.ntiles + (int)gridDim.x - 1) / (int)gridDim.x;
+  uint64_t* full = reinterpret_cast<uint64_t*>(accsm + (p.nslices > 1 ? (size_t)max_tiles * red_stride : 0));
   uint64_t* empty = full + kMaxStages;
-  __half* xs_h = reinterpret_cast<__half*>(after_ring + 2 * kMaxStages * 8 + 64);
-  float* xsum = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(xs_h) + (size_t)p.cols * CS * 2);
-  float* red = xsum + (size_t)nblk * 8 * NT;  // [2][kCW][16 * 8 * NT]
-  __shared__ float warp_part[4 * kCW], oscale[32];
+  __shared__ float warp_part[2 * kCW], rinv[16];
+  const uint32_t xbase = smem_u32(xreg);
+  (void)my_tiles;
 
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");  // the next kernel may start its own weight stream
   if (tid == 0) {
@@ -164,29 +103,31 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
   }
   __syncthreads();
 
-  const int stages_per_tile = (p.nchunks + kSC - 1) / kSC;
+  const int NSg = NS / kTG;  // ring slots per tile group; group gi owns slots [gi * NSg, (gi + 1) * NSg)
 
   if (warp == kCW) {
-    // ===== producer: stream this CTA's row tiles through the ring ==================
+    // ===== producer: stream this CTA's row tiles through the ring, slice by slice ==========
     if (lane == 0) {
       bool failed = false;
-      const int NSg = NS / kTG;  // ring slots per tile group; group g owns slots [g * NSg, (g + 1) * NSg)
       int tcount = 0;
-      for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++tcount) {
-        const int grp = tcount % kTG;
-        int use = (tcount / kTG) * stages_per_tile;  // stage uses of this group so far
-        for (int st = 0; st < stages_per_tile; ++st, ++use) {
-          const int s = grp * NSg + use % NSg;
-          const uint32_t ph = (uint32_t)(use / NSg) & 1u;
-          if (!failed && !mbar_wait(smem_u32(empty + s), ph ^ 1u)) failed = true;
-          const int c0 = st * kSC;
-          const int nc = min(kSC, p.nchunks - c0);
-          const uint32_t bar = smem_u32(full + s);
-          const uint32_t dst = smem_u32(ring + (size_t)s * kStageBytes);
-          const size_t chunk = (size_t)tile * p.nchunks + c0;
-          mbar_expect_tx(bar, (uint32_t)nc * 576u);
-          bulk_g2s(dst, p.qs + chunk * 32, (uint32_t)nc * 512u, bar);
-          bulk_g2s(dst + kSC * 512, p.sc + chunk * 8, (uint32_t)nc * 64u, bar);
+      int use[4] = {0, 0, 0, 0};  // stage uses per tile group
+      for (int sl = 0; sl < p.nslices; ++sl) {
+        const int cs0 = sl * p.slice_chunks, cs1 = min(p.nchunks, cs0 + p.slice_chunks);
+        for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++tcount) {
+          const int grp = tcount % kTG;
+          for (int c0 = cs0; c0 < cs1; c0 += p.stage_chunks) {
+            const int u = use[grp]++;
+            const int s = grp * NSg + u % NSg;
+            const uint32_t ph = (uint32_t)(u / NSg) & 1u;
+            if (!failed && !mbar_wait(smem_u32(empty + s), ph ^ 1u)) failed = true;
+            const int nc = min(p.stage_chunks, cs1 - c0);
+            const uint32_t bar = smem_u32(full + s);
+            const uint32_t dst = smem_u32(ring) + (uint32_t)s * stage_bytes;
+            const size_t chunk = (size_t)tile * p.nchunks + c0;
+            mbar_expect_tx(bar, (uint32_t)nc * 576u);
+            bulk_g2s(dst, p.qs + chunk * 32, (uint32_t)nc * 512u, bar);
+            bulk_g2s(dst + (uint32_t)p.stage_chunks * 512u, p.sc + chunk * 8, (uint32_t)nc * 64u, bar);
+          }
         }
       }
       if (failed) atomicExch(p.status, 4);
@@ -209,322 +150,267 @@ __global__ void __launch_bounds__(kThreadsS, 1) gemv_q4_stream_kernel(const Stre
   // The weights never change, so only the consumers wait for the kernel that produced the
   // activations (a no-op unless launched with programmatic stream serialization).
   asm volatile("griddepcontrol.wait;\n" ::: "memory");
-  // ---- stage the activations as f16 (hi | lo columns), fused RMSNorm -----------------
-  // Row m is scaled by a power of two 2^sh so that its largest magnitude lands in
-  // [2^14, 2^15): the f16 split hi + lo then never touches the subnormal range for
-  // values that matter, and the slots that meet a code pre-multiplied by 16 (see the
-  // unpacking below) can hold x/16 exactly.  The epilogue multiplies by 2^-sh.
-  // One thread owns up to kGroups groups of 8 consecutive k (loaded once, kept in
-  // registers across the reduction); the 4 groups of a 32-block sit in one quad.
-  const int ngroups = Kp / 8;
+  // the zero region other blocks' lanes read (several blocks per fragment)
+  if (kZeroed)
+    for (uint32_t o = (uint32_t)tid * 16u; o < x_zero_bytes(L); o += kCT * 16u)
+      asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(xbase + L.zero + o), "r"(0u) : "memory");
+
   const bool vec_ok = p.x_dtype == QENG_F32 && ((reinterpret_cast<uintptr_t>(p.x) | (uintptr_t)(p.ldx * 4)) & 15) == 0 &&
                       (p.gamma == nullptr || (reinterpret_cast<uintptr_t>(p.gamma) & 15) == 0) && (p.K & 7) == 0;
-  // The raw values of row m + 1 are requested before row m is reduced and converted, so with
-  // several activation rows only the first one waits for memory.
-  auto load_row = [&](int m, float (&dst)[kGroups][8]) {
+  // eight consecutive activations of row m starting at k0 (zero beyond K)
+  auto load8 = [&](int m, int k0, float (&dst)[8]) {
 #pragma unroll
-    for (int j = 0; j < kGroups; ++j) {
-      const int k0 = (tid + j * kCT) * 8;
+    for (int i = 0; i < 8; ++i) dst[i] = 0.f;
+    if (k0 < p.K) {
+      if (vec_ok) {
+        const float4* xp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x) + (long long)m * p.ldx + k0);
+        const float4 a = xp[0], b = xp[1];
+        dst[0] = a.x; dst[1] = a.y; dst[2] = a.z; dst[3] = a.w;
+        dst[4] = b.x; dst[5] = b.y; dst[6] = b.z; dst[7] = b.w;
+      } else {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) dst[j][i] = 0.f;
-      if (k0 < p.K) {
-        if (vec_ok) {
-          const float4* xp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x) + (long long)m * p.ldx + k0);
-          const float4 a = xp[0], b = xp[1];
-          dst[j][0] = a.x; dst[j][1] = a.y; dst[j][2] = a.z; dst[j][3] = a.w;
-          dst[j][4] = b.x; dst[j][5] = b.y; dst[j][6] = b.z; dst[j][7] = b.w;
-        } else {
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-            if (k0 + i < p.K) dst[j][i] = act_f32(p.x, p.x_dtype, (long long)m * p.ldx + k0 + i);
-        }
+        for (int i = 0; i < 8; ++i)
+          if (k0 + i < p.K) dst[i] = act_f32(p.x, p.x_dtype, (long long)m * p.ldx + k0 + i);
       }
     }
   };
-  float nv[kGroups][8];
-  load_row(0, nv);
-  for (int m = 0; m < p.M; ++m) {
-    float v[kGroups][8];
+  auto gamma8 = [&](int k0, float mul, float (&v)[8]) {
+    if (p.gamma == nullptr || k0 >= p.K) return;
+    if (vec_ok) {
+      const float4* gp = reinterpret_cast<const float4*>(p.gamma + k0);
+      const float4 a = gp[0], b = gp[1];
+      v[0] *= a.x * mul; v[1] *= a.y * mul; v[2] *= a.z * mul; v[3] *= a.w * mul;
+      v[4] *= b.x * mul; v[5] *= b.y * mul; v[6] *= b.z * mul; v[7] *= b.w * mul;
+    } else {
 #pragma unroll
-    for (int j = 0; j < kGroups; ++j)
+      for (int i = 0; i < 8; ++i)
+        if (k0 + i < p.K) v[i] *= p.gamma[k0 + i] * mul;
+    }
+  };
+  // quantise the group at slice-local group index `grp` (block grp / 4, quad lane grp % 4) of row m
+  auto put = [&](int m, int grp, const float (&v)[8], bool valid) {
+    const uint32_t c0 = (uint32_t)(kLimbs * m);
+    quantise_group<kLimbs>(v, valid, xbase + L.xq + c0 * L.col_stride, L.col_stride, xbase + L.zin + c0 * L.zs,
+                           xbase + L.fex + c0 * L.zs, L.zs, (grp >> 2) * 32, grp & 3);
+  };
+  const int ngroups = L.nblk * 4;  // (block, quad lane) groups of the staged slice, padding included
+
+  if (p.nslices == 1) {
+    // ---- whole K staged once; a thread keeps its groups in registers across the norm's reduction.
+    // The raw values of row m + 1 are requested before row m is reduced and converted, so with
+    // several activation rows only the first one waits for memory.
+    float nv[kGroups][8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[j][i] = nv[j][i];
-    if (m + 1 < p.M) load_row(m + 1, nv);
-    float ss = 0.f, amax = 0.f;
+    for (int j = 0; j < kGroups; ++j) load8(0, (tid + j * kCT) * 8, nv[j]);
+    for (int m = 0; m < p.M; ++m) {
+      float v[kGroups][8];
 #pragma unroll
-    for (int j = 0; j < kGroups; ++j) {
-      const int k0 = (tid + j * kCT) * 8;
-      if (k0 < p.K) {
+      for (int j = 0; j < kGroups; ++j)
 #pragma unroll
-        for (int i = 0; i < 8; ++i) ss = fmaf(v[j][i], v[j][i], ss);
-        if (p.gamma != nullptr) {
-          if (vec_ok) {
-            const float4* gp = reinterpret_cast<const float4*>(p.gamma + k0);
-            const float4 a = gp[0], b = gp[1];
-            v[j][0] *= a.x; v[j][1] *= a.y; v[j][2] *= a.z; v[j][3] *= a.w;
-            v[j][4] *= b.x; v[j][5] *= b.y; v[j][6] *= b.z; v[j][7] *= b.w;
-          } else {
+        for (int i = 0; i < 8; ++i) v[j][i] = nv[j][i];
+      if (m + 1 < p.M) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-              if (k0 + i < p.K) v[j][i] *= p.gamma[k0 + i];
-          }
+        for (int j = 0; j < kGroups; ++j) load8(m + 1, (tid + j * kCT) * 8, nv[j]);
+      }
+      float rs = 1.f;
+      if (p.gamma != nullptr) {
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < kGroups; ++j)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ss = fmaf(v[j][i], v[j][i], ss);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        float* wp = warp_part + (m & 1) * kCW;  // double-buffered: one barrier per row
+        if (lane == 0) wp[warp] = ss;
+        consumer_sync();
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < kCW; ++w) tot += wp[w];
+        rs = rsqrtf(tot / (float)p.K + p.eps);
+      }
+#pragma unroll
+      for (int j = 0; j < kGroups; ++j) {
+        const int grp = tid + j * kCT;
+        if ((grp & ~31) < ngroups) {  // whole warps take part (shuffles); ngroups is a multiple of 8
+          gamma8(grp * 8, rs, v[j]);
+          put(m, grp, v[j], grp < ngroups);
         }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
       }
     }
+  } else if (p.gamma != nullptr) {
+    // ---- several slices: 1/rms of every row first (the slices are quantised as they come)
+    for (int m = 0; m < p.M; ++m) {
+      float ss = 0.f;
+      for (int k0 = tid * 8; k0 < p.K; k0 += kCT * 8) {
+        float v[8];
+        load8(m, k0, v);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    }
-    float* wp = warp_part + (m & 1) * (2 * kCW);  // double-buffered: one barrier per row
-    if (lane == 0) {
-      wp[warp] = ss;
-      wp[kCW + warp] = amax;
-    }
-    consumer_sync();
-    float tot = 0.f, mx = 0.f;
-#pragma unroll
-    for (int w = 0; w < kCW; ++w) {
-      tot += wp[w];
-      mx = fmaxf(mx, wp[kCW + w]);
-    }
-    float rs = 1.f;
-    if (p.gamma != nullptr) {
-      rs = rsqrtf(tot / (float)p.K + p.eps);
-      mx *= rs;
-    }
-    int sh = 0;
-    if (mx > 0.f && mx < 3.0e38f) sh = 14 - (((int)(__float_as_uint(mx) >> 23) & 0xff) - 127);
-    sh = max(-100, min(100, sh));
-    const float mul = rs * __uint_as_float((uint32_t)(sh + 127) << 23);
-    if (tid == 0) oscale[m] = __uint_as_float((uint32_t)(127 - sh) << 23);
-    const int colh = p.split ? 2 * m : m;
-#pragma unroll
-    for (int j = 0; j < kGroups; ++j) {
-      const int grp = tid + j * kCT;
-      // whole warps take part (the block sums use shuffles); ngroups is a multiple of 8, so a quad
-      // is either entirely valid or entirely past the end
-      if ((grp & ~31) < ngroups) {
-        const bool valid = grp < ngroups;
-        const int k0 = grp * 8;
-        float a[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float t0 = v[j][i] * mul;
-          a[i] = (i & 1) ? t0 * 0.0625f : t0;  // odd k of the group meet codes pre-multiplied by 16
-        }
-        // order 0,4,1,5,2,6,3,7: one 128-bit shared load yields the B registers of both MMAs of a block
-        uint4 hi;
-        hi.x = h2bits(a[0], a[4]); hi.y = h2bits(a[1], a[5]); hi.z = h2bits(a[2], a[6]); hi.w = h2bits(a[3], a[7]);
-        const __half2* hh = reinterpret_cast<const __half2*>(&hi);
-        const float2 a0 = __half22float2(hh[0]), a1 = __half22float2(hh[1]), a2 = __half22float2(hh[2]),
-                     a3 = __half22float2(hh[3]);
-        // block sums carry the zero point: -8 * 2^-24 * sum of the values the MMA effectively sees
-        float hsum = ((a0.x + a0.y) + (a2.x + a2.y)) + 16.f * ((a1.x + a1.y) + (a3.x + a3.y));
-        float lsum = 0.f;
-        if (valid) *reinterpret_cast<uint4*>(xs_h + (size_t)colh * CS + k0) = hi;
-        if (p.split) {
-          uint4 lo;
-          lo.x = h2bits(a[0] - a0.x, a[4] - a0.y); lo.y = h2bits(a[1] - a1.x, a[5] - a1.y);
-          lo.z = h2bits(a[2] - a2.x, a[6] - a2.y); lo.w = h2bits(a[3] - a3.x, a[7] - a3.y);
-          const __half2* ll = reinterpret_cast<const __half2*>(&lo);
-          const float2 b0 = __half22float2(ll[0]), b1 = __half22float2(ll[1]), b2 = __half22float2(ll[2]),
-                       b3 = __half22float2(ll[3]);
-          lsum = ((b0.x + b0.y) + (b2.x + b2.y)) + 16.f * ((b1.x + b1.y) + (b3.x + b3.y));
-          if (valid) *reinterpret_cast<uint4*>(xs_h + (size_t)(colh + 1) * CS + k0) = lo;
-        }
-        hsum += __shfl_xor_sync(0xffffffffu, hsum, 1);
-        hsum += __shfl_xor_sync(0xffffffffu, hsum, 2);
-        lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
-        lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
-        if (valid && (lane & 3) == 0) {
-          const int blk = grp >> 2;
-          xsum[blk * (8 * NT) + colh] = hsum * (-8.0f * 5.9604644775390625e-08f);
-          if (p.split) xsum[blk * (8 * NT) + colh + 1] = lsum * (-8.0f * 5.9604644775390625e-08f);
-        }
+        for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
       }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      float* wp = warp_part + (m & 1) * kCW;
+      if (lane == 0) wp[warp] = ss;
+      consumer_sync();
+      float tot = 0.f;
+#pragma unroll
+      for (int w = 0; w < kCW; ++w) tot += wp[w];
+      if (tid == 0) rinv[m] = rsqrtf(tot / (float)p.K + p.eps);
     }
   }
   consumer_sync();
 
-  // ---- main loop over this CTA's row tiles -------------------------------------------
+  // ---- main loop: slices x this CTA's row tiles --------------------------------------------
   // The consumer warps form kTG independent groups that take the CTA's tiles in turn: while one
-  // group reduces a tile and waits for its next stage, the other keeps the pipes busy.
+  // group reduces a tile and waits for its next stage, the other keeps the pipes busy.  Each group
+  // owns NS / kTG consecutive ring slots and is the only waiter on their barriers, so a barrier's
+  // phases are seen strictly in order however far the groups drift apart.
   const int gi = warp / kGW, wi = warp % kGW;
-  // Lanes whose B column lies beyond the activations read an existing column instead:
-  // every load stays in bounds and unpredicated, and their output columns are ignored.
-  // All addresses are 32-bit shared-space byte addresses advanced by compile-time strides.
-  uint32_t xcol[NT];
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt)
-    xcol[nt] = smem_u32(xs_h) + (uint32_t)((min(nt * 8 + g, p.cols - 1) * CS + t * 8) * 2) + (uint32_t)wi * 128u;
-  const uint32_t zcol = smem_u32(xsum) + (uint32_t)t * 8u + (uint32_t)wi * (2u * 32u * NT);
-  const uint32_t ring_w = smem_u32(ring) + (uint32_t)wi * 512u + (uint32_t)lane * 16u;
-  const uint32_t ring_s = smem_u32(ring) + kSC * 512u + (uint32_t)wi * 64u + (uint32_t)g * 8u;
-  const int red_stride = 16 * 8 * NT;  // floats per warp per buffer
   bool failed = false;
-  // Each group owns NS / kTG consecutive ring slots and is the only waiter on their barriers, so a
-  // barrier's phases are seen strictly in order however far the groups drift apart.
-  const int NSg = NS / kTG, s_first = gi * NSg, s_end = s_first + NSg;
-  int s = s_first, buf = 0, tcount = 0;
-  uint32_t ph = 0;
-  for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++tcount) {
-    if ((tcount % kTG) != gi) continue;  // another group's tile
-    float acc[NT][4];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-
-    uint32_t xo = 0, zo = 0;  // byte offsets of the current stage along k
-    for (int st = 0; st < stages_per_tile; ++st) {
-      if (!failed && !mbar_wait(smem_u32(full + s), ph)) failed = true;
-      const int nc = min(kSC, p.nchunks - st * kSC);
-      const uint32_t wb = ring_w + (uint32_t)s * kStageBytes;
-      const uint32_t sb = ring_s + (uint32_t)s * kStageBytes;
-#pragma unroll
-      for (int rep = 0; rep < kSC / kGW; ++rep) {
-        if (wi + rep * kGW < nc) {
-          const uint4 w = lds128(wb + rep * (kGW * 512));
-          const uint2 s2 = lds64(sb + rep * (kGW * 64));
-#pragma unroll
-          for (int b1 = 0; b1 < 2; ++b1) {
-            // A fragments: a 4-bit code c in the low mantissa bits of an f16 is the subnormal
-            // c*2^-24; one nibble higher it is 16c*2^-24 (its activation slot holds x/16).
-            const uint32_t w0 = b1 ? w.z : w.x, w1 = b1 ? w.w : w.y;
-            const uint32_t v0 = w0 >> 8, v1 = w1 >> 8;
-            const uint32_t mlo = 0x000f000fu, mhi = 0x00f000f0u;
-            const uint32_t sbits = b1 ? s2.y : s2.x;
-            const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&sbits));
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-              const uint4 xb = lds128(xcol[nt] + xo + (rep * kGW * 128 + b1 * 64));
-              const float2 z = lds64f(zcol + zo + ((rep * kGW * 2 + b1) * 32 * NT + nt * 32));
-              float d[4];
-              mma16816(d, w0 & mlo, w1 & mlo, w0 & mhi, w1 & mhi, xb.x, xb.y, z.x, z.y, z.x, z.y);
-              mma16816(d, v0 & mlo, v1 & mlo, v0 & mhi, v1 & mhi, xb.z, xb.w, d[0], d[1], d[2], d[3]);
-              acc[nt][0] = fmaf(sf.x, d[0], acc[nt][0]);
-              acc[nt][1] = fmaf(sf.x, d[1], acc[nt][1]);
-              acc[nt][2] = fmaf(sf.y, d[2], acc[nt][2]);
-              acc[nt][3] = fmaf(sf.y, d[3], acc[nt][3]);
-            }
+  int tcount = 0, buf = 0, use = 0;
+  for (int sl = 0; sl < p.nslices; ++sl) {
+    const int cs0 = sl * p.slice_chunks, cs1 = min(p.nchunks, cs0 + p.slice_chunks);
+    if (p.nslices > 1) {
+      if (sl > 0) consumer_sync();  // every warp is done with the previous slice's activations
+      for (int m = 0; m < p.M; ++m) {
+        const float rs = p.gamma != nullptr ? rinv[m] : 1.f;
+        for (int grp0 = 0; grp0 < ngroups; grp0 += kCT) {
+          const int grp = grp0 + tid;
+          if ((grp & ~31) < ngroups) {
+            float v[8];
+            const int k0 = cs0 * 64 + grp * 8;
+            load8(m, grp < ngroups ? k0 : p.K, v);
+            gamma8(k0, rs, v);
+            put(m, grp, v, grp < ngroups);
           }
         }
       }
-      xo += kSC * 128;
-      zo += kSC * 2 * 32 * NT;
-      // this warp is done with the stage
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(empty + s));
-      if (++s == s_end) {
-        s = s_first;
-        ph ^= 1u;
-      }
+      consumer_sync();
     }
-
-    // ---- the 16 partial accumulators meet in shared memory --------------------------
-    // red[buf][warp][act][row16]; the reader of buffer `buf` finishes before it arrives at
-    // the next tile's barrier, and buffer `buf` is written again only after that barrier
-    float* myred = red + (((size_t)gi * 2 + buf) * kGW + wi) * red_stride;
+    int tl = 0;  // index of the tile among this CTA's tiles
+    for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++tcount, ++tl) {
+      if ((tcount % kTG) != gi) continue;  // another group's tile
+      float acc1[2] = {0.f, 0.f};
+      float accn[NT][2];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      if (p.split) {
-        const int a = nt * 4 + t;
-        myred[a * 16 + g] = acc[nt][0] + acc[nt][1];
-        myred[a * 16 + g + 8] = acc[nt][2] + acc[nt][3];
-      } else {
-        const int a = nt * 8 + 2 * t;
-        myred[a * 16 + g] = acc[nt][0];
-        myred[(a + 1) * 16 + g] = acc[nt][1];
-        myred[a * 16 + g + 8] = acc[nt][2];
-        myred[(a + 1) * 16 + g + 8] = acc[nt][3];
+      for (int nt = 0; nt < NT; ++nt) accn[nt][0] = accn[nt][1] = 0.f;
+      for (int c0 = cs0; c0 < cs1; c0 += p.stage_chunks, ++use) {
+        const int s = gi * NSg + use % NSg;
+        const uint32_t ph = (uint32_t)(use / NSg) & 1u;
+        if (!failed && !mbar_wait(smem_u32(full + s), ph)) failed = true;
+        const int nc = min(p.stage_chunks, cs1 - c0);
+        const uint32_t wb = smem_u32(ring) + (uint32_t)s * stage_bytes;
+        const uint32_t sb = wb + (uint32_t)p.stage_chunks * 512u;
+        const int blk0 = (c0 - cs0) * 2;
+        if (MODE == kM1L3) consume_m1l3<kGW>(acc1, wb, sb, nc, blk0, L, xbase, wi, lane);
+        else if (MODE == kM1L2) consume_g4<kGW>(acc1, wb, sb, nc, blk0, L, xbase, wi, lane);
+        else if (MODE == kM2L2) consume_g2<kGW>(acc1, wb, sb, nc, blk0, L, xbase, wi, lane);
+        else consume_g1<kGW, NT>(accn, wb, sb, nc, blk0, L, xbase, p.cols, wi, lane);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(empty + s));  // this warp is done with the stage
       }
-    }
-    group_sync<kGW>(gi);
-    if (wi == ((tcount / kTG) % kGW)) {
-      const float* rb = red + ((size_t)gi * 2 + buf) * kGW * red_stride;
-      if (p.epilogue == QENG_EPI_QKV) {
-        const qeng_qkv_epi& E = p.qkv;
-        const int head = tile >> 3, i = ((tile & 7) << 3);
-        for (int e = lane; e < p.M * 8; e += 32) {
-          const int a = e >> 3, r = e & 7;
-          float lo = 0.f, hi = 0.f;  // dims i+r and i+r+64 of this head
-#pragma unroll
-          for (int w = 0; w < kGW; ++w) {
-            lo += rb[w * red_stride + a * 16 + r];
-            hi += rb[w * red_stride + a * 16 + r + 8];
-          }
-          const float os = oscale[a];
-          lo = lo * 16777216.0f * os;
-          hi = hi * 16777216.0f * os;
-          const int ps = E.pos[a];
-          if (ps < 0 || ps >= E.max_seq || (ps >> 4) >= E.max_pages) {
-            atomicExch(p.status, 2);
-            continue;
-          }
-          const int d = i + r;
-          if (head < E.Hq + E.Hkv) {
-            const float c = E.cs[(size_t)ps * 128 + d], sn = E.cs[(size_t)ps * 128 + 64 + d];
-            const float a0 = lo * c - hi * sn, a1 = hi * c + lo * sn;
-            lo = a0;
-            hi = a1;
-          }
-          if (head < E.Hq) {
-            __half* dst = E.q16 + ((size_t)a * E.Hq + head) * 128 + d;
-            dst[0] = __float2half_rn(lo);
-            dst[64] = __float2half_rn(hi);
-          } else {
-            const int pid = E.table[(size_t)a * E.max_pages + (ps >> 4)];
-            if ((unsigned)pid >= (unsigned)E.pages) {
-              atomicExch(p.status, 1);
-              continue;
-            }
-            const int kh = head - E.Hq;
-            const int isv = kh >= E.Hkv ? 1 : 0;
-            __half* dst = E.pool + (((size_t)pid * E.Hkv + (kh - isv * E.Hkv)) * 2 + isv) * (16 * 128) + (ps & 15) * 128 + d;
-            dst[0] = __float2half_rn(lo);
-            dst[64] = __float2half_rn(hi);
-          }
-        }
-      } else if (p.epilogue == QENG_EPI_SWIGLU) {
-        for (int e = lane; e < p.M * 8; e += 32) {
-          const int a = e >> 3, r = e & 7;
-          float gate = 0.f, up = 0.f;
-#pragma unroll
-          for (int w = 0; w < kGW; ++w) {
-            gate += rb[w * red_stride + a * 16 + r];
-            up += rb[w * red_stride + a * 16 + r + 8];
-          }
-          const float os = oscale[a];
-          gate = gate * 16777216.0f * os;
-          up = up * 16777216.0f * os;
-          p.y[(size_t)a * p.ldy + (size_t)tile * 8 + r] = gate / (1.0f + __expf(-gate)) * up;
-        }
+
+      // ---- the partial accumulators of the group's warps meet in shared memory ------------------
+      // red[group][buf][warp][row m][16]; the reader of buffer `buf` finishes before it arrives at
+      // the next tile's barrier, and buffer `buf` is written again only after that barrier
+      float* myred = red + (((size_t)gi * 2 + buf) * kGW + wi) * red_stride;
+      if (MODE == kM1L3 || MODE == kM1L2) {
+        acc1[0] += __shfl_xor_sync(0xffffffffu, acc1[0], 1);
+        acc1[1] += __shfl_xor_sync(0xffffffffu, acc1[1], 1);
+        acc1[0] += __shfl_xor_sync(0xffffffffu, acc1[0], 2);
+        acc1[1] += __shfl_xor_sync(0xffffffffu, acc1[1], 2);
+        if (t == 0) { myred[g] = acc1[0]; myred[g + 8] = acc1[1]; }
+      } else if (MODE == kM2L2) {
+        acc1[0] += __shfl_xor_sync(0xffffffffu, acc1[0], 1);
+        acc1[1] += __shfl_xor_sync(0xffffffffu, acc1[1], 1);
+        if ((t & 1) == 0) { myred[(t >> 1) * 16 + g] = acc1[0]; myred[(t >> 1) * 16 + g + 8] = acc1[1]; }
       } else {
-        for (int e = lane; e < p.M * 16; e += 32) {
-          const int a = e >> 4, r = e & 15;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          myred[(nt * 4 + t) * 16 + g] = accn[nt][0];
+          myred[(nt * 4 + t) * 16 + g + 8] = accn[nt][1];
+        }
+      }
+      group_sync<kGW>(gi);
+      if (wi == ((tcount / kTG) % kGW)) {
+        const float* rb = red + ((size_t)gi * 2 + buf) * kGW * red_stride;
+        float* at = accsm + (size_t)tl * red_stride;
+        const bool first = sl == 0, last = sl + 1 == p.nslices;
+        // sum of the group's warps for activation row a, weight row r of the tile (plus earlier slices)
+        auto total = [&](int a, int r) {
           float v = 0.f;
 #pragma unroll
           for (int w = 0; w < kGW; ++w) v += rb[w * red_stride + a * 16 + r];
-          v = v * 16777216.0f * oscale[a];
-          const size_t o = (size_t)a * p.ldy + (size_t)tile * 16 + r;
-          if (p.epilogue == QENG_EPI_ACCUM) v += p.y[o];
-          else if (p.epilogue == QENG_EPI_RESID) v += p.resid[o];
-          p.y[o] = v;
+          if (!first) v += at[a * 16 + r];
+          return v;
+        };
+        if (!last) {
+          for (int e = lane; e < p.M * 16; e += 32) at[e] = total(e >> 4, e & 15);
+        } else if (p.epilogue == QENG_EPI_QKV) {
+          const qeng_qkv_epi& E = p.qkv;
+          const int head = tile >> 3, i = ((tile & 7) << 3);
+          for (int e = lane; e < p.M * 8; e += 32) {
+            const int a = e >> 3, r = e & 7;
+            float lo = total(a, r), hi = total(a, r + 8);  // dims i+r and i+r+64 of this head
+            const int ps = E.pos[a];
+            if (ps < 0 || ps >= E.max_seq || (ps >> 4) >= E.max_pages) {
+              atomicExch(p.status, 2);
+              continue;
+            }
+            const int d = i + r;
+            if (head < E.Hq + E.Hkv) {
+              const float c = E.cs[(size_t)ps * 128 + d], sn = E.cs[(size_t)ps * 128 + 64 + d];
+              const float a0 = lo * c - hi * sn, a1 = hi * c + lo * sn;
+              lo = a0;
+              hi = a1;
+            }
+            if (head < E.Hq) {
+              __half* dst = E.q16 + ((size_t)a * E.Hq + head) * 128 + d;
+              dst[0] = __float2half_rn(lo);
+              dst[64] = __float2half_rn(hi);
+            } else {
+              const int pid = E.table[(size_t)a * E.max_pages + (ps >> 4)];
+              if ((unsigned)pid >= (unsigned)E.pages) {
+                atomicExch(p.status, 1);
+                continue;
+              }
+              const int kh = head - E.Hq;
+              const int isv = kh >= E.Hkv ? 1 : 0;
+              __half* dst = E.pool + (((size_t)pid * E.Hkv + (kh - isv * E.Hkv)) * 2 + isv) * (16 * 128) + (ps & 15) * 128 + d;
+              dst[0] = __float2half_rn(lo);
+              dst[64] = __float2half_rn(hi);
+            }
+          }
+        } else if (p.epilogue == QENG_EPI_SWIGLU) {
+          for (int e = lane; e < p.M * 8; e += 32) {
+            const int a = e >> 3, r = e & 7;
+            const float gate = total(a, r), up = total(a, r + 8);
+            p.y[(size_t)a * p.ldy + (size_t)tile * 8 + r] = gate / (1.0f + __expf(-gate)) * up;
+          }
+        } else {
+          for (int e = lane; e < p.M * 16; e += 32) {
+            const int a = e >> 4, r = e & 15;
+            float v = total(a, r);
+            const size_t o = (size_t)a * p.ldy + (size_t)tile * 16 + r;
+            if (p.epilogue == QENG_EPI_ACCUM) v += p.y[o];
+            else if (p.epilogue == QENG_EPI_RESID) v += p.resid[o];
+            p.y[o] = v;
+          }
         }
       }
+      buf ^= 1;
     }
-    buf ^= 1;
   }
   if (failed && lane == 0) atomicExch(p.status, 4);
 }
 
-template <int NT, int kTG>
+template <int MODE, int NT, int kTG>
 int32_t launch_stream(qeng_ctx* ctx, const StreamParams& p, size_t smem, cudaStream_t stream) {
   static bool configured_on[64] = {};  // the opt-in shared-memory size is set per device
   bool& configured = configured_on[ctx->device & 63];
   if (!configured) {
-    QENG_CUDA(ctx, cudaFuncSetAttribute(gemv_q4_stream_kernel<NT, kTG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    QENG_CUDA(ctx, cudaFuncSetAttribute(gemv_q4_stream_kernel<MODE, NT, kTG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     configured = true;
   }
   const int grid = p.ntiles < ctx->sm_count ? p.ntiles : ctx->sm_count;
@@ -532,7 +418,7 @@ int32_t launch_stream(qeng_ctx* ctx, const StreamParams& p, size_t smem, cudaStr
   // running; everything that depends on the predecessor sits behind griddepcontrol.wait
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
-  cfg.blockDim = dim3(kThreadsS);
+  cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -540,51 +426,66 @@ int32_t launch_stream(qeng_ctx* ctx, const StreamParams& p, size_t smem, cudaStr
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = ctx->pdl ? 1 : 0;
-  QENG_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4_stream_kernel<NT, kTG>, p));
+  QENG_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4_stream_kernel<MODE, NT, kTG>, p));
   return QENG_OK;
 }
 
-}  // namespace
-
-namespace {
 struct StreamFit {
   bool ok;
-  int split, cols, NT, nstages;
+  int mode, NT, cols, nstages, stage_chunks, slice_chunks, nslices;
   size_t smem;
 };
-StreamFit stream_fit(const qeng_weight* w, int x_dtype, int64_t M, bool split_f32) {
+
+// Shared-memory plan for a shape: the staged activations (whole K for up to 4 rows, else the
+// largest K slice that leaves the ring at least ~100 KB), reduction buffers, then as many ring
+// slots as fit.
+StreamFit stream_fit(const qeng_ctx* ctx, const qeng_weight* w, int64_t M, bool two_limbs) {
   StreamFit f = {};
-  f.split = (x_dtype == QENG_F32 && split_f32) ? 1 : 0;
-  f.cols = f.split ? 2 * (int)M : (int)M;
-  if (M < 1 || f.cols > 32) return f;
-  if (w->nchunks * 64 > 8 * kGroups * kCT) return f;  // staged through registers: K <= 12288
-  f.NT = f.cols <= 8 ? 1 : (f.cols <= 16 ? 2 : 4);
-  const int64_t Kp = w->nchunks * 64;
-  const size_t fixed = (size_t)2 * kMaxStages * 8 + 64                  // barriers
-                       + (size_t)f.cols * (Kp + 32) * 2                 // staged activations
-                       + (size_t)w->nchunks * 2 * 8 * f.NT * 4          // block sums
-                       + (size_t)2 * kCW * 16 * 8 * f.NT * 4;           // reduction buffers
-  const size_t budget = 226 * 1024 - 512;
-  if (fixed + (size_t)2 * kStageBytes > budget) return f;
-  f.nstages = (int)((budget - fixed) / kStageBytes);
-  if (f.nstages > kMaxStages) f.nstages = kMaxStages;
-  f.smem = (size_t)f.nstages * kStageBytes + fixed;
-  f.ok = true;
+  if (M < 1 || M > 16) return f;
+  f.mode = M == 1 ? (two_limbs ? kM1L2 : kM1L3) : (M == 2 ? kM2L2 : kMN);
+  f.cols = f.mode == kM1L3 ? 3 : 2 * (int)M;
+  f.NT = f.mode == kMN ? (int)((M + 3) / 4) : 1;
+  const int kMR = f.mode == kMN ? 4 * f.NT : (f.mode == kM2L2 ? 2 : 1);
+  const int nch = (int)w->nchunks;
+  const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
+  const int grid = w->ntiles < sms ? (int)w->ntiles : sms;
+  const int tiles_per_cta = (int)((w->ntiles + grid - 1) / grid);
+  const size_t budget = 226 * 1024 - 1024;
+  const size_t bars = 2 * kMaxStages * 8;
+  auto plan = [&](int slice) -> bool {
+    const int nsl = (nch + slice - 1) / slice;
+    if (nsl == 1 && nch * 64 > 8 * kGroups * kCT) return false;  // single-slice staging goes through registers: K <= 12288
+    const int alloc = f.mode == kM1L2 ? (slice + 1) & ~1 : slice;
+    const XLayout L = x_layout(f.cols, alloc, f.mode != kMN);
+    const size_t red = (size_t)2 * kCW * kMR * 16 * 4;  // the same for every number of tile groups
+    const size_t accs = nsl > 1 ? (size_t)tiles_per_cta * kMR * 16 * 4 : 0;
+    const size_t fixed = L.bytes + red + accs + bars + 256;
+    const int sc = slice < 64 ? slice : 64;
+    const size_t slot = (size_t)sc * 576;
+    if (fixed + 2 * slot > budget) return false;
+    int ns = (int)((budget - fixed) / slot);
+    if (ns > kMaxStages) ns = kMaxStages;
+    if ((size_t)ns * slot < (size_t)96 * 1024 && slice > 8) return false;  // too little in flight: stage a smaller K slice
+    f.nstages = ns; f.stage_chunks = sc; f.slice_chunks = slice; f.nslices = nsl;
+    f.smem = (((size_t)ns * slot + 127) & ~(size_t)127) + fixed;
+    return true;
+  };
+  if (plan(nch)) { f.ok = true; return f; }  // the whole K range staged once
+  for (int slice = 64; slice >= 8; slice >>= 1)
+    if (slice < nch && plan(slice)) { f.ok = true; return f; }
   return f;
 }
 }  // namespace
 
-bool qeng_gemm_q4_stream_fits(const qeng_weight* w, int64_t M, bool split) {
-  return stream_fit(w, QENG_F32, M, split).ok;
-}
+bool qeng_gemm_q4_stream_fits(const qeng_ctx* ctx, const qeng_weight* w, int64_t M) { return stream_fit(ctx, w, M, false).ok; }
 
-// *handled = false when the shape does not fit this kernel (activations too large to keep
-// resident in shared memory); the caller then uses the register-streaming kernel.
+// *handled = false when the shape does not fit this kernel; the caller then uses the
+// register-streaming kernel.
 int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t x_dtype, int64_t M,
-                            int64_t ldx, float* y, int64_t ldy, bool split_f32, const qeng_gemm_fuse& fuse,
-                            cudaStream_t stream, bool* handled) {
+                            int64_t ldx, float* y, int64_t ldy, const qeng_gemm_fuse& fuse, cudaStream_t stream,
+                            bool* handled) {
   *handled = false;
-  const StreamFit f = stream_fit(w, x_dtype, M, split_f32);
+  const StreamFit f = stream_fit(ctx, w, M, fuse.two_limbs);
   if (!f.ok) {
     if (fuse.epilogue == QENG_EPI_QKV) return qeng_fail(ctx, QENG_ERR_SHAPE, "gemm_q4: the fused q|k|v epilogue needs the streaming kernel");
     return QENG_OK;
@@ -592,10 +493,11 @@ int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
   StreamParams p;
   p.qs = w->qs; p.sc = w->sc;
   p.ntiles = (int)w->ntiles; p.nchunks = (int)w->nchunks; p.K = (int)w->K;
-  p.x = x; p.x_dtype = x_dtype; p.ldx = ldx; p.M = (int)M; p.cols = f.cols; p.split = f.split;
+  p.x = x; p.x_dtype = x_dtype; p.ldx = ldx; p.M = (int)M; p.cols = f.cols;
   p.y = y; p.ldy = ldy;
   p.gamma = fuse.norm_gamma; p.eps = fuse.norm_eps; p.epilogue = fuse.epilogue; p.resid = fuse.resid;
-  p.nstages = f.nstages; p.status = ctx->status;
+  p.nstages = f.nstages; p.stage_chunks = f.stage_chunks; p.slice_chunks = f.slice_chunks; p.nslices = f.nslices;
+  p.status = ctx->status;
   const qeng_weight* nx = ctx->l2_prefetch ? w->next : nullptr;
   p.pf_qs = nx ? nx->qs : nullptr; p.pf_sc = nx ? nx->sc : nullptr;
   p.pf_ntiles = nx ? (int)nx->ntiles : 0; p.pf_nchunks = nx ? (int)nx->nchunks : 0;
@@ -609,19 +511,24 @@ int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
   // so the split follows the number of tiles a CTA owns.
   const int grid = p.ntiles < ctx->sm_count ? p.ntiles : ctx->sm_count;
   const int per_cta = (p.ntiles + grid - 1) / grid;
-  int tg = per_cta >= 8 ? 4 : (per_cta >= 2 ? 2 : 1);
-  // every group keeps at least two ring slots, and no fewer than one row tile needs (K > 4096: a tile
-  // spans several stages, and a group whose ring is shorter than its tile stalls the producer)
-  const int spt = (p.nchunks + kSC - 1) / kSC;
-  while (tg > 1 && f.nstages / tg < (spt > 2 ? spt : 2)) tg >>= 1;
+  int tg = per_cta >= 2 ? 4 : 1;
+  // a group needs a ring of its own at least as long as one row tile (a tile may span several
+  // stages, and a group whose ring is shorter than its tile stalls the producer)
+  const int spt = (f.slice_chunks + f.stage_chunks - 1) / f.stage_chunks;
+  while (tg > 1 && f.nstages / tg < spt) tg >>= 1;
   if (ctx->stream_groups == 1 || ctx->stream_groups == 2 || ctx->stream_groups == 4) tg = ctx->stream_groups;
-#define QENG_STREAM_CASE(NT_)                                                   \
-  (tg == 4 ? launch_stream<NT_, 4>(ctx, p, f.smem, stream)                      \
-           : (tg == 2 ? launch_stream<NT_, 2>(ctx, p, f.smem, stream) : launch_stream<NT_, 1>(ctx, p, f.smem, stream)))
+  while (tg > 1 && f.nstages / tg < 1) tg >>= 1;
+#define QENG_STREAM_CASE(MODE_, NT_)                                                   \
+  (tg == 4 ? launch_stream<MODE_, NT_, 4>(ctx, p, f.smem, stream)                      \
+           : (tg == 2 ? launch_stream<MODE_, NT_, 2>(ctx, p, f.smem, stream) : launch_stream<MODE_, NT_, 1>(ctx, p, f.smem, stream)))
+  if (f.mode == kM1L3) return QENG_STREAM_CASE(kM1L3, 1);
+  if (f.mode == kM1L2) return QENG_STREAM_CASE(kM1L2, 1);
+  if (f.mode == kM2L2) return QENG_STREAM_CASE(kM2L2, 1);
   switch (f.NT) {
-    case 1: return QENG_STREAM_CASE(1);
-    case 2: return QENG_STREAM_CASE(2);
-    default: return QENG_STREAM_CASE(4);
+    case 1: return QENG_STREAM_CASE(kMN, 1);
+    case 2: return QENG_STREAM_CASE(kMN, 2);
+    case 3: return QENG_STREAM_CASE(kMN, 3);
+    default: return QENG_STREAM_CASE(kMN, 4);
   }
 #undef QENG_STREAM_CASE
 }

@@ -114,6 +114,7 @@ struct qeng_gemm_fuse {
   int epilogue = 0;                   // see QENG_EPI_*
   const float* resid = nullptr;       // QENG_EPI_RESID: y = resid + x.W^T
   const qeng_qkv_epi* qkv = nullptr;  // QENG_EPI_QKV (streaming kernel only)
+  bool two_limbs = false;             // a single activation row in 15 instead of 22 bits (QENG_GEMM_FAST_F16)
 };
 // SWIGLU: rows g (gate) and g+8 (up) of every 16-row tile are combined into one
 // output y[8*tile + g] = silu(gate) * up, so y has N/2 columns.
@@ -128,10 +129,10 @@ int32_t qeng_attn_reserve(qeng_ctx* ctx, int64_t B, int64_t Hq, int64_t Hkv, int
 
 // gemv_q4_stream.cu: the persistent bulk-copy kernel; *handled = false when the shape does not fit it
 int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t x_dtype, int64_t M,
-                            int64_t ldx, float* y, int64_t ldy, bool split_f32, const qeng_gemm_fuse& fuse,
-                            cudaStream_t stream, bool* handled);
+                            int64_t ldx, float* y, int64_t ldy, const qeng_gemm_fuse& fuse, cudaStream_t stream,
+                            bool* handled);
 // true when the streaming kernel takes this shape (its fused-only epilogues may then be used)
-bool qeng_gemm_q4_stream_fits(const qeng_weight* w, int64_t M, bool split);
+bool qeng_gemm_q4_stream_fits(const qeng_ctx* ctx, const qeng_weight* w, int64_t M);
 
 // ops.cu: LM head with optional fused RMSNorm and optional greedy finalisation (argmax over the
 // vocabulary, record the token, advance the sequences, gather the next embedding) in one launch.

@@ -26,14 +26,11 @@ def _events(torch):
 def gemv(args):
     import torch
     from cyb_b200 import qeng
-    ctx = qeng.Context(0)
+    ctx = qeng.Context(0, stream_groups=args.groups) if args.groups else qeng.Context(0)
     n, k, m = args.n, args.k, args.m
     wbytes = n * k * 0.5625
     pool = args.pool or max(2, int(160e6 // wbytes) + 1)
-    rng = np.random.Generator(np.random.PCG64(0))
-    q = rng.integers(0, 16, (n, k), dtype=np.uint8)
-    s = rng.uniform(0.002, 0.02, (n, k // 32)).astype(np.float16)
-    ws = [ctx.pack_q4(np.roll(q, i, axis=1), s) for i in range(pool)]
+    ws = [ctx.quantize_q4(torch.randn(n, k, device="cuda") * 0.05) for _ in range(pool)]  # timing only: any weights do
     dt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[args.dtype]
     x = torch.randn(m, k, device="cuda").to(dt)
     y = torch.empty(m, n, device="cuda")
@@ -225,6 +222,7 @@ def main(argv=None):
     g.add_argument("--pool", type=int, default=0)
     g.add_argument("--iters", type=int, default=20)
     g.add_argument("--flags", type=int, default=0)
+    g.add_argument("--groups", type=int, default=0, help="tile groups of the streaming kernel (1, 2, 4; 0 = by shape)")
     a = sub.add_parser("attn")
     a.add_argument("--batch", type=int, default=16)
     a.add_argument("--lo", type=int, default=512)

@@ -47,9 +47,10 @@ enum { QENG_F32 = 0, QENG_F16 = 1, QENG_BF16 = 2 };
 /* flags of qeng_gemm_q4 */
 enum {
   QENG_GEMM_ACCUMULATE = 1, /* y += x.W^T instead of y = x.W^T (fused residual add) */
-  QENG_GEMM_FAST_F16 = 2    /* f32 activations are rounded to f16 once instead of
-                               being split into two f16 terms (halves tensor work,
-                               costs ~2e-4 of the error budget) */
+  QENG_GEMM_FAST_F16 = 2    /* a single activation row is quantised to 15 bits per 32-block
+                               instead of 22 (a little faster; costs ~6e-5 of the error
+                               budget instead of ~5e-7); no effect for 2 or more rows, which
+                               always use 15 bits */
 };
 
 typedef struct qeng_ctx qeng_ctx;
@@ -144,8 +145,9 @@ int32_t qeng_weight_set_next(qeng_ctx* ctx, qeng_weight* w, const qeng_weight* n
 
 /* ---- quantized matmul (the "QKV / O proj / FFN" steps of decide/pipeline.md:51)
  * y[M,N] (f32, leading dimension ldy) = x[M,K] (x_dtype, leading dimension ldx)
- * . dequant(W)^T, f32 accumulation.  M < 256 runs the decode kernels (dequantise in
- * registers, activations exact); M >= 256 the tensor-core prefill kernel, which rounds
+ * . dequant(W)^T, f32 accumulation.  M < 256 runs the decode kernels (weights unpacked in
+ * registers, activations in block fixed point: 22 bits for one row, 15 bits per row otherwise,
+ * integer tensor-core contraction, per-block f32 scaling); M >= 256 the tensor-core prefill kernel, which rounds
  * activations and dequantised weights to bf16 (tolerance 5e-3 instead of 2e-3). */
 int32_t qeng_gemm_q4(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t x_dtype,
                      int64_t M, int64_t ldx, float* y, int64_t ldy, int32_t flags, void* stream);
