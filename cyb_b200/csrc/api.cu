@@ -50,7 +50,7 @@ int32_t qeng_create_opts(int32_t device, const qeng_options* opts, qeng_ctx** ou
   ctx->l2_prefetch = !o.no_l2_prefetch;
   ctx->p2p_allowed = !o.no_p2p_allreduce;
   ctx->attn_cluster = !o.no_attn_cluster;
-  ctx->step_kernel = !o.no_step_kernel;
+  ctx->step_kernel = o.step_kernel != 0;
   ctx->attn_ctas_per_sm = o.attn_ctas_per_sm > 0 ? o.attn_ctas_per_sm : 8;
   ctx->stream_groups = o.stream_groups;
   if (cudaMalloc(&ctx->status, 64) != cudaSuccess || cudaMemset(ctx->status, 0, 64) != cudaSuccess) {

@@ -205,6 +205,10 @@ struct qeng_decoder {
   cudaGraphExec_t graph = nullptr;
   int graph_batch = 0;
   uint64_t graph_scratch_gen = 0;  // ctx->scratch_gen at capture time
+  // the fused decode step (all layers in one persistent kernel), planned lazily; dropped whenever a
+  // buffer or weight it points at is replaced
+  qeng_step* fused = nullptr;
+  bool step_planned = false;
   int launches = 0;
 };
 
@@ -220,6 +224,7 @@ int32_t ensure_rows(qeng_ctx* ctx, qeng_decoder* d, int64_t rows) {
   if (rows <= d->rows_cap) return QENG_OK;
   QENG_CUDA(ctx, cudaDeviceSynchronize());
   if (d->graph) { cudaGraphExecDestroy(d->graph); d->graph = nullptr; }
+  qeng_step_free(d->fused); d->fused = nullptr; d->step_planned = false;
   float** fb[] = {&d->x, &d->qkv, &d->att, &d->act, &d->part, &d->xnr, &d->gu};
   for (auto p : fb)
     if (*p) { cudaFree(*p); *p = nullptr; }
@@ -463,6 +468,30 @@ int32_t tail(qeng_ctx* ctx, qeng_decoder* d, const float* x_last, int B, bool fi
   return rc;
 }
 
+// Plan the fused step kernel for this decoder (once per set of weights and buffers).  Leaves
+// d->fused null when the model is outside what the kernel takes: per-head q/k gains, more than one
+// rank (the sharded step still runs operator by operator), unusual widths.
+int32_t plan_step(qeng_ctx* ctx, qeng_decoder* d) {
+  d->step_planned = true;
+  if (d->cfg.tp_world != 1) return QENG_OK;
+  qeng_step_desc desc;
+  for (int l = 0; l < d->cfg.layers; ++l) {
+    Layer& L = d->layers[l];
+    if (!L.wqkv || !L.wo || !L.wgu || !L.wdown || !L.norm1 || !L.norm2 || L.qnorm || L.knorm) return QENG_OK;
+    qeng_step_layer_desc ld;
+    ld.w[0] = L.wqkv; ld.w[1] = L.wo; ld.w[2] = L.wgu; ld.w[3] = L.wdown;
+    ld.norm1 = L.norm1; ld.norm2 = L.norm2;
+    ld.pool = d->pool + (size_t)l * d->pages * d->Hkv * 2 * kPage * kHD;
+    desc.layers.push_back(ld);
+  }
+  desc.dm = d->cfg.d_model; desc.F = d->F; desc.Hq = d->Hq; desc.Hkv = d->Hkv;
+  desc.max_pages = d->max_pages; desc.pages = (int)d->pages; desc.max_seq = d->cfg.max_seq; desc.eps = d->cfg.rms_eps;
+  desc.x = d->x; desc.pos = d->pos; desc.lens = d->lens; desc.table = d->dec_table; desc.cs = d->rope_cs;
+  desc.q16 = d->q16; desc.act = d->act;
+  desc.world = 1; desc.rank = 0;
+  return qeng_step_create(ctx, desc, &d->fused);
+}
+
 // one decode step, all state on the device: x holds the embedding of the token to feed
 int32_t decode_step(qeng_ctx* ctx, qeng_decoder* d, cudaStream_t st) {
   const int B = d->batch;
@@ -575,6 +604,7 @@ int32_t qeng_decoder_free(qeng_ctx* ctx, qeng_decoder* d) {
   if (ctx) cudaSetDevice(ctx->device);
   cudaDeviceSynchronize();
   if (d->graph) cudaGraphExecDestroy(d->graph);
+  qeng_step_free(d->fused);
   for (auto& L : d->layers) {
     qeng_weight_free(ctx, L.wqkv); qeng_weight_free(ctx, L.wo); qeng_weight_free(ctx, L.wgu); qeng_weight_free(ctx, L.wdown);
     if (L.norm1) cudaFree(L.norm1);
@@ -686,6 +716,7 @@ int32_t qeng_decoder_load_matrix(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, 
   }
   link_weights(d);
   if (d->graph) { cudaGraphExecDestroy(d->graph); d->graph = nullptr; }
+  qeng_step_free(d->fused); d->fused = nullptr; d->step_planned = false;
   return rc;
 }
 
@@ -699,6 +730,7 @@ int32_t qeng_decoder_load_norm(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, in
   if (!*dst) QENG_CUDA(ctx, cudaMalloc(dst, n * 4));
   QENG_CUDA(ctx, cudaMemcpy(*dst, gamma, n * 4, cudaMemcpyHostToDevice));
   if (which >= 2 && d->graph) { cudaGraphExecDestroy(d->graph); d->graph = nullptr; }  // the step takes another path
+  qeng_step_free(d->fused); d->fused = nullptr; d->step_planned = false;
   return QENG_OK;
 }
 
@@ -804,23 +836,37 @@ int32_t qeng_decoder_decode(qeng_ctx* ctx, qeng_decoder* d, int32_t steps, int32
     QENG_LAUNCH_CHECK(ctx);
   }
   d->next_ready = false;  // until this call's steps have run to the end
-  if (!d->graph || d->graph_batch != B || d->graph_scratch_gen != ctx->scratch_gen) {
-    QENG_CUDA(ctx, cudaStreamSynchronize(st));
-    if (d->graph) { cudaGraphExecDestroy(d->graph); d->graph = nullptr; }
-    cudaGraph_t g = nullptr;
-    QENG_CUDA(ctx, cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-    d->launches = 0;
-    int32_t rc = decode_step(ctx, d, st);
-    cudaError_t e = cudaStreamEndCapture(st, &g);
-    if (rc != QENG_OK) { if (g) cudaGraphDestroy(g); return rc; }
-    if (e != cudaSuccess) return qeng_fail(ctx, QENG_ERR_CUDA, "decoder_decode: capture failed: %s", cudaGetErrorString(e));
-    e = cudaGraphInstantiate(&d->graph, g, 0);
-    cudaGraphDestroy(g);
-    if (e != cudaSuccess) return qeng_fail(ctx, QENG_ERR_CUDA, "decoder_decode: instantiate failed: %s", cudaGetErrorString(e));
-    d->graph_batch = B;
-    d->graph_scratch_gen = ctx->scratch_gen;
+  if (!d->step_planned) {
+    int32_t rc = plan_step(ctx, d);
+    if (rc != QENG_OK) return rc;
   }
-  for (int s = 0; s < steps; ++s) QENG_CUDA(ctx, cudaGraphLaunch(d->graph, st));
+  if (qeng_step_takes(d->fused, B)) {
+    // all layers in one persistent kernel, then the LM head (norm, head, sample, advance, embed)
+    for (int s = 0; s < steps; ++s) {
+      d->launches = 1;
+      int32_t rc = qeng_step_launch(ctx, d->fused, B, st);
+      if (rc == QENG_OK) rc = tail(ctx, d, d->x, B, true, st);
+      if (rc != QENG_OK) return rc;
+    }
+  } else {
+    if (!d->graph || d->graph_batch != B || d->graph_scratch_gen != ctx->scratch_gen) {
+      QENG_CUDA(ctx, cudaStreamSynchronize(st));
+      if (d->graph) { cudaGraphExecDestroy(d->graph); d->graph = nullptr; }
+      cudaGraph_t g = nullptr;
+      QENG_CUDA(ctx, cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+      d->launches = 0;
+      int32_t rc = decode_step(ctx, d, st);
+      cudaError_t e = cudaStreamEndCapture(st, &g);
+      if (rc != QENG_OK) { if (g) cudaGraphDestroy(g); return rc; }
+      if (e != cudaSuccess) return qeng_fail(ctx, QENG_ERR_CUDA, "decoder_decode: capture failed: %s", cudaGetErrorString(e));
+      e = cudaGraphInstantiate(&d->graph, g, 0);
+      cudaGraphDestroy(g);
+      if (e != cudaSuccess) return qeng_fail(ctx, QENG_ERR_CUDA, "decoder_decode: instantiate failed: %s", cudaGetErrorString(e));
+      d->graph_batch = B;
+      d->graph_scratch_gen = ctx->scratch_gen;
+    }
+    for (int s = 0; s < steps; ++s) QENG_CUDA(ctx, cudaGraphLaunch(d->graph, st));
+  }
   QENG_CUDA(ctx, cudaMemcpyAsync(out_tokens, d->out_tokens, (size_t)steps * B * 4, cudaMemcpyDeviceToHost, st));
   int32_t status = 0;
   QENG_CUDA(ctx, cudaMemcpyAsync(&status, ctx->status, 4, cudaMemcpyDeviceToHost, st));
@@ -908,5 +954,13 @@ int32_t qeng_decoder_weight(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, int32
 }
 
 int32_t qeng_decoder_launches_per_step(const qeng_decoder* d) { return d ? d->launches : 0; }
+
+int32_t qeng_decoder_step_profile(qeng_ctx* ctx, qeng_decoder* d, uint64_t* out_ns, int32_t capacity, int32_t* n_written) {
+  if (!ctx || !d || !out_ns || !n_written) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_step_profile: null argument");
+  *n_written = 0;
+  if (!d->fused) return qeng_fail(ctx, QENG_ERR_STATE, "decoder_step_profile: the fused step kernel is not in use for this decoder");
+  QENG_CUDA(ctx, cudaSetDevice(ctx->device));
+  return qeng_step_profile(ctx, d->fused, out_ns, capacity, n_written);
+}
 
 }  // extern "C"

@@ -80,20 +80,17 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
 __device__ __forceinline__ void l2_prefetch(const void* gptr, uint32_t bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(gptr), "r"(bytes) : "memory");
 }
+// Shared-memory loads by 32-bit shared-window address.  Plain (non-volatile) loads: the compiler may
+// move and interleave them with the arithmetic of neighbouring iterations; their order against the
+// barriers is kept by the barriers' own memory clobbers.
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
+  return *reinterpret_cast<const uint4*>(__cvta_shared_to_generic((size_t)addr));
 }
 __device__ __forceinline__ uint2 lds64(uint32_t addr) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-  return v;
+  return *reinterpret_cast<const uint2*>(__cvta_shared_to_generic((size_t)addr));
 }
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
-  return v;
+  return *reinterpret_cast<const uint32_t*>(__cvta_shared_to_generic((size_t)addr));
 }
 __device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
   asm volatile("st.shared.v2.u32 [%0], {%1,%2};\n" ::"r"(addr), "r"(a), "r"(b) : "memory");
@@ -132,8 +129,10 @@ struct XLayout {
   int nblk;
 };
 // zeroed = true when several blocks share an accumulator fragment (the lanes of the other blocks
-// read zeros); chunks = 64-wide K chunks of the slice
-__host__ __device__ inline XLayout x_layout(int cols, int chunks, bool zeroed) {
+// read zeros); chunks = 64-wide K chunks of the slice.  zero_reserved > 0 puts the zero region
+// first, at a fixed place and size whatever the columns are (a kernel that stages several
+// different operands clears it once); it must be >= x_zero_bytes of every layout used.
+__host__ __device__ inline XLayout x_layout(int cols, int chunks, bool zeroed, uint32_t zero_reserved = 0) {
   XLayout L;
   L.nblk = chunks * 2;
   const uint32_t raw = ((uint32_t)chunks * 64u + 127u) / 128u * 128u;
@@ -142,9 +141,16 @@ __host__ __device__ inline XLayout x_layout(int cols, int chunks, bool zeroed) {
   // (mod 128); the zero region starts 64 bytes off (mod 128) and the upper half-warp enters it
   // another 64 bytes further on.
   L.col_stride = raw + 32u;
-  L.xq = 0;
-  L.zero = ((uint32_t)cols * L.col_stride + 127u) / 128u * 128u + 64u;
-  const uint32_t after = zeroed ? L.zero + raw + 128u : (uint32_t)cols * L.col_stride;
+  uint32_t after;
+  if (zero_reserved > 0) {
+    L.zero = 64u;
+    L.xq = (64u + zero_reserved + 127u) / 128u * 128u;
+    after = L.xq + (uint32_t)cols * L.col_stride;
+  } else {
+    L.xq = 0;
+    L.zero = ((uint32_t)cols * L.col_stride + 127u) / 128u * 128u + 64u;
+    after = zeroed ? L.zero + raw + 128u : (uint32_t)cols * L.col_stride;
+  }
   L.zin = (after + 127u) & ~127u;
   L.zs = ((uint32_t)L.nblk * 4u + 127u) / 128u * 128u + 16u;
   L.fex = L.zin + (uint32_t)cols * L.zs;

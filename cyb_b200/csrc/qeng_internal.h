@@ -6,6 +6,7 @@
 #include <stdio.h>
 
 #include <string>
+#include <vector>
 
 #include "../../include/qeng.h"
 
@@ -59,7 +60,7 @@ struct qeng_ctx {
   bool l2_prefetch = true;    // the streaming matmul requests the hinted next matrix into L2
   bool pdl = true;            // launch the streaming matmul with programmatic stream serialization
   // remaining switches of qeng_options
-  bool p2p_allowed = true, attn_cluster = true, step_kernel = true;
+  bool p2p_allowed = true, attn_cluster = true, step_kernel = false;
   int attn_ctas_per_sm = 8, stream_groups = 0;
   // bumped whenever attn_scratch moves: a captured graph that holds the old address is stale
   uint64_t scratch_gen = 0;
@@ -157,6 +158,33 @@ struct qeng_lm_tail {
   int pair_slot = 0;
 };
 int32_t qeng_lm_head_fused(qeng_ctx* ctx, const qeng_lm_tail& t, cudaStream_t stream);
+
+// decode_step.cu: all layers of one decode step (1 or 2 rows) in one persistent cooperative kernel
+struct qeng_step;
+struct qeng_step_layer_desc {
+  const qeng_weight* w[4];  // q|k|v, o, gate|up (interleaved), down
+  const float *norm1, *norm2;
+  __half* pool;             // this layer's KV pages
+};
+struct qeng_step_desc {
+  std::vector<qeng_step_layer_desc> layers;
+  int dm = 0, F = 0, Hq = 0, Hkv = 0, max_pages = 0, pages = 0, max_seq = 0;
+  float eps = 0.f;
+  float* x = nullptr;                 // [rows][dm] residual stream, read and rewritten by a step
+  const int32_t *pos = nullptr, *lens = nullptr, *table = nullptr;
+  const float* cs = nullptr;
+  __half* q16 = nullptr;
+  float* act = nullptr;
+  int world = 1, rank = 0;
+  void* peer_inbox[8] = {};           // world > 1: every rank's inbox as mapped here (own included)
+};
+// *out stays null when the shapes are outside what the kernel takes, or the context disabled it
+int32_t qeng_step_create(qeng_ctx* ctx, const qeng_step_desc& d, qeng_step** out);
+void qeng_step_free(qeng_step* s);
+bool qeng_step_takes(const qeng_step* s, int B);
+int32_t qeng_step_launch(qeng_ctx* ctx, qeng_step* s, int B, cudaStream_t stream);
+size_t qeng_step_inbox_bytes(int world, int dm);
+int32_t qeng_step_profile(qeng_ctx* ctx, qeng_step* s, uint64_t* out, int32_t capacity, int32_t* n);
 
 // tp.cu
 int32_t qeng_tp_all_reduce_internal(qeng_ctx* ctx, float* buf, int64_t n, cudaStream_t stream);

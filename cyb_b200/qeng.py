@@ -53,7 +53,7 @@ class Options(C.Structure):
     """qeng_options: tuning switches fixed when a context is created (0 keeps the default)."""
     _fields_ = [("struct_size", C.c_int32), ("no_pdl", C.c_int32), ("no_l2_prefetch", C.c_int32),
                 ("no_p2p_allreduce", C.c_int32), ("no_attn_cluster", C.c_int32), ("attn_ctas_per_sm", C.c_int32),
-                ("stream_groups", C.c_int32), ("no_step_kernel", C.c_int32)]
+                ("stream_groups", C.c_int32), ("step_kernel", C.c_int32)]
 
 
 class ModelCfg(C.Structure):
@@ -121,6 +121,7 @@ _sig("qeng_decoder_layer", _i32, _vp, _vp, _i32, _vp, _vp, _i32, _vp, _vp)
 _sig("qeng_decoder_set_stream", _i32, _vp, _vp, _vp)
 _sig("qeng_decoder_weight", _i32, _vp, _vp, _i32, _i32, C.POINTER(_vp))
 _sig("qeng_decoder_launches_per_step", _i32, _vp)
+_sig("qeng_decoder_step_profile", _i32, _vp, _vp, _vp, _i32, C.POINTER(_i32))
 
 
 def _np_ptr(a):
@@ -141,7 +142,7 @@ class Context:
 
     def __init__(self, device=0, **options):
         """`options`: fields of qeng_options (no_pdl, no_l2_prefetch, no_p2p_allreduce, no_attn_cluster,
-        attn_ctas_per_sm, stream_groups, no_step_kernel)."""
+        attn_ctas_per_sm, stream_groups, step_kernel)."""
         h = _vp()
         if options:
             o = Options(struct_size=C.sizeof(Options), **{k: int(v) for k, v in options.items()})
@@ -469,6 +470,13 @@ class Decoder:
 
     def use_current_stream(self):
         self.ctx.check(_lib.qeng_decoder_set_stream(self.ctx.h, self.h, _cur_stream()))
+
+    def step_profile(self):
+        """Phase timestamps (ns) of the last fused decode step: array [2 CTAs, layers, 16]."""
+        out = np.zeros(2 * self.cfg.layers * 16, np.uint64)
+        n = _i32(0)
+        self.ctx.check(_lib.qeng_decoder_step_profile(self.ctx.h, self.h, _np_ptr(out), out.size, C.byref(n)))
+        return out[:n.value].reshape(2, self.cfg.layers, 16)
 
     @property
     def launches_per_step(self):

@@ -74,7 +74,8 @@ typedef struct qeng_options {
   int32_t no_attn_cluster;   /* 1: decode attention always uses fixed splits + scratch */
   int32_t attn_ctas_per_sm;  /* CTAs per SM the split-KV attention aims for (default 8) */
   int32_t stream_groups;     /* tile groups of the streaming matmul: 1, 2 or 4 (default: by shape) */
-  int32_t no_step_kernel;    /* 1: a decode step is the per-operator kernel chain, never the fused step kernel */
+  int32_t step_kernel;       /* 1: decode steps of 1 or 2 sequences run all layers in one persistent cooperative
+                                kernel (tagged data flow between the operators) instead of one kernel per operator */
 } qeng_options;
 int32_t qeng_create_opts(int32_t device, const qeng_options* opts, qeng_ctx** out);
 int32_t qeng_destroy(qeng_ctx* ctx);
@@ -276,6 +277,14 @@ int32_t qeng_decoder_weight(qeng_ctx* ctx, qeng_decoder* dec, int32_t layer, int
                             const qeng_weight** out);
 /* Kernel launches issued per decode step (for reporting). */
 int32_t qeng_decoder_launches_per_step(const qeng_decoder* dec);
+/* Where the last fused decode step spent its time: device timestamps in nanoseconds, laid out
+ * [2 CTAs: the grid's first and last][layers][16 stamps].  Stamps of a layer: 0 start, 1 residual
+ * gathered, 2 q|k|v staged, 3 q|k|v done, 4 barrier passed, 5 attention done, 6 barrier passed,
+ * 7 o staged, 8 o done, 9 residual gathered, 10 gate|up staged, 11 gate|up done, 12 barrier
+ * passed, 13 down staged, 14 down done.  Synchronises the device.  QENG_ERR_STATE when the decoder
+ * runs its steps operator by operator (no counterpart in the reference). */
+int32_t qeng_decoder_step_profile(qeng_ctx* ctx, qeng_decoder* dec, uint64_t* out_ns, int32_t capacity,
+                                  int32_t* n_written);
 
 #ifdef __cplusplus
 }

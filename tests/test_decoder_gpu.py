@@ -272,3 +272,35 @@ def test_full_size_prompt_of_512_rows_then_a_decode_row(ctx):
     assert e1 < 2e-3, e1
     ctx.device_status()
     dec.free()
+
+
+@pytest.mark.parametrize("batch", [1, 2])
+def test_fused_step_kernel_matches_the_teacher(built_lib, batch):
+    """The opt-in fused decode step (all layers in one persistent cooperative kernel, operators
+    linked by tagged stores and one grid barrier per layer): greedy tokens and logits against the
+    float64 teacher, decode calls of several lengths, a reset in between, and the phase profile."""
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from cyb_b200 import qeng
+    c = qeng.Context(0, step_kernel=1)
+    cfg = ref.DecoderConfig(**CFG)
+    W = ref.make_decoder_weights(cfg, seed=5)
+    dec = c.decoder(layers=cfg.layers, d_model=cfg.d, ffn=cfg.ffn, heads=cfg.heads, kv_heads=cfg.kv_heads,
+                    vocab=cfg.vocab, max_batch=2, max_seq=96)
+    qeng.load_decoder_weights(dec, W, cfg)
+    teacher = ref.Decoder(cfg, W)
+    for plen in (5, 37):   # 37 tokens: three pages, the newest token mid-page
+        prompt = ref.rng_of(900 + plen + batch).integers(0, cfg.vocab, (batch, plen)).astype(np.int32)
+        want, logs = teacher.generate(prompt, 9)
+        dec.reset(batch)
+        dec.prefill(prompt)
+        got = np.concatenate([dec.decode(1), dec.decode(5), dec.decode(3)], 1)
+        assert dec.launches_per_step == 2  # the step kernel and the LM head
+        c.device_status()
+        assert np.array_equal(got, want), (plen, got, want)
+        assert ref.err_inf(dec.logits(), teacher.forward(want[:, -1:], np.full((batch, 1), plen + 8))) < 2e-3
+    prof = dec.step_profile()
+    assert prof.shape == (2, cfg.layers, 16) and (np.diff(prof[0, :, :15].astype(np.int64), axis=1) >= 0).all()
+    dec.free()
+    c.close()
