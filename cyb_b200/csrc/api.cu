@@ -74,6 +74,7 @@ int32_t qeng_destroy(qeng_ctx* ctx) {
   if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);
   if (ctx->status) cudaFree(ctx->status);
   if (ctx->xbf16) cudaFree(ctx->xbf16);
+  if (ctx->ximage) cudaFree(ctx->ximage);
   if (ctx->tail_val) cudaFree(ctx->tail_val);
   if (ctx->tail_idx) cudaFree(ctx->tail_idx);
   if (ctx->tail_cnt) cudaFree(ctx->tail_cnt);

@@ -815,6 +815,10 @@ int32_t qeng_decoder_decode(qeng_ctx* ctx, qeng_decoder* d, int32_t steps, int32
   cudaStream_t st = d->stream;
   {
     int32_t rc = qeng_attn_reserve(ctx, B, d->Hq, d->Hkv, d->max_pages);  // never allocate inside the capture
+    const Layer& L0 = d->layers[0];
+    const qeng_weight* ws[4] = {L0.wqkv, L0.wo, L0.wgu, L0.wdown};
+    for (int i = 0; rc == QENG_OK && i < 4; ++i)
+      if (ws[i]) rc = qeng_gemm_q4_stream_reserve(ctx, ws[i], B < 16 ? B : 16);
     if (rc != QENG_OK) return rc;
   }
   std::vector<int32_t> pos(B), lens(B);

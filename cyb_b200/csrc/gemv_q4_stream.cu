@@ -54,7 +54,71 @@ struct StreamParams {
   int nslices;
   int32_t* status;
   qeng_qkv_epi qkv;
+  // more than 4 rows: the activations arrive quantised, as one ready-made image of the staging area
+  // per K slice (written by quantise_rows_kernel), and are brought in with one bulk copy per slice
+  const unsigned char* ximage;
+  uint32_t ximage_slice_bytes;
 };
+
+// Quantises the activation rows once per matmul (instead of once per CTA) into the exact bytes the
+// streaming kernel keeps in shared memory for a K slice: columns, accumulator start values and
+// block factors at the offsets of x_layout().  Grid (slices, rows).
+__global__ void __launch_bounds__(512) quantise_rows_kernel(const void* __restrict__ x, int x_dtype, long long ldx, int M, int K,
+                                                            const float* __restrict__ gamma, float eps, int slice_chunks,
+                                                            unsigned char* __restrict__ image, uint32_t slice_bytes) {
+  extern __shared__ __align__(16) unsigned char qsm[];
+  __shared__ float part[16];
+  const int sl = blockIdx.x, m = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const XLayout L = x_layout(2 * M, slice_chunks, false);
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  float rs = 1.f;
+  if (gamma != nullptr) {
+    float ss = 0.f;
+    for (int k = tid; k < K; k += 512) {
+      const float v = act_f32(x, x_dtype, (long long)m * ldx + k);
+      ss = fmaf(v, v, ss);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) part[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 16; ++w) tot += part[w];
+    rs = rsqrtf(tot / (float)K + eps);
+  }
+  // local copy of this row's two columns and its z / f entries
+  const uint32_t sx = smem_u32(qsm), sz = sx + 2u * L.col_stride, sf = sz + 2u * L.zs;
+  const int ngroups = L.nblk * 4;
+  for (int grp0 = 0; grp0 < ngroups; grp0 += 512) {
+    const int grp = grp0 + tid;
+    if ((grp & ~31) < ngroups) {
+      float v[8];
+      const int k0 = sl * slice_chunks * 64 + grp * 8;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[i] = 0.f;
+        if (grp < ngroups && k0 + i < K) {
+          v[i] = act_f32(x, x_dtype, (long long)m * ldx + k0 + i);
+          if (gamma != nullptr) v[i] *= gamma[k0 + i] * rs;
+        }
+      }
+      quantise_group<2>(v, grp < ngroups, sx, L.col_stride, sz, sf, L.zs, (grp >> 2) * 32, grp & 3);
+    }
+  }
+  __syncthreads();
+  unsigned char* img = image + (size_t)sl * slice_bytes;
+  const uint4* src = reinterpret_cast<const uint4*>(qsm);
+  uint4* dx = reinterpret_cast<uint4*>(img + L.xq + (size_t)(2 * m) * L.col_stride);
+  for (uint32_t i = tid; i < 2u * L.col_stride / 16u; i += 512) dx[i] = src[i];
+  uint4* dz = reinterpret_cast<uint4*>(img + L.zin + (size_t)(2 * m) * L.zs);
+  const uint4* srz = reinterpret_cast<const uint4*>(qsm + 2u * L.col_stride);
+  for (uint32_t i = tid; i < 2u * L.zs / 16u; i += 512) dz[i] = srz[i];
+  uint4* df = reinterpret_cast<uint4*>(img + L.fex + (size_t)(2 * m) * L.zs);
+  const uint4* srf = reinterpret_cast<const uint4*>(qsm + 2u * L.col_stride + 2u * L.zs);
+  for (uint32_t i = tid; i < 2u * L.zs / 16u; i += 512) df[i] = srf[i];
+}
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(kCT) : "memory"); }
 // the warps of one tile group (named barriers 2, 3, ...)
@@ -82,13 +146,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
   // carve: ring | activations (128-byte aligned) | reduction buffers | slice accumulators | barriers
   unsigned char* ring = smem;
   unsigned char* xreg = smem + (((size_t)NS * stage_bytes + 127) & ~(size_t)127);
-  float* red = reinterpret_cast<float*>(xreg + L.bytes);          // [kTG][2][kGW][kMR * 16]
+  const bool two_areas = MODE == kMN && p.ximage != nullptr;
+  float* red = reinterpret_cast<float*>(xreg + (two_areas ? 2u * ((L.bytes + 127u) & ~127u) : L.bytes));  // [kTG][2][kGW][kMR * 16]
   constexpr int red_stride = kMR * 16;
   float* accsm = red + kTG * 2 * kGW * red_stride;                 // [tiles of this CTA][kMR * 16] (several slices only)
   const int my_tiles = p.ntiles > (int)blockIdx.x ? (p.ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
   const int max_tiles = (p.ntiles + (int)gridDim.x - 1) / (int)gridDim.x;
   uint64_t* full = reinterpret_cast<uint64_t*>(accsm + (p.nslices > 1 ? (size_t)max_tiles * red_stride : 0));
   uint64_t* empty = full + kMaxStages;
+  __shared__ __align__(8) uint64_t xbar[2];  // arrival of a slice image (two staging areas, used in turn)
+  const bool imaged = MODE == kMN && p.ximage != nullptr;
+  const uint32_t ximg_stride = (L.bytes + 127u) & ~127u;  // second staging area right behind the first
   __shared__ float warp_part[2 * kCW], rinv[16];
   const uint32_t xbase = smem_u32(xreg);
   (void)my_tiles;
@@ -99,6 +167,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
       mbar_init(smem_u32(full + s), 1);
       mbar_init(smem_u32(empty + s), kGW);
     }
+    mbar_init(smem_u32(xbar), 1);
+    mbar_init(smem_u32(xbar + 1), 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncthreads();
@@ -195,7 +265,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
   };
   const int ngroups = L.nblk * 4;  // (block, quad lane) groups of the staged slice, padding included
 
-  if (p.nslices == 1) {
+  if (imaged) {
+    // the first slice's image is requested now; later ones one slice ahead (see the main loop)
+    if (tid == 0) {
+      mbar_expect_tx(smem_u32(xbar), L.bytes);
+      bulk_g2s(xbase, p.ximage, L.bytes, smem_u32(xbar));
+    }
+  } else if (p.nslices == 1) {
     // ---- whole K staged once; a thread keeps its groups in registers across the norm's reduction.
     // The raw values of row m + 1 are requested before row m is reduced and converted, so with
     // several activation rows only the first one waits for memory.
@@ -271,7 +347,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
   int tcount = 0, buf = 0, use = 0;
   for (int sl = 0; sl < p.nslices; ++sl) {
     const int cs0 = sl * p.slice_chunks, cs1 = min(p.nchunks, cs0 + p.slice_chunks);
-    if (p.nslices > 1) {
+    uint32_t xb = xbase;  // this slice's staging area
+    if (imaged) {
+      if (sl > 0) consumer_sync();  // every warp is done with the slice before: its area may be refilled
+      if (tid == 0 && sl + 1 < p.nslices) {
+        const int nb = (sl + 1) & 1;
+        mbar_expect_tx(smem_u32(xbar + nb), L.bytes);
+        bulk_g2s(xbase + (uint32_t)nb * ximg_stride, p.ximage + (size_t)(sl + 1) * p.ximage_slice_bytes, L.bytes, smem_u32(xbar + nb));
+      }
+      xb = xbase + (uint32_t)(sl & 1) * ximg_stride;
+      if (!failed && !mbar_wait(smem_u32(xbar + (sl & 1)), (uint32_t)(sl >> 1) & 1u)) failed = true;
+    } else if (p.nslices > 1) {
       if (sl > 0) consumer_sync();  // every warp is done with the previous slice's activations
       for (int m = 0; m < p.M; ++m) {
         const float rs = p.gamma != nullptr ? rinv[m] : 1.f;
@@ -303,10 +389,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
         const uint32_t wb = smem_u32(ring) + (uint32_t)s * stage_bytes;
         const uint32_t sb = wb + (uint32_t)p.stage_chunks * 512u;
         const int blk0 = (c0 - cs0) * 2;
-        if (MODE == kM1L3) consume_m1l3<kGW>(acc1, wb, sb, nc, blk0, L, xbase, wi, lane);
-        else if (MODE == kM1L2) consume_g4<kGW>(acc1, wb, sb, nc, blk0, L, xbase, wi, lane);
-        else if (MODE == kM2L2) consume_g2<kGW>(acc1, wb, sb, nc, blk0, L, xbase, wi, lane);
-        else consume_g1<kGW, NT>(accn, wb, sb, nc, blk0, L, xbase, p.cols, wi, lane);
+        if (MODE == kM1L3) consume_m1l3<kGW>(acc1, wb, sb, nc, blk0, L, xb, wi, lane);
+        else if (MODE == kM1L2) consume_g4<kGW>(acc1, wb, sb, nc, blk0, L, xb, wi, lane);
+        else if (MODE == kM2L2) consume_g2<kGW>(acc1, wb, sb, nc, blk0, L, xb, wi, lane);
+        else consume_g1<kGW, NT>(accn, wb, sb, nc, blk0, L, xb, p.cols, wi, lane);
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(empty + s));  // this warp is done with the stage
       }
@@ -433,6 +519,8 @@ int32_t launch_stream(qeng_ctx* ctx, const StreamParams& p, size_t smem, cudaStr
 struct StreamFit {
   bool ok;
   int mode, NT, cols, nstages, stage_chunks, slice_chunks, nslices;
+  bool imaged;
+  uint32_t image_slice_bytes;
   size_t smem;
 };
 
@@ -452,14 +540,17 @@ StreamFit stream_fit(const qeng_ctx* ctx, const qeng_weight* w, int64_t M, bool 
   const int tiles_per_cta = (int)((w->ntiles + grid - 1) / grid);
   const size_t budget = 226 * 1024 - 1024;
   const size_t bars = 2 * kMaxStages * 8;
+  f.imaged = M > 4;  // quantised once by a small kernel, copied in per slice
   auto plan = [&](int slice) -> bool {
     const int nsl = (nch + slice - 1) / slice;
-    if (nsl == 1 && nch * 64 > 8 * kGroups * kCT) return false;  // single-slice staging goes through registers: K <= 12288
+    if (!f.imaged && nsl == 1 && nch * 64 > 8 * kGroups * kCT) return false;  // single-slice staging goes through registers: K <= 12288
     const int alloc = f.mode == kM1L2 ? (slice + 1) & ~1 : slice;
     const XLayout L = x_layout(f.cols, alloc, f.mode != kMN);
     const size_t red = (size_t)2 * kCW * kMR * 16 * 4;  // the same for every number of tile groups
     const size_t accs = nsl > 1 ? (size_t)tiles_per_cta * kMR * 16 * 4 : 0;
-    const size_t fixed = L.bytes + red + accs + bars + 256;
+    const size_t xarea = f.imaged ? 2 * (((size_t)L.bytes + 127) & ~(size_t)127) : L.bytes;
+    const size_t fixed = xarea + red + accs + bars + 256;
+    f.image_slice_bytes = (L.bytes + 127u) & ~127u;
     const int sc = slice < 64 ? slice : 64;
     const size_t slot = (size_t)sc * 576;
     if (fixed + 2 * slot > budget) return false;
@@ -478,6 +569,24 @@ StreamFit stream_fit(const qeng_ctx* ctx, const qeng_weight* w, int64_t M, bool 
 }  // namespace
 
 bool qeng_gemm_q4_stream_fits(const qeng_ctx* ctx, const qeng_weight* w, int64_t M) { return stream_fit(ctx, w, M, false).ok; }
+
+// Grow the context's activation-image scratch to what a matmul of M rows over `w` needs (never
+// inside a stream capture: the decoder calls this before it captures a step).
+int32_t qeng_gemm_q4_stream_reserve(qeng_ctx* ctx, const qeng_weight* w, int64_t M) {
+  const StreamFit f = stream_fit(ctx, w, M, false);
+  if (!f.ok || !f.imaged) return QENG_OK;
+  const size_t need = (size_t)f.nslices * f.image_slice_bytes;
+  if (need <= ctx->ximage_bytes) return QENG_OK;
+  QENG_CUDA(ctx, cudaSetDevice(ctx->device));
+  QENG_CUDA(ctx, cudaDeviceSynchronize());
+  if (ctx->ximage) cudaFree(ctx->ximage);
+  ctx->ximage = nullptr;
+  ctx->ximage_bytes = 0;
+  QENG_CUDA(ctx, cudaMalloc(&ctx->ximage, need));
+  ctx->ximage_bytes = need;
+  ctx->scratch_gen++;
+  return QENG_OK;
+}
 
 // *handled = false when the shape does not fit this kernel; the caller then uses the
 // register-streaming kernel.
@@ -505,6 +614,32 @@ int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
   if (fuse.epilogue == QENG_EPI_QKV) {
     if (!fuse.qkv) return qeng_fail(ctx, QENG_ERR_ARG, "gemm_q4: fused q|k|v epilogue without its arguments");
     p.qkv = *fuse.qkv;
+  }
+  p.ximage = nullptr; p.ximage_slice_bytes = f.image_slice_bytes;
+  if (f.imaged) {
+    int32_t rr = qeng_gemm_q4_stream_reserve(ctx, w, M);  // grows outside the steady state only
+    if (rr != QENG_OK) return rr;
+    const XLayout L = x_layout(f.cols, f.slice_chunks, false);
+    const size_t qsmem = 2 * (size_t)L.col_stride + 4 * (size_t)L.zs;
+    static bool qconf[64] = {};
+    if (!qconf[ctx->device & 63]) {
+      QENG_CUDA(ctx, cudaFuncSetAttribute(quantise_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+      qconf[ctx->device & 63] = true;
+    }
+    if (qsmem > 64 * 1024) return qeng_fail(ctx, QENG_ERR_SHAPE, "gemm_q4: K slice too wide for the activation quantiser");
+    cudaLaunchConfig_t qc = {};
+    qc.gridDim = dim3((unsigned)f.nslices, (unsigned)M);
+    qc.blockDim = dim3(512);
+    qc.dynamicSmemBytes = qsmem;
+    qc.stream = stream;
+    cudaLaunchAttribute qa[1];
+    qa[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    qa[0].val.programmaticStreamSerializationAllowed = 1;
+    qc.attrs = qa;
+    qc.numAttrs = ctx->pdl ? 1 : 0;
+    QENG_CUDA(ctx, cudaLaunchKernelEx(&qc, quantise_rows_kernel, x, (int)x_dtype, (long long)ldx, (int)M, (int)w->K, fuse.norm_gamma,
+                                      fuse.norm_eps, f.slice_chunks, reinterpret_cast<unsigned char*>(ctx->ximage), f.image_slice_bytes));
+    p.ximage = reinterpret_cast<const unsigned char*>(ctx->ximage);
   }
   *handled = true;
   // Tile groups: more groups hide more of the per-tile reduction, but a group with no tile idles,

@@ -49,6 +49,9 @@ struct qeng_ctx {
   // bf16 copy of f32 activations for the tensor-core prefill matmul
   void* xbf16 = nullptr;
   size_t xbf16_bytes = 0;
+  // activations quantised once per decode-batch matmul (more than 4 rows), one image per K slice
+  void* ximage = nullptr;
+  size_t ximage_bytes = 0;
   // tensor parallelism (tp.cu)
   void* nccl_comm = nullptr;
   int tp_rank = 0, tp_world = 1;
@@ -134,6 +137,7 @@ int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
                             bool* handled);
 // true when the streaming kernel takes this shape (its fused-only epilogues may then be used)
 bool qeng_gemm_q4_stream_fits(const qeng_ctx* ctx, const qeng_weight* w, int64_t M);
+int32_t qeng_gemm_q4_stream_reserve(qeng_ctx* ctx, const qeng_weight* w, int64_t M);
 
 // ops.cu: LM head with optional fused RMSNorm and optional greedy finalisation (argmax over the
 // vocabulary, record the token, advance the sequences, gather the next embedding) in one launch.
