@@ -959,6 +959,12 @@ int32_t qeng_decoder_weight(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, int32
 
 int32_t qeng_decoder_launches_per_step(const qeng_decoder* d) { return d ? d->launches : 0; }
 
+int32_t qeng_decoder_config(qeng_ctx* ctx, const qeng_decoder* d, qeng_model_cfg* out) {
+  if (!d || !out) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_config: null argument");
+  *out = d->cfg;
+  return QENG_OK;
+}
+
 int32_t qeng_decoder_step_profile(qeng_ctx* ctx, qeng_decoder* d, uint64_t* out_ns, int32_t capacity, int32_t* n_written) {
   if (!ctx || !d || !out_ns || !n_written) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_step_profile: null argument");
   *n_written = 0;

@@ -121,6 +121,9 @@ _sig("qeng_decoder_layer", _i32, _vp, _vp, _i32, _vp, _vp, _i32, _vp, _vp)
 _sig("qeng_decoder_set_stream", _i32, _vp, _vp, _vp)
 _sig("qeng_decoder_weight", _i32, _vp, _vp, _i32, _i32, C.POINTER(_vp))
 _sig("qeng_decoder_launches_per_step", _i32, _vp)
+_sig("qeng_decoder_config", _i32, _vp, _vp, C.POINTER(ModelCfg))
+_sig("qeng_model_file_config", _i32, _vp, C.c_char_p, C.POINTER(ModelCfg), C.POINTER(_i64))
+_sig("qeng_decoder_load_file", _i32, _vp, _vp, C.c_char_p)
 _sig("qeng_decoder_step_profile", _i32, _vp, _vp, _vp, _i32, C.POINTER(_i32))
 
 
@@ -421,6 +424,10 @@ class Decoder:
         self.ctx.check(_lib.qeng_decoder_load_matrix(self.ctx.h, self.h, layer, which, _np_ptr(q), _np_ptr(s),
                                                      q.shape[0], q.shape[1]))
 
+    def load_file(self, path):
+        """Load all weights from a `.model` container (qeng_decoder_load_file)."""
+        self.ctx.check(_lib.qeng_decoder_load_file(self.ctx.h, self.h, str(path).encode()))
+
     def load_norm(self, layer, which, gamma):
         g = np.ascontiguousarray(gamma, dtype=np.float32)
         self.ctx.check(_lib.qeng_decoder_load_norm(self.ctx.h, self.h, layer, which, _np_ptr(g)))
@@ -493,6 +500,16 @@ class Decoder:
                 self.free()
         except Exception:
             pass
+
+
+def model_file_config(path, ctx=None):
+    """(ModelCfg, number of tensors) of a `.model` container; raises QengError on a malformed file."""
+    cfg = ModelCfg()
+    n = _i64(0)
+    rc = _lib.qeng_model_file_config(ctx.h if ctx is not None else None, str(path).encode(), C.byref(cfg), C.byref(n))
+    if rc != 0:
+        raise QengError(rc, _lib.qeng_last_error(ctx.h).decode() if ctx is not None else "malformed model file")
+    return cfg, n.value
 
 
 def load_decoder_weights(dec, W, cfg):

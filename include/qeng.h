@@ -249,6 +249,21 @@ int32_t qeng_decoder_load_norm(qeng_ctx* ctx, qeng_decoder* dec, int32_t layer, 
  * a decode step exchanges one (max, index) pair per sequence and rank to pick the token. */
 int32_t qeng_decoder_load_head(qeng_ctx* ctx, qeng_decoder* dec, const uint16_t* emb, const uint16_t* lm_head,
                                const float* final_gamma);
+/* The configuration a decoder was created with. */
+int32_t qeng_decoder_config(qeng_ctx* ctx, const qeng_decoder* dec, qeng_model_cfg* out);
+/* ---- `.model` containers (".cyb -> graph IR ... tensor index, tensor data (Q4/Q8/F16/F32)",
+ *      decide/pipeline.md:28-30; container rules reference/format.md:16-18,110-117; the reference
+ *      maps its model files, shell/src/lib.rs:31-33).  The tensor-index schema is this engine's own
+ *      (the `cyb-model` page is not in the reference checkout); INTEGRATION.md writes it down.
+ * Read a container's `config` into a qeng_model_cfg (max_batch = 1, max_seq = 0, tp = 1/0: the
+ * caller sets those before qeng_decoder_create) and count its tensors.  ctx may be NULL. */
+int32_t qeng_model_file_config(qeng_ctx* ctx, const char* path, qeng_model_cfg* out, int64_t* n_tensors);
+/* Load every layer matrix, norm gain, embedding and LM head of a container into a decoder whose
+ * configuration matches the file's (with tensor parallelism every rank reads the same file and
+ * keeps its shard).  Q4 tensors are re-tiled from the mapped file; F32 / F16 / BF16 linear weights
+ * are quantised on the device first; `lm_head.weight` may be absent (tied to the embedding);
+ * `self_attn.q_norm / k_norm` are optional.  Synchronous. */
+int32_t qeng_decoder_load_file(qeng_ctx* ctx, qeng_decoder* dec, const char* path);
 /* Forget all sequences (KV lengths to zero). */
 int32_t qeng_decoder_reset(qeng_ctx* ctx, qeng_decoder* dec, int32_t batch);
 /* Prompt phase: tokens HOST int32 [batch, T]; fills the KV cache and leaves the
