@@ -72,6 +72,53 @@ class SomaConfig:
     model_path: Optional[str] = None
 
 
+@dataclass
+class MindStatus:
+    """What the mind runs and how its answers went: the running means cyb keeps per answer
+    (`MindStatus::push_speed`, shell/src/worlds/models/mod.rs:36-52; fed from the Answer event,
+    shell/src/worlds/soma_bridge.rs:303-305; cleared of its last rate when the model changes,
+    models/mod.rs:386-394)."""
+    model: Optional[str] = None
+    last_tok_per_s: Optional[float] = None
+    avg_tok_in_s: float = 0.0
+    avg_tok_out_s: float = 0.0
+    n_speed: int = 0
+
+    def push_speed(self, tok_in_s: float, tok_out_s: float) -> None:
+        n = float(self.n_speed)
+        self.n_speed += 1
+        k = float(self.n_speed)
+        self.avg_tok_in_s = (self.avg_tok_in_s * n + tok_in_s) / k
+        self.avg_tok_out_s = (self.avg_tok_out_s * n + tok_out_s) / k
+
+    def observe(self, event) -> None:
+        """Feed every polled event through here to keep the status current."""
+        if isinstance(event, Answer):
+            self.last_tok_per_s = event.tok_per_s
+            self.push_speed(event.tok_in_s, event.tok_out_s)
+        elif isinstance(event, ModelChanged):
+            self.model = event.path
+            self.last_tok_per_s = None
+
+
+def model_file_engine(ctx, max_seq: int = 2048):
+    """Engine factory over `.model` containers: `factory(path)` reads the container's config, creates a
+    decoder of that shape on `ctx` and loads the file into it (what `use_model(path)` followed by
+    the next ask amounts to; weights are held until the next switch)."""
+    from cyb_b200 import qeng
+
+    def factory(path):
+        if path is None:
+            raise ValueError("no model chosen (SomaConfig.model_path / use_model)")
+        mc, _ = qeng.model_file_config(path, ctx)
+        dec = ctx.decoder(layers=mc.layers, d_model=mc.d_model, ffn=mc.ffn, heads=mc.heads, kv_heads=mc.kv_heads,
+                          vocab=mc.vocab, head_dim=mc.head_dim, rms_eps=mc.rms_eps, rope_base=mc.rope_base,
+                          max_batch=1, max_seq=max_seq)
+        dec.load_file(path)
+        return dec
+    return factory
+
+
 def encode(text: str) -> List[int]:
     return list(text.encode("utf-8"))
 
@@ -149,6 +196,8 @@ class Soma:
                 if item[0] == "stop":
                     return
                 if item[0] == "model":
+                    if self._engine is not None and hasattr(self._engine, "free"):
+                        self._engine.free()  # the old weights go before the new ones are mapped
                     self._engine = None  # reload lazily
                     self._model_path = item[1]
                     self._events.put(ModelChanged(item[1]))

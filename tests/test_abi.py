@@ -55,3 +55,21 @@ def test_product_does_not_import_the_oracle():
             if f.endswith((".py", ".cu", ".h", ".cpp")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text.replace("no oracle", ""), os.path.join(dirpath, f)
+
+
+def test_rust_declarations_name_every_symbol():
+    """bindings/qeng.rs (uncompiled: no Rust toolchain here) declares exactly the header's functions."""
+    import re
+    from cyb_b200 import qeng
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    rs = open(os.path.join(root, "bindings", "qeng.rs")).read()
+    declared = sorted(set(re.findall(r"pub fn (qeng_[a-z0-9_]+)\(", rs)))
+    assert declared == qeng.declared_symbols()
+    # the two plain structs carry the header's fields in the header's order
+    hdr = open(qeng.HEADER_PATH).read()
+    for struct in ("qeng_options", "qeng_model_cfg"):
+        body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (struct, struct), hdr, re.S).group(1)
+        body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+        c_fields = re.findall(r"([a-z_0-9]+)\s*[,;]", body)
+        r_body = re.search(r"pub struct %s \{(.*?)\}" % struct, rs, re.S).group(1)
+        assert re.findall(r"pub ([a-z_0-9]+):", r_body) == c_fields, struct
