@@ -81,20 +81,6 @@ __device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ uint4 ld_volatile16(const void* p) {
-  uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_pair(uint2* p, float v, unsigned tag) {
-  asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};\n" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
-}
-
-// what a CTA-wide wait does when it ran out: record, and never wait again in this launch
-struct Waits {
-  bool failed = false;
-};
-
 // All consumer warps of all CTAs.  `target` = arrivals that complete this barrier.
 __device__ __forceinline__ void grid_barrier(unsigned* cnt, unsigned target, int tid, Waits& w, int32_t* status) {
   consumer_sync();
@@ -114,51 +100,6 @@ __device__ __forceinline__ void grid_barrier(unsigned* cnt, unsigned target, int
     __threadfence();
   }
   consumer_sync();
-}
-
-// Eight (value, tag) pairs at `src` (64 bytes, 16-byte aligned) -> out[8], waiting until all carry `tag`.
-__device__ __forceinline__ void poll8(const uint2* src, unsigned tag, float (&out)[8], Waits& w, int32_t* status) {
-  unsigned long long t0 = 0;
-  for (int spin = 0;; ++spin) {
-    const uint4 a = ld_volatile16(src), b = ld_volatile16(src + 2), c = ld_volatile16(src + 4), d = ld_volatile16(src + 6);
-    const bool ok = a.y == tag && a.w == tag && b.y == tag && b.w == tag && c.y == tag && c.w == tag && d.y == tag && d.w == tag;
-    if (ok || w.failed) {
-      out[0] = __uint_as_float(a.x); out[1] = __uint_as_float(a.z); out[2] = __uint_as_float(b.x); out[3] = __uint_as_float(b.z);
-      out[4] = __uint_as_float(c.x); out[5] = __uint_as_float(c.z); out[6] = __uint_as_float(d.x); out[7] = __uint_as_float(d.z);
-      return;
-    }
-    __nanosleep(200);  // thousands of threads poll: keep them off the L2 while the data is on its way
-    if ((spin & 255) == 255) {
-      const unsigned long long t1 = globaltimer();
-      if (t0 == 0) t0 = t1;
-      if (t1 - t0 > 2000000000ull) {
-        atomicExch(status, 5);
-        w.failed = true;
-      }
-    }
-  }
-}
-
-// Two pairs (16 bytes, 16-byte aligned)
-__device__ __forceinline__ void poll2(const uint2* src, unsigned tag, float (&out)[2], Waits& w, int32_t* status) {
-  unsigned long long t0 = 0;
-  for (int spin = 0;; ++spin) {
-    const uint4 a = ld_volatile16(src);
-    if ((a.y == tag && a.w == tag) || w.failed) {
-      out[0] = __uint_as_float(a.x);
-      out[1] = __uint_as_float(a.z);
-      return;
-    }
-    __nanosleep(200);  // thousands of threads poll: keep them off the L2 while the data is on its way
-    if ((spin & 255) == 255) {
-      const unsigned long long t1 = globaltimer();
-      if (t0 == 0) t0 = t1;
-      if (t1 - t0 > 2000000000ull) {
-        atomicExch(status, 5);
-        w.failed = true;
-      }
-    }
-  }
 }
 
 enum { kEpiQkv = 0, kEpiPush = 1, kEpiSwiglu = 2 };

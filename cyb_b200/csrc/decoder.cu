@@ -182,6 +182,7 @@ struct qeng_decoder {
   // activations (rows = batch in decode, batch*T in prefill)
   int64_t rows_cap = 0;
   float *x = nullptr, *qkv = nullptr, *att = nullptr, *act = nullptr, *part = nullptr;
+  float* xalt = nullptr;  // second residual buffer: a fused tensor-parallel gather reads one and writes the other
   float *xnr = nullptr, *gu = nullptr;  // prefill only: normalised rows, gate|up before SwiGLU
   __half* q16 = nullptr;
   int32_t *pos = nullptr, *lens = nullptr, *table = nullptr, *tok = nullptr;  // per row
@@ -225,7 +226,7 @@ int32_t ensure_rows(qeng_ctx* ctx, qeng_decoder* d, int64_t rows) {
   QENG_CUDA(ctx, cudaDeviceSynchronize());
   if (d->graph) { cudaGraphExecDestroy(d->graph); d->graph = nullptr; }
   qeng_step_free(d->fused); d->fused = nullptr; d->step_planned = false;
-  float** fb[] = {&d->x, &d->qkv, &d->att, &d->act, &d->part, &d->xnr, &d->gu};
+  float** fb[] = {&d->x, &d->xalt, &d->qkv, &d->att, &d->act, &d->part, &d->xnr, &d->gu};
   for (auto p : fb)
     if (*p) { cudaFree(*p); *p = nullptr; }
   if (d->q16) { cudaFree(d->q16); d->q16 = nullptr; }
@@ -235,6 +236,7 @@ int32_t ensure_rows(qeng_ctx* ctx, qeng_decoder* d, int64_t rows) {
   d->rows_cap = 0;
   const int64_t dm = d->cfg.d_model;
   QENG_CUDA(ctx, cudaMalloc(&d->x, rows * dm * 4));
+  QENG_CUDA(ctx, cudaMalloc(&d->xalt, rows * dm * 4));
   QENG_CUDA(ctx, cudaMalloc(&d->qkv, rows * d->nqkv * 4));
   QENG_CUDA(ctx, cudaMalloc(&d->att, rows * d->Hq * kHD * 4));
   QENG_CUDA(ctx, cudaMalloc(&d->act, rows * d->F * 4));
@@ -361,15 +363,26 @@ int32_t run_layer_prefill(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, c
 }
 
 // One layer over `rows` rows whose positions / lengths / page-table rows are on the device.
-int32_t run_layer(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, const int32_t* table, cudaStream_t st) {
+// `px`, when given (decode steps with mapped peers), selects the fused tensor-parallel form: o and
+// down send their partial sums from the epilogue to every rank's inbox, the next matmul's staging
+// adds the parts onto the residual rows of *px and leaves the result in the other residual buffer,
+// to which *px then points.  No collective kernel runs.
+int32_t run_layer(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, const int32_t* table, cudaStream_t st, float** px = nullptr) {
   Layer& L = d->layers[l];
   if (!L.wqkv || !L.wo || !L.wgu || !L.wdown || !L.norm1 || !L.norm2)
     return qeng_fail(ctx, QENG_ERR_STATE, "decoder: layer %d is not fully loaded", l);
   if (rows >= kPrefillRows) return run_layer_prefill(ctx, d, l, rows, table, st);
   const int64_t dm = d->cfg.d_model;
+  const bool fused = px != nullptr;
+  float* x = fused ? *px : d->x;
+  auto other = [&](float* cur) { return cur == d->x ? d->xalt : d->x; };
   __half* pool = d->pool + (size_t)l * d->pages * d->Hkv * 2 * kPage * kHD;
   qeng_gemm_fuse f;
   f.norm_gamma = L.norm1; f.norm_eps = d->cfg.rms_eps; f.epilogue = QENG_EPI_STORE;
+  f.tp_layers = d->cfg.layers;
+  if (fused && l > 0) {  // the parts of the previous layer's down projection
+    f.tp_gather_kind = 1; f.tp_gather_layer = l - 1; f.tp_writeback = other(x);
+  }
   int32_t rc;
   if ((L.qnorm == nullptr) != (L.knorm == nullptr))
     return qeng_fail(ctx, QENG_ERR_STATE, "decoder: layer %d has only one of the q / k head gains", l);
@@ -379,28 +392,45 @@ int32_t run_layer(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, const int
     E.pos = d->pos; E.table = table; E.cs = d->rope_cs; E.q16 = d->q16; E.pool = pool;
     E.max_pages = d->max_pages; E.pages = (int)d->pages; E.Hq = d->Hq; E.Hkv = d->Hkv; E.max_seq = d->cfg.max_seq;
     f.epilogue = QENG_EPI_QKV; f.qkv = &E;
-    rc = mm(ctx, d, L.wqkv, d->x, dm, rows, d->qkv, d->nqkv, f, st);
+    rc = mm(ctx, d, L.wqkv, x, dm, rows, d->qkv, d->nqkv, f, st);
     if (rc != QENG_OK) return rc;
   } else {
-    rc = mm(ctx, d, L.wqkv, d->x, dm, rows, d->qkv, d->nqkv, f, st);
+    rc = mm(ctx, d, L.wqkv, x, dm, rows, d->qkv, d->nqkv, f, st);
     if (rc != QENG_OK) return rc;
     rope_append_kernel<<<(unsigned)rows, 256, 0, st>>>(d->qkv, d->rope_cs, d->pos, table, d->max_pages, (int)d->pages,
                                                        d->Hq, d->Hkv, d->cfg.max_seq, d->q16, pool, ctx->status, L.qnorm, L.knorm, d->cfg.rms_eps);
     QENG_LAUNCH_CHECK(ctx);
     d->launches++;
   }
+  if (f.tp_gather_kind >= 0) x = other(x);  // the gathered rows are the residual stream from here on
   d->view.pages = d->pages; d->view.kv_heads = d->Hkv; d->view.hd = kHD; d->view.data = pool;
   rc = qeng_attn_decode(ctx, &d->view, reinterpret_cast<const uint16_t*>(d->q16), table, d->max_pages, d->lens, rows,
                         d->Hq, 1.0f / sqrtf((float)kHD), d->att, st);
   if (rc != QENG_OK) return rc;
   d->launches += 1;
-  rc = row_split(ctx, d, L.wo, d->att, (int64_t)d->Hq * kHD, rows, st);
-  if (rc != QENG_OK) return rc;
   qeng_gemm_fuse fg;
   fg.norm_gamma = L.norm2; fg.norm_eps = d->cfg.rms_eps; fg.epilogue = QENG_EPI_SWIGLU; fg.two_limbs = true;
-  rc = mm(ctx, d, L.wgu, d->x, dm, rows, d->act, d->F, fg, st);
+  fg.tp_layers = d->cfg.layers;
+  if (!fused) {
+    rc = row_split(ctx, d, L.wo, d->att, (int64_t)d->Hq * kHD, rows, st);
+    if (rc != QENG_OK) return rc;
+    rc = mm(ctx, d, L.wgu, d->x, dm, rows, d->act, d->F, fg, st);
+    if (rc != QENG_OK) return rc;
+    return row_split(ctx, d, L.wdown, d->act, d->F, rows, st);
+  }
+  qeng_gemm_fuse fp;
+  fp.epilogue = QENG_EPI_STORE; fp.two_limbs = true; fp.tp_layers = d->cfg.layers; fp.tp_layer = l;
+  fp.tp_push_kind = 0;
+  rc = mm(ctx, d, L.wo, d->att, (int64_t)d->Hq * kHD, rows, d->part, dm, fp, st);
   if (rc != QENG_OK) return rc;
-  return row_split(ctx, d, L.wdown, d->act, d->F, rows, st);
+  fg.tp_gather_kind = 0; fg.tp_gather_layer = l; fg.tp_writeback = other(x);
+  rc = mm(ctx, d, L.wgu, x, dm, rows, d->act, d->F, fg, st);
+  if (rc != QENG_OK) return rc;
+  x = other(x);
+  fp.tp_push_kind = 1;
+  rc = mm(ctx, d, L.wdown, d->act, d->F, rows, d->part, dm, fp, st);
+  *px = x;
+  return rc;
 }
 
 // sharded LM head: every rank fills its vocabulary columns of the logits, in chunks of up to 4 rows
@@ -495,11 +525,21 @@ int32_t plan_step(qeng_ctx* ctx, qeng_decoder* d) {
 // one decode step, all state on the device: x holds the embedding of the token to feed
 int32_t decode_step(qeng_ctx* ctx, qeng_decoder* d, cudaStream_t st) {
   const int B = d->batch;
+  const bool fused = d->cfg.tp_world > 1 && qeng_tp_fuse_ready(ctx, B, d->cfg.d_model);
+  float* x = d->x;
   for (int l = 0; l < d->cfg.layers; ++l) {
-    int32_t rc = run_layer(ctx, d, l, B, d->dec_table, st);
+    int32_t rc = run_layer(ctx, d, l, B, d->dec_table, st, fused ? &x : nullptr);
     if (rc != QENG_OK) return rc;
   }
-  return tail(ctx, d, d->x, B, true, st);
+  if (fused) {
+    // the one gather no matmul absorbs: the parts of the last down projection, added in place
+    int32_t rc = qeng_tp_fuse_gather(ctx, x, B, d->cfg.d_model, 1, d->cfg.layers - 1, d->cfg.layers, st);
+    if (rc != QENG_OK) return rc;
+    d->launches += 2;
+  }
+  int32_t rc = tail(ctx, d, x, B, true, st);  // leaves the next token's embedding in d->x
+  if (rc == QENG_OK && fused) rc = qeng_tp_fuse_advance(ctx, st);
+  return rc;
 }
 
 // shard of a full host matrix: rows [r0,r1) x columns [k0,k1)
@@ -612,7 +652,7 @@ int32_t qeng_decoder_free(qeng_ctx* ctx, qeng_decoder* d) {
     if (L.qnorm) cudaFree(L.qnorm);
     if (L.knorm) cudaFree(L.knorm);
   }
-  void* bufs[] = {d->emb, d->lm_head, d->final_norm, d->rope_cs, d->pool, d->x, d->qkv, d->att, d->act, d->part, d->xnr, d->gu, d->q16,
+  void* bufs[] = {d->emb, d->lm_head, d->final_norm, d->rope_cs, d->pool, d->x, d->xalt, d->qkv, d->att, d->act, d->part, d->xnr, d->gu, d->q16,
                   d->pos, d->lens, d->table, d->tok, d->xn, d->xlast, d->logits, d->next, d->out_tokens, d->step, d->dec_table, d->tp_pairs, d->tp_gath};
   for (void* p : bufs)
     if (p) cudaFree(p);

@@ -58,6 +58,14 @@ struct StreamParams {
   // per K slice (written by quantise_rows_kernel), and are brought in with one bulk copy per slice
   const unsigned char* ximage;
   uint32_t ximage_slice_bytes;
+  // tensor parallelism carried by the matmuls (qeng_gemm_fuse::tp_push_kind / tp_gather_kind)
+  uint2* push_inbox[8];        // every rank's inbox of the push kind, as mapped here
+  int push_world, push_rank;   // push_world = 0: the epilogue writes y as usual
+  const uint2* gather_inbox;   // this rank's inbox of the gather kind
+  int gather_world;            // 0: x is used as it is
+  float* x_writeback;          // the gathered rows, written by CTA 0 (the residual stream itself)
+  const unsigned* tp_seq;      // decode steps completed: the tag base
+  unsigned tp_tags_per_step, push_tag_off, gather_tag_off;
 };
 
 // Quantises the activation rows once per matmul (instead of once per CTA) into the exact bytes the
@@ -65,18 +73,49 @@ struct StreamParams {
 // block factors at the offsets of x_layout().  Grid (slices, rows).
 __global__ void __launch_bounds__(512) quantise_rows_kernel(const void* __restrict__ x, int x_dtype, long long ldx, int M, int K,
                                                             const float* __restrict__ gamma, float eps, int slice_chunks,
-                                                            unsigned char* __restrict__ image, uint32_t slice_bytes) {
+                                                            unsigned char* __restrict__ image, uint32_t slice_bytes,
+                                                            const uint2* __restrict__ gather_inbox, int gather_world,
+                                                            const unsigned* __restrict__ tp_seq, unsigned tags_per_step,
+                                                            unsigned gather_tag_off, float* __restrict__ x_writeback,
+                                                            int32_t* status) {
   extern __shared__ __align__(16) unsigned char qsm[];
   __shared__ float part[16];
   const int sl = blockIdx.x, m = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const XLayout L = x_layout(2 * M, slice_chunks, false);
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  // With a gather, the row (f32) is first completed in shared memory: x + the ranks' tagged parts, in
+  // rank order; the CTA of slice 0 writes it back as the new residual row.
+  float* xrow = nullptr;
+  if (gather_world > 0) {
+    xrow = reinterpret_cast<float*>(qsm + 2u * L.col_stride + 4u * L.zs);
+    const unsigned tag = *tp_seq * tags_per_step + gather_tag_off + 1u;
+    Waits W;
+    for (int k0 = tid * 8; k0 < K; k0 += 512 * 8) {
+      const float4* xp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + (long long)m * ldx + k0);
+      float4 a = xp[0], b = xp[1];
+      for (int r = 0; r < gather_world; ++r) {
+        float pt[8];
+        poll8(gather_inbox + ((size_t)r * kTpFuseRows + m) * kTpFuseDm + k0, tag, pt, W, status);
+        a.x += pt[0]; a.y += pt[1]; a.z += pt[2]; a.w += pt[3];
+        b.x += pt[4]; b.y += pt[5]; b.z += pt[6]; b.w += pt[7];
+      }
+      *reinterpret_cast<float4*>(xrow + k0) = a;
+      *reinterpret_cast<float4*>(xrow + k0 + 4) = b;
+      if (sl == 0) {
+        float4* wp = reinterpret_cast<float4*>(x_writeback + (long long)m * ldx + k0);
+        wp[0] = a;
+        wp[1] = b;
+      }
+    }
+    __syncthreads();
+  }
+  auto xval = [&](int k) { return xrow ? xrow[k] : act_f32(x, x_dtype, (long long)m * ldx + k); };
   float rs = 1.f;
   if (gamma != nullptr) {
     float ss = 0.f;
     for (int k = tid; k < K; k += 512) {
-      const float v = act_f32(x, x_dtype, (long long)m * ldx + k);
+      const float v = xval(k);
       ss = fmaf(v, v, ss);
     }
 #pragma unroll
@@ -100,7 +139,7 @@ __global__ void __launch_bounds__(512) quantise_rows_kernel(const void* __restri
       for (int i = 0; i < 8; ++i) {
         v[i] = 0.f;
         if (grp < ngroups && k0 + i < K) {
-          v[i] = act_f32(x, x_dtype, (long long)m * ldx + k0 + i);
+          v[i] = xval(k0 + i);
           if (gamma != nullptr) v[i] *= gamma[k0 + i] * rs;
         }
       }
@@ -220,6 +259,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
   // The weights never change, so only the consumers wait for the kernel that produced the
   // activations (a no-op unless launched with programmatic stream serialization).
   asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  // tags of this call's pushes and gathers (the step counter is only stable behind the wait above)
+  const unsigned tp_step = p.tp_seq != nullptr ? *p.tp_seq : 0u;
+  const unsigned tag_push = tp_step * p.tp_tags_per_step + p.push_tag_off + 1u;
+  const unsigned tag_gather = tp_step * p.tp_tags_per_step + p.gather_tag_off + 1u;
+  Waits TW;
+  (void)tag_gather;
   // the zero region other blocks' lanes read (several blocks per fragment)
   if (kZeroed)
     for (uint32_t o = (uint32_t)tid * 16u; o < x_zero_bytes(L); o += kCT * 16u)
@@ -287,6 +332,26 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
       if (m + 1 < p.M) {
 #pragma unroll
         for (int j = 0; j < kGroups; ++j) load8(m + 1, (tid + j * kCT) * 8, nv[j]);
+      }
+      if (p.gather_world > 0) {
+        // the ranks' parts of the residual update, added in rank order (the same bits on every rank)
+#pragma unroll
+        for (int j = 0; j < kGroups; ++j) {
+          const int kk = (tid + j * kCT) * 8;
+          if (kk < p.K) {
+            for (int r = 0; r < p.gather_world; ++r) {
+              float pt[8];
+              poll8(p.gather_inbox + ((size_t)r * kTpFuseRows + m) * kTpFuseDm + kk, tag_gather, pt, TW, p.status);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[j][i] += pt[i];
+            }
+            if (blockIdx.x == 0) {
+              float4* wp = reinterpret_cast<float4*>(p.x_writeback + (long long)m * p.ldx + kk);
+              wp[0] = make_float4(v[j][0], v[j][1], v[j][2], v[j][3]);
+              wp[1] = make_float4(v[j][4], v[j][5], v[j][6], v[j][7]);
+            }
+          }
+        }
       }
       float rs = 1.f;
       if (p.gamma != nullptr) {
@@ -474,6 +539,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
             const float gate = total(a, r), up = total(a, r + 8);
             p.y[(size_t)a * p.ldy + (size_t)tile * 8 + r] = gate / (1.0f + __expf(-gate)) * up;
           }
+        } else if (p.push_world > 0) {
+          // this rank's part of the residual update, tagged, into every rank's inbox (own included)
+          for (int e = lane; e < p.M * 16; e += 32) {
+            const int a = e >> 4, r = e & 15;
+            const float v = total(a, r);
+            const size_t o = ((size_t)p.push_rank * kTpFuseRows + a) * kTpFuseDm + (size_t)tile * 16 + r;
+            for (int rr = 0; rr < p.push_world; ++rr) st_pair(p.push_inbox[(p.push_rank + rr) % p.push_world] + o, v, tag_push);
+          }
         } else {
           for (int e = lane; e < p.M * 16; e += 32) {
             const int a = e >> 4, r = e & 15;
@@ -615,12 +688,32 @@ int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
     if (!fuse.qkv) return qeng_fail(ctx, QENG_ERR_ARG, "gemm_q4: fused q|k|v epilogue without its arguments");
     p.qkv = *fuse.qkv;
   }
+  p.push_world = 0; p.gather_world = 0; p.gather_inbox = nullptr; p.x_writeback = nullptr; p.tp_seq = nullptr;
+  p.push_rank = ctx->tp_rank; p.tp_tags_per_step = 2u * (unsigned)fuse.tp_layers; p.push_tag_off = 0; p.gather_tag_off = 0;
+  for (int r = 0; r < 8; ++r) p.push_inbox[r] = nullptr;
+  if (fuse.tp_push_kind >= 0 || fuse.tp_gather_kind >= 0) {
+    if (!qeng_tp_fuse_ready(ctx, M, fuse.tp_push_kind >= 0 ? w->N : w->K) || x_dtype != QENG_F32 || (ldx & 3) != 0)
+      return qeng_fail(ctx, QENG_ERR_STATE, "gemm_q4: the fused tensor-parallel forms need mapped peers, f32 rows and at most %d rows", kTpFuseRows);
+    p.tp_seq = qeng_tp_fuse_seq(ctx);
+    if (fuse.tp_push_kind >= 0) {
+      p.push_world = ctx->tp_world;
+      for (int r = 0; r < ctx->tp_world; ++r) p.push_inbox[r] = qeng_tp_fuse_inbox(ctx, r, fuse.tp_push_kind);
+      p.push_tag_off = 2u * (unsigned)fuse.tp_layer + (unsigned)fuse.tp_push_kind;
+    }
+    if (fuse.tp_gather_kind >= 0) {
+      p.gather_world = ctx->tp_world;
+      p.gather_inbox = qeng_tp_fuse_inbox(ctx, ctx->tp_rank, fuse.tp_gather_kind);
+      p.gather_tag_off = 2u * (unsigned)fuse.tp_gather_layer + (unsigned)fuse.tp_gather_kind;
+      if (!fuse.tp_writeback || fuse.tp_writeback == x) return qeng_fail(ctx, QENG_ERR_ARG, "gemm_q4: a gather needs a write-back buffer other than x");
+      p.x_writeback = fuse.tp_writeback;
+    }
+  }
   p.ximage = nullptr; p.ximage_slice_bytes = f.image_slice_bytes;
   if (f.imaged) {
     int32_t rr = qeng_gemm_q4_stream_reserve(ctx, w, M);  // grows outside the steady state only
     if (rr != QENG_OK) return rr;
     const XLayout L = x_layout(f.cols, f.slice_chunks, false);
-    const size_t qsmem = 2 * (size_t)L.col_stride + 4 * (size_t)L.zs;
+    const size_t qsmem = 2 * (size_t)L.col_stride + 4 * (size_t)L.zs + (p.gather_world > 0 ? (size_t)w->K * 4 : 0);
     static bool qconf[64] = {};
     if (!qconf[ctx->device & 63]) {
       QENG_CUDA(ctx, cudaFuncSetAttribute(quantise_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
@@ -638,7 +731,11 @@ int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
     qc.attrs = qa;
     qc.numAttrs = ctx->pdl ? 1 : 0;
     QENG_CUDA(ctx, cudaLaunchKernelEx(&qc, quantise_rows_kernel, x, (int)x_dtype, (long long)ldx, (int)M, (int)w->K, fuse.norm_gamma,
-                                      fuse.norm_eps, f.slice_chunks, reinterpret_cast<unsigned char*>(ctx->ximage), f.image_slice_bytes));
+                                      fuse.norm_eps, f.slice_chunks, reinterpret_cast<unsigned char*>(ctx->ximage), f.image_slice_bytes,
+                                      p.gather_inbox, p.gather_world, p.tp_seq, p.tp_tags_per_step, p.gather_tag_off, p.x_writeback,
+                                      ctx->status));
+    // the main kernel then sees completed activations: its own staging gathers nothing
+    p.gather_world = 0;
     p.ximage = reinterpret_cast<const unsigned char*>(ctx->ximage);
   }
   *handled = true;

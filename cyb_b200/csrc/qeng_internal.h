@@ -59,6 +59,7 @@ struct qeng_ctx {
   void* p2p_local = nullptr;
   void* p2p_peer[8] = {};
   size_t p2p_flag_off = 0, p2p_counter_off = 0;
+  size_t p2p_fuse_off = 0;    // fused-decode inbox region inside the peer-mapped buffer
   bool p2p_ready = false;
   bool l2_prefetch = true;    // the streaming matmul requests the hinted next matrix into L2
   bool pdl = true;            // launch the streaming matmul with programmatic stream serialization
@@ -119,7 +120,18 @@ struct qeng_gemm_fuse {
   const float* resid = nullptr;       // QENG_EPI_RESID: y = resid + x.W^T
   const qeng_qkv_epi* qkv = nullptr;  // QENG_EPI_QKV (streaming kernel only)
   bool two_limbs = false;             // a single activation row in 15 instead of 22 bits (QENG_GEMM_FAST_F16)
+  // Tensor parallelism without a collective of its own (decode steps of up to kTpFuseRows rows):
+  //   tp_push_kind >= 0: the epilogue sends this rank's partial sums, tagged, to every rank's inbox
+  //                      of that kind (0: after o, 1: after down) instead of writing y;
+  //   tp_gather_kind >= 0: the staging first adds all ranks' parts of that kind (tag of tp_gather_layer)
+  //                      onto x, in rank order, and CTA 0 writes the updated rows back to x.
+  int tp_push_kind = -1, tp_gather_kind = -1, tp_layer = 0, tp_gather_layer = 0, tp_layers = 1;
+  float* tp_writeback = nullptr;      // where CTA 0 leaves the gathered rows: NOT x itself (other CTAs still read x)
 };
+constexpr int kTpFuseRows = 16;      // activation rows an inbox holds
+constexpr int kTpFuseDm = 8192;      // widest residual stream an inbox holds
+// bytes of the fused-decode inbox region: [2 kinds][world][kTpFuseRows][kTpFuseDm] (value, tag) pairs
+inline size_t qeng_tp_fuse_bytes(int world) { return (size_t)2 * world * kTpFuseRows * kTpFuseDm * 8; }
 // SWIGLU: rows g (gate) and g+8 (up) of every 16-row tile are combined into one
 // output y[8*tile + g] = silu(gate) * up, so y has N/2 columns.
 enum { QENG_EPI_STORE = 0, QENG_EPI_ACCUM = 1, QENG_EPI_RESID = 2, QENG_EPI_SWIGLU = 3, QENG_EPI_QKV = 4 };
@@ -195,6 +207,12 @@ int32_t qeng_tp_all_reduce_internal(qeng_ctx* ctx, float* buf, int64_t n, cudaSt
 void qeng_tp_release(qeng_ctx* ctx);
 bool qeng_tp_p2p_ready(const qeng_ctx* ctx, int64_t n);
 int32_t qeng_tp_allreduce_add(qeng_ctx* ctx, float* dst, const float* part, int64_t n, cudaStream_t stream);
+// fused decode (the matmuls carry the collective): see qeng_gemm_fuse::tp_push_kind
+bool qeng_tp_fuse_ready(const qeng_ctx* ctx, int64_t rows, int64_t dm);
+uint2* qeng_tp_fuse_inbox(const qeng_ctx* ctx, int r, int kind);
+const unsigned* qeng_tp_fuse_seq(const qeng_ctx* ctx);
+int32_t qeng_tp_fuse_gather(qeng_ctx* ctx, float* x, int64_t rows, int64_t dm, int kind, int layer, int layers, cudaStream_t stream);
+int32_t qeng_tp_fuse_advance(qeng_ctx* ctx, cudaStream_t stream);
 
 // gemm_q4_tc.cu: tcgen05 prefill matmul (bf16 operands, f32 accumulation in tensor memory)
 int32_t qeng_gemm_q4_prefill(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t x_dtype, int64_t M, int64_t ldx,

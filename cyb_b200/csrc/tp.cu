@@ -193,9 +193,11 @@ int32_t qeng_tp_p2p_handle(qeng_ctx* ctx, uint8_t* out64) {
   if (!ctx->p2p_local) {
     const size_t inbox = (size_t)2 * ctx->tp_world * kP2pMaxElems * sizeof(uint2);
     ctx->p2p_flag_off = inbox;
-    ctx->p2p_counter_off = inbox;
-    QENG_CUDA(ctx, cudaMalloc(&ctx->p2p_local, inbox + 256));
-    QENG_CUDA(ctx, cudaMemset(ctx->p2p_local, 0, inbox + 256));
+    ctx->p2p_counter_off = inbox;   // [0] calls completed, [1] CTAs done, [2] decode steps completed (tag base of the fused inbox)
+    ctx->p2p_fuse_off = inbox + 256;
+    const size_t total = inbox + 256 + qeng_tp_fuse_bytes(ctx->tp_world);
+    QENG_CUDA(ctx, cudaMalloc(&ctx->p2p_local, total));
+    QENG_CUDA(ctx, cudaMemset(ctx->p2p_local, 0, total));
   }
   cudaIpcMemHandle_t h;
   QENG_CUDA(ctx, cudaIpcGetMemHandle(&h, ctx->p2p_local));
@@ -230,7 +232,7 @@ int32_t qeng_tp_p2p_reset(qeng_ctx* ctx) {
   QENG_CUDA(ctx, cudaSetDevice(ctx->device));
   QENG_CUDA(ctx, cudaDeviceSynchronize());
   const size_t inbox = (size_t)2 * ctx->tp_world * kP2pMaxElems * sizeof(uint2);
-  QENG_CUDA(ctx, cudaMemset(ctx->p2p_local, 0, inbox + 256));  // tags and the call counter start over
+  QENG_CUDA(ctx, cudaMemset(ctx->p2p_local, 0, inbox + 256 + qeng_tp_fuse_bytes(ctx->tp_world)));  // tags and the counters start over
   QENG_CUDA(ctx, cudaMemset(ctx->status, 0, 4));
   return QENG_OK;
 }
@@ -258,3 +260,55 @@ int32_t qeng_tp_all_reduce_f32(qeng_ctx* ctx, float* buf, int64_t n, void* strea
 }
 
 }  // extern "C"
+
+// ---- fused decode: what is left of the collective when the matmuls carry it ----------------------
+#include "gemm_q4_s8.cuh"
+
+// x[rows][dm] += sum over ranks of the parts of `kind` tagged for (step, layer): the one gather of a
+// decode step that no matmul staging absorbs (after the last layer's down projection).
+__global__ void __launch_bounds__(256) tp_fuse_gather_kernel(float* __restrict__ x, const uint2* __restrict__ inbox, int rows, int dm,
+                                                             int world, const unsigned* __restrict__ seq, unsigned tags_per_step,
+                                                             unsigned tag_off, int32_t* status) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;  // group of 8 values
+  const int per_row = dm / 8;
+  if (g >= rows * per_row) return;
+  const int m = g / per_row, k0 = (g - m * per_row) * 8;
+  const unsigned tag = *seq * tags_per_step + tag_off + 1u;
+  q4s8::Waits W;
+  float4* xp = reinterpret_cast<float4*>(x + (size_t)m * dm + k0);
+  float4 a = xp[0], b = xp[1];
+  for (int r = 0; r < world; ++r) {
+    float part[8];
+    q4s8::poll8(inbox + ((size_t)r * kTpFuseRows + m) * kTpFuseDm + k0, tag, part, W, status);
+    a.x += part[0]; a.y += part[1]; a.z += part[2]; a.w += part[3];
+    b.x += part[4]; b.y += part[5]; b.z += part[6]; b.w += part[7];
+  }
+  xp[0] = a;
+  xp[1] = b;
+}
+__global__ void tp_fuse_advance_kernel(unsigned* seq) { *seq += 1u; }
+
+bool qeng_tp_fuse_ready(const qeng_ctx* ctx, int64_t rows, int64_t dm) {
+  return ctx->tp_world > 1 && ctx->p2p_ready && rows <= kTpFuseRows && dm <= kTpFuseDm && (dm & 7) == 0;
+}
+// inbox of `kind` as mapped on this rank for peer r (own rank included)
+uint2* qeng_tp_fuse_inbox(const qeng_ctx* ctx, int r, int kind) {
+  char* base = reinterpret_cast<char*>(ctx->p2p_peer[r]) + ctx->p2p_fuse_off;
+  return reinterpret_cast<uint2*>(base) + (size_t)kind * ctx->tp_world * kTpFuseRows * kTpFuseDm;
+}
+const unsigned* qeng_tp_fuse_seq(const qeng_ctx* ctx) {
+  return reinterpret_cast<const unsigned*>(reinterpret_cast<const char*>(ctx->p2p_local) + ctx->p2p_counter_off) + 2;
+}
+int32_t qeng_tp_fuse_gather(qeng_ctx* ctx, float* x, int64_t rows, int64_t dm, int kind, int layer, int layers, cudaStream_t stream) {
+  const int groups = (int)(rows * dm / 8);
+  tp_fuse_gather_kernel<<<(groups + 255) / 256, 256, 0, stream>>>(x, qeng_tp_fuse_inbox(ctx, ctx->tp_rank, kind), (int)rows, (int)dm,
+                                                                   ctx->tp_world, qeng_tp_fuse_seq(ctx), 2u * (unsigned)layers,
+                                                                   2u * (unsigned)layer + (unsigned)kind, ctx->status);
+  QENG_LAUNCH_CHECK(ctx);
+  return QENG_OK;
+}
+int32_t qeng_tp_fuse_advance(qeng_ctx* ctx, cudaStream_t stream) {
+  tp_fuse_advance_kernel<<<1, 1, 0, stream>>>(const_cast<unsigned*>(qeng_tp_fuse_seq(ctx)));
+  QENG_LAUNCH_CHECK(ctx);
+  return QENG_OK;
+}
