@@ -100,4 +100,12 @@ int32_t qeng_device_status(qeng_ctx* ctx) {
 
 int32_t qeng_sm_count(const qeng_ctx* ctx) { return ctx ? ctx->sm_count : 0; }
 
+#ifdef QENG_TRACE
+// tuning builds only: the 64 bytes behind the status pointer (status word + 7 timestamps)
+int32_t qeng_debug_status_words(qeng_ctx* ctx, unsigned long long* out8) {
+  cudaDeviceSynchronize();
+  return cudaMemcpy(out8, ctx->status, 64, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -4;
+}
+#endif
+
 }  // extern "C"

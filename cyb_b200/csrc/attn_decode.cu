@@ -1,13 +1,16 @@
 // Decode attention (GQA) over a paged f16 KV cache, split over the KV length.
 //
 // Pool layout: f16 [page][kv head][K|V][16 tokens][128], so the K tile and the
-// V tile of one (page, kv head) are 4 KB contiguous each.  One CTA serves one
-// (sequence, kv head, split): its warps take pages round-robin, load the K and
-// V tiles straight into MMA fragments with 128-bit loads (the contraction
-// index of an MMA may be permuted freely as long as both operands agree, which
-// lets every lane load contiguous 16-byte pieces), and keep an online softmax
-// (max, sum, out) per query head of the group.  Warps are merged in shared
-// memory.  Splits: the eight CTAs of a thread-block cluster take the pages of a
+// V tile of one (page, kv head) are 8 KB contiguous.  One CTA serves one
+// (sequence, kv head, split).  A producer warp looks up the page ids and brings
+// the CTA's page tiles into a ring of 8 KB shared-memory slots with bulk
+// asynchronous copies (cp.async.bulk, completion counted on an mbarrier), so the
+// bytes in flight per SM (two CTAs x 80 KB) do not depend on registers.  Four
+// consumer warps take the slots round-robin, read the K and V tiles into MMA
+// fragments with 128-bit shared loads (the contraction index of an MMA may be
+// permuted freely as long as both operands agree, which lets every lane read
+// contiguous 16-byte pieces), and keep an online softmax (max, sum, out) per
+// query head of the group.  Warps are merged in shared memory.  Splits: the eight CTAs of a thread-block cluster take the pages of a
 // sequence round-robin and merge through distributed shared memory (no scratch,
 // no atomics); caches beyond 16K tokens fall back to fixed page ranges merged
 // through a scratch buffer by the CTA that arrives last.
@@ -20,7 +23,10 @@
 
 namespace {
 
-constexpr int kAW = 4;  // warps per CTA
+constexpr int kAW = 4;  // consumer warps per CTA (one more warp produces)
+constexpr int kAT = (kAW + 1) * 32;  // threads per CTA
+constexpr int kRing = 10;            // ring slots of one page tile (K and V of 16 tokens: 8 KB)
+constexpr int kSlotBytes = 2 * 16 * 128 * 2;
 constexpr int kHD = 128;
 constexpr int kCS = 8;  // largest cluster: CTAs (splits) per sequence and kv head; the launch picks 1, 2, 4 or 8
 
@@ -51,7 +57,50 @@ struct AttnParams {
   int* counters;   // [B][Hkv] arrivals per (sequence, kv head); null = merge in a second kernel
   int pages, Hkv, Hq, grp, max_pages, pps, S;
   float scale_log2;
+  float scale, softcap;  // softcap > 0: logits = softcap * tanh(q.k * scale / softcap) (Gemma family)
+  int window;            // > 0: only the last `window` tokens of a sequence are attended (sliding window)
 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(1000u)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up (false) two seconds after the first failed attempt.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t0));
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t1;
+    asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t1));
+    if (t1 - t0 > 2000000000ull) return false;
+  }
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  return *reinterpret_cast<const uint4*>(__cvta_shared_to_generic((size_t)addr));
+}
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -76,40 +125,39 @@ template <bool kCl>
 __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
   // the output projection that follows may start streaming its weights as CTAs of this kernel retire
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  extern __shared__ __align__(128) unsigned char ring[];  // kRing slots of one page tile (K then V)
+  __shared__ __align__(8) uint64_t full[kRing], empty[kRing];
+  __shared__ int slot_ok[kRing];
   const int s = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  // Pages of this warp: first, first + stride, ... below p1.  In a cluster the CTAs interleave the
-  // pages of the sequence (page = CTA rank + 8 * (warp + 4 i)), whatever its length, so the page
-  // ids can be fetched before the length is known; otherwise a CTA owns pages [p0, p0 + pps).
-  const int cs = p.S;  // cluster path: CTAs in the cluster (= gridDim.x)
-  const int p0 = kCl ? s + cs * warp : s * p.pps + warp;
-  const int pstride = kCl ? cs * kAW : kAW;
-  int my_pid = -1;
-  if (kCl) {  // lane i holds the id of the warp's i-th page (caches up to cs * 4 * 32 pages)
-    const int pg = p0 + lane * pstride;
-    if (pg < p.max_pages) my_pid = p.table[(size_t)b * p.max_pages + pg];
+  if (tid == 0) {
+    for (int i = 0; i < kRing; ++i) {
+      mbar_init(smem_u32(full + i), 1);
+      mbar_init(smem_u32(empty + i), 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
+  __syncthreads();
+  // Pages of this CTA, in order: in a cluster the CTAs interleave the pages of the sequence (page =
+  // first + cs * i), otherwise a CTA owns the pages [first, first + pps).  With a sliding window the
+  // pages that lie entirely before the window are not visited at all.
+  const int cs = p.S;  // cluster path: CTAs in the cluster (= gridDim.x)
   const int len = p.lens[b];
   const int npages = min((len + 15) >> 4, p.max_pages);
-  if (!kCl && s * p.pps >= npages) {
-    if (p.counters != nullptr && s == 0)  // empty sequence: nobody else writes its output
+  const int win0 = p.window > 0 ? max(0, len - p.window) : 0;  // first token inside the window
+  const int pg_first = win0 >> 4;
+  const int first = kCl ? pg_first + s : pg_first + s * p.pps;
+  const int pstep = kCl ? cs : 1;
+  const int pend = kCl ? npages : min(npages, pg_first + s * p.pps + p.pps);
+  const int n_mine = first < pend ? (pend - first + pstep - 1) / pstep : 0;
+  if (!kCl && n_mine == 0) {
+    if (p.counters != nullptr && s == 0 && tid < kHD)  // empty sequence: nobody else writes its output
       for (int hh = 0; hh < p.grp; ++hh) p.out[((size_t)b * p.Hq + (size_t)h * p.grp + hh) * kHD + tid] = 0.f;
     return;
   }
-  const int p1 = kCl ? npages : min(npages, s * p.pps + p.pps);
 
   __shared__ float sm_o[kAW][8][kHD];
   __shared__ float sm_m[kAW][8], sm_l[kAW][8];
-
-  // Q fragments: row g of the A operand = query head h*grp+g (rows >= grp are zero)
-  uint4 qa[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) qa[i] = make_uint4(0u, 0u, 0u, 0u);
-  if (g < p.grp) {
-    const uint4* qp = reinterpret_cast<const uint4*>(p.q + ((size_t)b * p.Hq + (size_t)h * p.grp + g) * kHD);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) qa[i] = qp[i * 4 + t];
-  }
 
   float m_run = -INFINITY, l_run = 0.f;
   float o[16][4];
@@ -118,124 +166,144 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
 
-  // Page tiles are double-buffered in registers: the loads of the next tile are in flight while the
-  // tensor cores work on the current one.
-  // all page ids of this warp are fetched up front (lane i holds the id of the warp's i-th page), so a
-  // tile load is one memory round trip, not a table lookup followed by a dependent load
-  if (!kCl) {
-    const int pg = p0 + lane * pstride;  // at most 64 pages per split: 16 per warp
-    if (pg < p1) my_pid = p.table[(size_t)b * p.max_pages + pg];
-  }
-  auto load_tile = [&](int pg, uint4 (&kq)[2][4], uint4 (&vv)[4][2]) -> bool {
-    const int pid = __shfl_sync(0xffffffffu, my_pid, kCl ? ((pg - p0) / kAW) / cs : (pg - p0) / kAW);
-    if ((unsigned)pid >= (unsigned)p.pages) {  // malformed page table: record and skip
-      if (lane == 0) atomicExch(p.status, 1);
-      return false;
-    }
-    const uint4* kt = reinterpret_cast<const uint4*>(p.pool + ((size_t)pid * p.Hkv + h) * (2 * 16 * kHD));
-    const uint4* vt = kt + 16 * kHD / 8;
-    // K rows of tokens g and g+8: the 16 bytes at d = 32i + 8t .. +7
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) kq[nt][i] = ldg_nc(kt + (nt * 8 + g) * 16 + i * 4 + t);
-    // V rows of tokens 2t, 2t+1, 2t+8, 2t+9: d = 8g..8g+7 and 64+8g..64+8g+7
-#pragma unroll
-    for (int x = 0; x < 4; ++x) {
-      const int tk = 2 * t + (x & 1) + ((x >> 1) << 3);
-#pragma unroll
-      for (int r = 0; r < 2; ++r) vv[x][r] = ldg_nc(vt + tk * 16 + r * 8 + g);
-    }
-    return true;
-  };
-  auto compute_tile = [&](int pg, uint4 (&kq)[2][4], uint4 (&vv)[4][2]) {
-    // S = Q K^T for 16 tokens: two n-tiles of 8 tokens
-    float sacc[2][4];
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        mma16816(sacc[nt], qa[i].x, 0u, qa[i].y, 0u, kq[nt][i].x, kq[nt][i].y);
-        mma16816(sacc[nt], qa[i].z, 0u, qa[i].w, 0u, kq[nt][i].z, kq[nt][i].w);
+  if (warp == kAW) {
+    // ===== producer: page ids 32 at a time, one 8 KB bulk copy per page ==========================
+    bool failed = false;
+    for (int base = 0; base < n_mine; base += 32) {
+      const int i = base + lane;
+      int pid = -1;
+      if (i < n_mine) pid = p.table[(size_t)b * p.max_pages + first + i * pstep];
+      const int cnt = min(32, n_mine - base);
+      for (int j = 0; j < cnt; ++j) {
+        const int pj = __shfl_sync(0xffffffffu, pid, j);
+        if (lane == 0) {
+          const int it = base + j, slot = it % kRing;
+          if (!failed && !mbar_wait(smem_u32(empty + slot), ((uint32_t)(it / kRing) & 1u) ^ 1u)) failed = true;
+          const uint32_t bar = smem_u32(full + slot);
+          if ((unsigned)pj >= (unsigned)p.pages) {  // malformed page table: record, hand over an empty slot
+            atomicExch(p.status, 1);
+            slot_ok[slot] = 0;
+            mbar_arrive(bar);
+          } else {
+            slot_ok[slot] = 1;
+            mbar_expect_tx(bar, kSlotBytes);
+            bulk_g2s(smem_u32(ring) + (uint32_t)slot * kSlotBytes, p.pool + ((size_t)pj * p.Hkv + h) * (2 * 16 * kHD), kSlotBytes, bar);
+          }
+        }
       }
     }
-    // scale (log2 domain), mask the tail of the last page
-    const int tok0 = pg * 16;
-    float sv[4];
+    if (failed && lane == 0) atomicExch(p.status, 4);
+  } else {
+    // ===== consumers =================================================================================
+    // Q fragments: row g of the A operand = query head h*grp+g (rows >= grp are zero)
+    uint4 qa[4];
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
+    for (int i = 0; i < 4; ++i) qa[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (g < p.grp) {
+      const uint4* qp = reinterpret_cast<const uint4*>(p.q + ((size_t)b * p.Hq + (size_t)h * p.grp + g) * kHD);
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int tok = tok0 + nt * 8 + 2 * t + c;
-        sv[nt * 2 + c] = tok < len ? sacc[nt][c] * p.scale_log2 : -INFINITY;
+      for (int i = 0; i < 4; ++i) qa[i] = qp[i * 4 + t];
+    }
+    auto compute_tile = [&](int pg, uint4 (&kq)[2][4], uint4 (&vv)[4][2]) {
+      // S = Q K^T for 16 tokens: two n-tiles of 8 tokens
+      float sacc[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          mma16816(sacc[nt], qa[i].x, 0u, qa[i].y, 0u, kq[nt][i].x, kq[nt][i].y);
+          mma16816(sacc[nt], qa[i].z, 0u, qa[i].w, 0u, kq[nt][i].z, kq[nt][i].w);
+        }
       }
-    float tmax = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
-    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
-    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
-    const float m_new = fmaxf(m_run, tmax);  // finite: token tok0 of a listed page is valid
-    const float alpha = exp2f(m_run - m_new);
-    float pr[4];
+      // scale (optionally soft-capped), log2 domain, mask the tail of the last page and what lies before the window
+      const int tok0 = pg * 16;
+      float sv[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) pr[i] = exp2f(sv[i] - m_new);
-    l_run = l_run * alpha + (pr[0] + pr[1] + pr[2] + pr[3]);
-    m_run = m_new;
-    if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int tok = tok0 + nt * 8 + 2 * t + c;
+          float x = sacc[nt][c] * p.scale;
+          if (p.softcap > 0.f) x = p.softcap * tanhf(x / p.softcap);
+          sv[nt * 2 + c] = (tok < len && tok >= win0) ? x * 1.4426950408889634f : -INFINITY;
+        }
+      float tmax = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+      tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+      tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+      const float m_new = fmaxf(m_run, tmax);  // finite: a listed page holds at least one attended token
+      const float alpha = exp2f(m_run - m_new);
+      float pr[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) pr[i] = exp2f(sv[i] - m_new);
+      l_run = l_run * alpha + (pr[0] + pr[1] + pr[2] + pr[3]);
+      m_run = m_new;
+      if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          o[j][0] *= alpha;
+          o[j][1] *= alpha;
+        }
+      }
+      // P as A operand, split into two f16 terms so no probability precision is lost
+      const uint32_t ph0 = pack_h2(pr[0], pr[1]), ph1 = pack_h2(pr[2], pr[3]);
+      const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&ph0));
+      const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&ph1));
+      const uint32_t pl0 = pack_h2(pr[0] - f0.x, pr[1] - f0.y), pl1 = pack_h2(pr[2] - f1.x, pr[3] - f1.y);
+      // zero V rows that are not attended (their probability is 0, but 0 * garbage may be NaN)
+      if (tok0 + 16 > len || tok0 < win0) {
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const int tok = tok0 + 2 * t + (x & 1) + ((x >> 1) << 3);
+          if (tok >= len || tok < win0) vv[x][0] = vv[x][1] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+      // O += P V : n-tile j covers d = 8n + (j&7) + 64*(j>>3), n = column of the tile
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
-        o[j][0] *= alpha;
-        o[j][1] *= alpha;
+        const int r = j >> 3, jj = j & 7;
+        const uint32_t* va = reinterpret_cast<const uint32_t*>(&vv[0][r]);
+        const uint32_t* vb = reinterpret_cast<const uint32_t*>(&vv[1][r]);
+        const uint32_t* vc = reinterpret_cast<const uint32_t*>(&vv[2][r]);
+        const uint32_t* vd = reinterpret_cast<const uint32_t*>(&vv[3][r]);
+        const uint32_t sel = (jj & 1) ? 0x7632u : 0x5410u;
+        const uint32_t b0 = __byte_perm(va[jj >> 1], vb[jj >> 1], sel);
+        const uint32_t b1 = __byte_perm(vc[jj >> 1], vd[jj >> 1], sel);
+        mma16816(o[j], ph0, 0u, ph1, 0u, b0, b1);
+        mma16816(o[j], pl0, 0u, pl1, 0u, b0, b1);
       }
-    }
-    // P as A operand, split into two f16 terms so no probability precision is lost
-    const uint32_t ph0 = pack_h2(pr[0], pr[1]), ph1 = pack_h2(pr[2], pr[3]);
-    const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&ph0));
-    const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&ph1));
-    const uint32_t pl0 = pack_h2(pr[0] - f0.x, pr[1] - f0.y), pl1 = pack_h2(pr[2] - f1.x, pr[3] - f1.y);
-    // zero V rows beyond the sequence (their probability is 0, but 0 * garbage may be NaN)
-    if (tok0 + 16 > len) {
+    };
+    bool failed = false;
+    for (int it = warp; it < n_mine; it += kAW) {
+      const int slot = it % kRing;
+      if (!failed && !mbar_wait(smem_u32(full + slot), (uint32_t)(it / kRing) & 1u)) failed = true;
+      if (slot_ok[slot]) {
+        const uint32_t kt = smem_u32(ring) + (uint32_t)slot * kSlotBytes, vt = kt + 16 * kHD * 2;
+        uint4 kq[2][4], vv[4][2];
+        // K rows of tokens g and g+8: the 16 bytes at d = 32i + 8t .. +7
 #pragma unroll
-      for (int x = 0; x < 4; ++x) {
-        const int tok = tok0 + 2 * t + (x & 1) + ((x >> 1) << 3);
-        if (tok >= len) vv[x][0] = vv[x][1] = make_uint4(0u, 0u, 0u, 0u);
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) kq[nt][i] = lds128(kt + (uint32_t)(((nt * 8 + g) * 16 + i * 4 + t) * 16));
+        // V rows of tokens 2t, 2t+1, 2t+8, 2t+9: d = 8g..8g+7 and 64+8g..64+8g+7
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const int tk = 2 * t + (x & 1) + ((x >> 1) << 3);
+#pragma unroll
+          for (int r = 0; r < 2; ++r) vv[x][r] = lds128(vt + (uint32_t)((tk * 16 + r * 8 + g) * 16));
+        }
+        compute_tile(first + it * pstep, kq, vv);
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(empty + slot));  // the slot may be refilled
     }
-    // O += P V : n-tile j covers d = 8n + (j&7) + 64*(j>>3), n = column of the tile
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const int r = j >> 3, jj = j & 7;
-      const uint32_t* va = reinterpret_cast<const uint32_t*>(&vv[0][r]);
-      const uint32_t* vb = reinterpret_cast<const uint32_t*>(&vv[1][r]);
-      const uint32_t* vc = reinterpret_cast<const uint32_t*>(&vv[2][r]);
-      const uint32_t* vd = reinterpret_cast<const uint32_t*>(&vv[3][r]);
-      const uint32_t sel = (jj & 1) ? 0x7632u : 0x5410u;
-      const uint32_t b0 = __byte_perm(va[jj >> 1], vb[jj >> 1], sel);
-      const uint32_t b1 = __byte_perm(vc[jj >> 1], vd[jj >> 1], sel);
-      mma16816(o[j], ph0, 0u, ph1, 0u, b0, b1);
-      mma16816(o[j], pl0, 0u, pl1, 0u, b0, b1);
-    }
-  };
-  {
-    uint4 kqA[2][4], vvA[4][2], kqB[2][4], vvB[4][2];
-    int pg = p0;
-    bool okA = false, okB = false;
-    if (pg < p1) okA = load_tile(pg, kqA, vvA);
-    while (pg < p1) {
-      const int pgn = pg + pstride;
-      if (pgn < p1) okB = load_tile(pgn, kqB, vvB);
-      if (okA) compute_tile(pg, kqA, vvA);
-      if (pgn >= p1) break;
-      const int pgnn = pgn + pstride;
-      if (pgnn < p1) okA = load_tile(pgnn, kqA, vvA);
-      if (okB) compute_tile(pgn, kqB, vvB);
-      pg = pgnn;
-    }
+    if (failed && lane == 0) atomicExch(p.status, 4);
   }
 
   // ---- merge the warps of this CTA ------------------------------------------
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-  if (g < p.grp) {
+  if (warp < kAW && g < p.grp) {
     if (t == 0) {
       sm_m[warp][g] = m_run;
       sm_l[warp][g] = l_run;
@@ -248,10 +316,10 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
     }
   }
   __syncthreads();
-  const int ns = kCl ? cs : (npages + p.pps - 1) / p.pps;
+  const int ns = kCl ? cs : (npages - pg_first + p.pps - 1) / p.pps;  // splits that hold pages
   const bool direct = !kCl && p.counters != nullptr && ns == 1;  // a single split: no partials needed
   __shared__ float c_o[8][kHD], c_m[8], c_l[8];  // this CTA's partial per query head (cluster merge)
-  for (int hh = 0; hh < p.grp; ++hh) {
+  for (int hh = 0; hh < p.grp && tid < kHD; ++hh) {
     float M = -INFINITY;
 #pragma unroll
     for (int w = 0; w < kAW; ++w) M = fmaxf(M, sm_m[w][hh]);
@@ -285,7 +353,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
     if (cs > 1) cluster_sync();
     else __syncthreads();
     const int dper = kHD / cs;
-    for (int e = tid; e < p.grp * dper; e += kAW * 32) {
+    for (int e = tid; e < p.grp * dper; e += kAT) {
       const int hh = e / dper, d = s * dper + e % dper;
       float mr[kCS], lr[kCS], orr[kCS];
 #pragma unroll
@@ -324,7 +392,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
   __threadfence();
   // one warp per query head; lanes first share the (max, sum) pairs of the splits, then each lane
   // merges 4 of the 128 output dims with independent (pipelined) loads
-  for (int hh = warp; hh < p.grp; hh += kAW) {
+  for (int hh = warp; hh < p.grp && warp < kAW; hh += kAW) {
     const size_t row0 = ((size_t)b * p.Hq + (size_t)h * p.grp + hh) * p.S;
     float M = -INFINITY;
     for (int s2 = lane; s2 < ns; s2 += 32) M = fmaxf(M, __ldcg(p.part_ml + (row0 + s2) * 2));
@@ -352,10 +420,10 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
   if (tid == 0) p.counters[b * p.Hkv + h] = 0;  // ready for the next call
 }
 
-__global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnParams p) { attn_decode_body<false>(p); }
+__global__ void __launch_bounds__(kAT) attn_decode_kernel(const AttnParams p) { attn_decode_body<false>(p); }
 
 // launched with a cluster dimension of (p.S, 1, 1) = (gridDim.x, 1, 1)
-__global__ void __launch_bounds__(kAW * 32) attn_decode_cluster_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kAT) attn_decode_cluster_kernel(const AttnParams p) {
   attn_decode_body<true>(p);
 }
 
@@ -363,7 +431,8 @@ __global__ void __launch_bounds__(kHD) attn_combine_kernel(const AttnParams p) {
   const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   const int len = p.lens[b];
   const int npages = min((len + 15) >> 4, p.max_pages);
-  const int ns = (npages + p.pps - 1) / p.pps;
+  const int pg_first = p.window > 0 ? max(0, len - p.window) >> 4 : 0;
+  const int ns = (npages - pg_first + p.pps - 1) / p.pps;
   const size_t row0 = ((size_t)b * p.Hq + head) * p.S;
   float M = -INFINITY;
   for (int s = 0; s < ns; ++s) M = fmaxf(M, p.part_ml[(row0 + s) * 2]);
@@ -491,35 +560,55 @@ int32_t qeng_kv_append(qeng_ctx* ctx, qeng_kv_pool* pool, const float* k, const 
   return QENG_OK;
 }
 
+// opt-in shared memory of the two attention kernels (the page-tile ring), once per device
+static int32_t attn_configure(qeng_ctx* ctx) {
+  static bool configured_on[64] = {};
+  bool& configured = configured_on[ctx->device & 63];
+  if (configured) return QENG_OK;
+  QENG_CUDA(ctx, cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing * kSlotBytes));
+  QENG_CUDA(ctx, cudaFuncSetAttribute(attn_decode_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing * kSlotBytes));
+  configured = true;
+  return QENG_OK;
+}
+
 int32_t qeng_attn_decode(qeng_ctx* ctx, const qeng_kv_pool* pool, const uint16_t* q_f16, const int32_t* page_table,
                          int64_t max_pages, const int32_t* lens, int64_t B, int64_t Hq, float scale, float* out,
                          void* stream) {
+  return qeng_attn_decode_ex(ctx, pool, q_f16, page_table, max_pages, lens, B, Hq, scale, 0.f, 0, out, stream);
+}
+
+int32_t qeng_attn_decode_ex(qeng_ctx* ctx, const qeng_kv_pool* pool, const uint16_t* q_f16, const int32_t* page_table,
+                            int64_t max_pages, const int32_t* lens, int64_t B, int64_t Hq, float scale, float softcap,
+                            int32_t window, float* out, void* stream) {
   if (!ctx || !pool || !q_f16 || !page_table || !lens || !out) return qeng_fail(ctx, QENG_ERR_ARG, "attn_decode: null argument");
   if (B <= 0 || max_pages <= 0 || Hq <= 0) return qeng_fail(ctx, QENG_ERR_ARG, "attn_decode: B, Hq, max_pages must be positive");
+  if (softcap < 0.f || window < 0) return qeng_fail(ctx, QENG_ERR_ARG, "attn_decode: softcap and window must not be negative");
   if (Hq % pool->kv_heads != 0 || Hq / pool->kv_heads > 8)
     return qeng_fail(ctx, QENG_ERR_SHAPE, "attn_decode: query heads per kv head must divide evenly and be <= 8");
   if (((reinterpret_cast<uintptr_t>(q_f16) | reinterpret_cast<uintptr_t>(out)) & 15) != 0)
     return qeng_fail(ctx, QENG_ERR_ALIGN, "attn_decode: q and out must be 16-byte aligned");
   QENG_ENTER(ctx);
+  int32_t rc0 = attn_configure(ctx);
+  if (rc0 != QENG_OK) return rc0;
   AttnParams p;
   p.pool = pool->data; p.q = reinterpret_cast<const __half*>(q_f16);
   p.table = page_table; p.lens = lens; p.out = out; p.status = ctx->status;
   p.pages = (int)pool->pages; p.Hkv = (int)pool->kv_heads; p.Hq = (int)Hq; p.grp = (int)(Hq / pool->kv_heads);
   p.max_pages = (int)max_pages;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.scale = scale; p.softcap = softcap; p.window = window;
   const bool no_cluster = !ctx->attn_cluster;
   // Cluster path: 1, 2, 4 or 8 CTAs per (sequence, kv head), as many as keep the grid within about one
-  // wave (two CTAs per SM), merged through distributed shared memory.  A lane holds one page id per
-  // tile of its warp, which caps the cache at cs * 4 * 32 pages; beyond that the fixed splits below.
+  // wave (two CTAs per SM), merged through distributed shared memory; caches beyond 16K tokens and
+  // long caches at large batch (bandwidth-bound, a little faster there) take the fixed splits below.
   int cs = kCS;
   while (cs > 1 && B * pool->kv_heads * cs > 2 * (int64_t)ctx->sm_count) cs >>= 1;
-  while (cs < kCS && max_pages > cs * kAW * 32) cs <<= 1;
-  // (long caches at large batch are bandwidth-bound and measured a little faster on the fixed splits)
-  if (!no_cluster && max_pages <= cs * kAW * 32 && B * pool->kv_heads * max_pages <= 16384) {
+  if (!no_cluster && max_pages <= 1024 && B * pool->kv_heads * max_pages <= 16384) {
     p.pps = 0; p.S = cs; p.counters = nullptr; p.part_o = nullptr; p.part_ml = nullptr;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)cs, (unsigned)p.Hkv, (unsigned)B);
-    cfg.blockDim = dim3(kAW * 32);
+    cfg.blockDim = dim3(kAT);
+    cfg.dynamicSmemBytes = kRing * kSlotBytes;
     cfg.stream = (cudaStream_t)stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -539,7 +628,7 @@ int32_t qeng_attn_decode(qeng_ctx* ctx, const qeng_kv_pool* pool, const uint16_t
   p.part_o = ctx->attn_scratch + kMaxAttnCounters;
   p.part_ml = p.part_o + (size_t)B * Hq * p.S * kHD;
   dim3 grid((unsigned)p.S, (unsigned)p.Hkv, (unsigned)B);
-  attn_decode_kernel<<<grid, kAW * 32, 0, (cudaStream_t)stream>>>(p);
+  attn_decode_kernel<<<grid, kAT, kRing * kSlotBytes, (cudaStream_t)stream>>>(p);
   QENG_LAUNCH_CHECK(ctx);
   return QENG_OK;
 }
@@ -582,12 +671,17 @@ int32_t qeng_attn_decode_noalloc(qeng_ctx* ctx, const qeng_kv_pool* pool, const 
   p.pages = (int)pool->pages; p.Hkv = (int)pool->kv_heads; p.Hq = (int)Hq; p.grp = (int)(Hq / pool->kv_heads);
   p.max_pages = (int)max_pages;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.scale = scale; p.softcap = 0.f; p.window = 0;
+  {
+    int32_t rc0 = attn_configure(ctx);
+    if (rc0 != QENG_OK) return rc0;
+  }
   // every partial that the merge reads is written by this call first: nothing has to start at zero
   p.counters = nullptr;  // merge in a second kernel
   p.part_o = scratch;
   p.part_ml = scratch + (size_t)B * Hq * p.S * kHD;
   dim3 grid((unsigned)p.S, (unsigned)p.Hkv, (unsigned)B);
-  attn_decode_kernel<<<grid, kAW * 32, 0, (cudaStream_t)stream>>>(p);
+  attn_decode_kernel<<<grid, kAT, kRing * kSlotBytes, (cudaStream_t)stream>>>(p);
   QENG_LAUNCH_CHECK(ctx);
   dim3 grid2((unsigned)Hq, (unsigned)B);
   attn_combine_kernel<<<grid2, kHD, 0, (cudaStream_t)stream>>>(p);

@@ -25,7 +25,12 @@
 #pragma once
 #include "qeng_internal.h"
 
+#ifndef QENG_G4_UNROLL
+#define QENG_G4_UNROLL 2
+#endif
+
 namespace q4s8 {
+constexpr int kG4Unroll = QENG_G4_UNROLL;  // items of the one-row loop in flight per warp
 
 constexpr int kCW = 16;               // consumer warps
 constexpr int kCT = kCW * 32;         // consumer threads
@@ -230,15 +235,16 @@ __device__ __forceinline__ void consume_g4(float (&acc)[2], uint32_t wbase, uint
   const int g = lane >> 2, t = lane & 3;
   const int limb = t >> 1;      // this lane's output columns: limb, blocks 2(t&1), 2(t&1)+1 of the item
   const int myblk = g & 3;      // this lane's B column: limb g>>2, block g&3 of the item
-  const uint32_t xcol = xbase + L.xq + (uint32_t)(g >> 2) * L.col_stride + (uint32_t)t * 8u;
-  const uint32_t zcol = xbase + L.zero + (uint32_t)(g >> 2) * 64u + (uint32_t)t * 8u;
-  uint32_t xa[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) xa[j] = (myblk == j ? xcol : zcol) + (uint32_t)(blk0 + j) * 32u;
+  // The lane reads the activation bytes of its own column once per item; in the MMA of another
+  // block its B registers are zero (selected, not loaded: shared-memory bandwidth is the scarcer
+  // resource in this loop).
+  const uint32_t xa = xbase + L.xq + (uint32_t)(g >> 2) * L.col_stride + (uint32_t)t * 8u + (uint32_t)(blk0 + myblk) * 32u;
   const uint32_t zin = xbase + L.zin + (uint32_t)limb * L.zs + (uint32_t)(blk0 + 2 * (t & 1)) * 4u;
   const uint32_t fex = xbase + L.fex + (uint32_t)limb * L.zs + (uint32_t)(blk0 + 2 * (t & 1)) * 4u;
+  const uint32_t k0 = myblk == 0 ? 0xffffffffu : 0u, k1 = myblk == 1 ? 0xffffffffu : 0u, k2 = myblk == 2 ? 0xffffffffu : 0u,
+                 k3 = myblk == 3 ? 0xffffffffu : 0u;
   const int nitems = (nc + 1) >> 1;
-#pragma unroll 2
+#pragma unroll kG4Unroll
   for (int it = wi; it < nitems; it += NW) {
     const uint32_t wo = wbase + (uint32_t)it * 1024u + (uint32_t)lane * 16u;
     const uint4 wA = lds128(wo);
@@ -248,17 +254,12 @@ __device__ __forceinline__ void consume_g4(float (&acc)[2], uint32_t wbase, uint
     if (ch >= nc) s2 = make_uint2(0u, 0u);  // a chunk past the stage's data: whatever the slot holds must not count
     const uint2 z2 = lds64(zin + (uint32_t)it * 16u);
     const uint2 f2 = lds64(fex + (uint32_t)it * 16u);
+    const uint2 b = lds64(xa + (uint32_t)it * 128u);
     int d[4] = {(int)z2.x, (int)z2.y, (int)z2.x, (int)z2.y};
-    const uint32_t xo = (uint32_t)it * 128u;
-    uint2 b;
-    b = lds64(xa[0] + xo);
-    block_mma(d, wA.x, wA.y, b.x, b.y);
-    b = lds64(xa[1] + xo);
-    block_mma(d, wA.z, wA.w, b.x, b.y);
-    b = lds64(xa[2] + xo);
-    block_mma(d, wB.x, wB.y, b.x, b.y);
-    b = lds64(xa[3] + xo);
-    block_mma(d, wB.z, wB.w, b.x, b.y);
+    block_mma(d, wA.x, wA.y, b.x & k0, b.y & k0);
+    block_mma(d, wA.z, wA.w, b.x & k1, b.y & k1);
+    block_mma(d, wB.x, wB.y, b.x & k2, b.y & k2);
+    block_mma(d, wB.z, wB.w, b.x & k3, b.y & k3);
     const float2 se = __half22float2(*reinterpret_cast<const __half2*>(&s2.x));  // (row g, row g+8) of the even block
     const float2 so = __half22float2(*reinterpret_cast<const __half2*>(&s2.y));  // ... of the odd block
     const float fe = __uint_as_float(f2.x), fo = __uint_as_float(f2.y);

@@ -200,6 +200,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
   const uint32_t xbase = smem_u32(xreg);
   (void)my_tiles;
 
+#ifdef QENG_TRACE
+  unsigned long long* trace = reinterpret_cast<unsigned long long*>(p.status) + 1;  // 7 stamps behind the status word
+#define QENG_STAMP(i) do { if (blockIdx.x == 0 && tid == 0) trace[i] = globaltimer(); } while (0)
+#else
+#define QENG_STAMP(i) do { } while (0)
+#endif
+  QENG_STAMP(0);
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");  // the next kernel may start its own weight stream
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
@@ -258,7 +265,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
   // ===== consumers ====================================================================
   // The weights never change, so only the consumers wait for the kernel that produced the
   // activations (a no-op unless launched with programmatic stream serialization).
+  QENG_STAMP(1);
   asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  QENG_STAMP(2);
   // tags of this call's pushes and gathers (the step counter is only stable behind the wait above)
   const unsigned tp_step = p.tp_seq != nullptr ? *p.tp_seq : 0u;
   const unsigned tag_push = tp_step * p.tp_tags_per_step + p.push_tag_off + 1u;
@@ -401,6 +410,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
     }
   }
   consumer_sync();
+  QENG_STAMP(3);
 
   // ---- main loop: slices x this CTA's row tiles --------------------------------------------
   // The consumer warps form kTG independent groups that take the CTA's tiles in turn: while one
@@ -484,6 +494,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
         }
       }
       group_sync<kGW>(gi);
+      if (tcount == 0) QENG_STAMP(4);
       if (wi == ((tcount / kTG) % kGW)) {
         const float* rb = red + ((size_t)gi * 2 + buf) * kGW * red_stride;
         float* at = accsm + (size_t)tl * red_stride;
@@ -561,6 +572,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
       buf ^= 1;
     }
   }
+  QENG_STAMP(5);
   if (failed && lane == 0) atomicExch(p.status, 4);
 }
 
@@ -743,7 +755,9 @@ int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
   // so the split follows the number of tiles a CTA owns.
   const int grid = p.ntiles < ctx->sm_count ? p.ntiles : ctx->sm_count;
   const int per_cta = (p.ntiles + grid - 1) / grid;
-  int tg = per_cta >= 2 ? 4 : 1;
+  // (a tile worked on by 4 warps takes ~1.8 us, by 8 warps ~0.9: with only two tiles per CTA two groups of
+  // 8 warps finish sooner than two of four groups of 4)
+  int tg = per_cta >= 3 ? 4 : (per_cta == 2 ? 2 : 1);
   // a group needs a ring of its own at least as long as one row tile (a tile may span several
   // stages, and a group whose ring is shorter than its tile stalls the producer)
   const int spt = (f.slice_chunks + f.stage_chunks - 1) / f.stage_chunks;

@@ -107,6 +107,7 @@ _sig("qeng_kv_pool_data", _vp, _vp)
 _sig("qeng_kv_pool_pages", _i64, _vp)
 _sig("qeng_kv_append", _i32, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp)
 _sig("qeng_attn_decode", _i32, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _f32, _vp, _vp)
+_sig("qeng_attn_decode_ex", _i32, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _f32, _f32, _i32, _vp, _vp)
 _sig("qeng_attn_decode_noalloc", _i32, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _f32, _vp, _vp)
 _sig("qeng_decoder_create", _i32, _vp, C.POINTER(ModelCfg), C.POINTER(_vp))
 _sig("qeng_decoder_free", _i32, _vp, _vp)
@@ -312,15 +313,19 @@ class Context:
         self.check(_lib.qeng_kv_append(self.h, pool.h, _dev_ptr(k), _dev_ptr(v), _dev_ptr(table), table.shape[1],
                                        _dev_ptr(pos), pos.numel(), _cur_stream()))
 
-    def attn_decode(self, pool, q, table, lens, scale=None, out=None):
+    def attn_decode(self, pool, q, table, lens, scale=None, out=None, softcap=0.0, window=0):
         import torch
         b, hq, hd = q.shape
         assert q.dtype == torch.float16 and q.is_contiguous()
         if out is None:
             out = torch.empty((b, hq, hd), dtype=torch.float32, device=q.device)
         scale = float(hd) ** -0.5 if scale is None else scale
-        self.check(_lib.qeng_attn_decode(self.h, pool.h, _dev_ptr(q), _dev_ptr(table), table.shape[1], _dev_ptr(lens),
-                                         b, hq, scale, _dev_ptr(out), _cur_stream()))
+        if softcap or window:
+            self.check(_lib.qeng_attn_decode_ex(self.h, pool.h, _dev_ptr(q), _dev_ptr(table), table.shape[1], _dev_ptr(lens),
+                                                b, hq, scale, float(softcap), int(window), _dev_ptr(out), _cur_stream()))
+        else:
+            self.check(_lib.qeng_attn_decode(self.h, pool.h, _dev_ptr(q), _dev_ptr(table), table.shape[1], _dev_ptr(lens),
+                                             b, hq, scale, _dev_ptr(out), _cur_stream()))
         return out
 
     def attn_decode_noalloc(self, pool, q, table, lens, scale=None, out=None):

@@ -199,6 +199,16 @@ int32_t qeng_attn_decode(qeng_ctx* ctx, const qeng_kv_pool* pool, const uint16_t
                          const int32_t* page_table, int64_t max_pages, const int32_t* lens,
                          int64_t B, int64_t Hq, float scale, float* out, void* stream);
 
+/* The same with the two attention deltas of the Gemma family, which the reference lists among
+ * what stopped its own catalog models ("Gemma extensions absent (softcapping, sliding window)",
+ * decide/model-lifecycle.md:175-176): softcap > 0 replaces the logits q.k*scale by
+ * softcap * tanh(q.k*scale / softcap); window > 0 attends only the last `window` cached tokens of
+ * every sequence (pages wholly before the window are not read).  0 switches either off. */
+int32_t qeng_attn_decode_ex(qeng_ctx* ctx, const qeng_kv_pool* pool, const uint16_t* q_f16,
+                            const int32_t* page_table, int64_t max_pages, const int32_t* lens,
+                            int64_t B, int64_t Hq, float scale, float softcap, int32_t window,
+                            float* out, void* stream);
+
 /* Same result as qeng_attn_decode, for callers that cannot allocate device memory
  * while they run: hosts that give the engine a fixed memory budget at start-up and
  * forbid later growth, or token loops that must never enter the CUDA allocator.

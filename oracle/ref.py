@@ -182,19 +182,28 @@ def f16_round(x):
 # --------------------------------------------------------------------------
 # decode attention (GQA) over per-sequence K/V
 # --------------------------------------------------------------------------
-def attn_decode(q, ks, vs, scale=None):
-    """q [B,Hq,hd]; ks/vs: list of [len_b,Hkv,hd].  Returns [B,Hq,hd] float64."""
+def attn_decode(q, ks, vs, scale=None, softcap=0.0, window=0):
+    """q [B,Hq,hd]; ks/vs: list of [len_b,Hkv,hd].  Returns [B,Hq,hd] float64.
+    softcap > 0: logits = softcap * tanh(q.k * scale / softcap); window > 0: only the last `window`
+    cached tokens are attended (the two attention deltas of the Gemma family that the reference
+    lists as missing from its runtime, decide/model-lifecycle.md:175-176)."""
     B, Hq, hd = q.shape
     scale = 1.0 / np.sqrt(hd) if scale is None else scale
     out = np.zeros((B, Hq, hd), np.float64)
     for b in range(B):
         k = ks[b].astype(np.float64)
         v = vs[b].astype(np.float64)
+        if window > 0:
+            k, v = k[-window:], v[-window:]
+        if k.shape[0] == 0:
+            continue
         Hkv = k.shape[1]
         grp = Hq // Hkv
         for h in range(Hq):
             kh = k[:, h // grp]
             logit = (kh @ q[b, h].astype(np.float64)) * scale
+            if softcap > 0:
+                logit = softcap * np.tanh(logit / softcap)
             logit -= logit.max()
             p = np.exp(logit)
             p /= p.sum()

@@ -118,3 +118,46 @@ def test_kv_append_round_trip(ctx):
         assert np.array_equal(p[pid, :, 1, slot], v[b].astype(np.float16))
     assert np.count_nonzero(p) == B * Hkv * 2 * 128
     pool.free()
+
+
+@pytest.mark.parametrize("softcap,window", [(50.0, 0), (0.0, 40), (30.0, 100), (0.0, 16), (0.0, 1)])
+def test_softcap_and_sliding_window(ctx, softcap, window):
+    """The attention deltas of the Gemma family (qeng_attn_decode_ex): soft-capped logits and a sliding
+    window over the last tokens, ragged lengths around page and window edges, against the oracle."""
+    lens, q, ks, vs, pool_np, table = ref.config4(seed=60 + window, B=6, lo=1, hi=300)
+    lens[:3] = [window if window else 5, 17, max(window - 1, 1)]
+    # rebuild K/V for the changed lengths
+    rng = ref.rng_of(61 + window)
+    ks, vs, pool_np, table = ref.paged_kv(rng, lens, 8, 128, 16)
+    q = (q.astype(np.float32) * 3).astype(np.float16)  # larger logits, so that the cap bites
+    pool = ctx.kv_pool(pool_np.shape[0], pool_np.shape[1])
+    pool.tensor().copy_(_t(pool_np))
+    out = ctx.attn_decode(pool, _t(q), _t(table), _t(lens), softcap=softcap, window=window).cpu().numpy()
+    want = ref.attn_decode(q, ks, vs, softcap=softcap, window=window)
+    assert ref.err_inf(out, want) < 1e-4
+    if softcap or window:
+        assert ref.err_inf(ref.attn_decode(q, ks, vs), want) > 1e-3  # the switches matter on this input
+    ctx.device_status()
+    pool.free()
+
+
+def test_long_cache_on_the_fixed_split_path_with_a_window(ctx):
+    lens = np.array([4096, 3000, 513, 2049], np.int32)
+    rng = ref.rng_of(70)
+    q = rng.standard_normal((4, 32, 128), dtype=np.float32).astype(np.float16)
+    ks, vs, pool_np, table = ref.paged_kv(rng, lens, 8, 128, 16)
+    pool = ctx.kv_pool(pool_np.shape[0], pool_np.shape[1])
+    pool.tensor().copy_(_t(pool_np))
+    from cyb_b200 import qeng
+    c2 = qeng.Context(0, no_attn_cluster=1)  # force the fixed splits + last-arriver merge
+    pool2 = c2.kv_pool(pool_np.shape[0], pool_np.shape[1])
+    pool2.tensor().copy_(_t(pool_np))
+    for window in (0, 1000):
+        want = ref.attn_decode(q, ks, vs, window=window)
+        for c, pl in ((ctx, pool), (c2, pool2)):
+            out = c.attn_decode(pl, _t(q), _t(table), _t(lens), window=window).cpu().numpy()
+            assert ref.err_inf(out, want) < 1e-4, window
+            c.device_status()
+    pool.free()
+    pool2.free()
+    c2.close()
