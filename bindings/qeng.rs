@@ -82,6 +82,8 @@ pub struct qeng_model_cfg {
     pub max_seq: i32,
     pub tp_rank: i32,
     pub tp_world: i32,
+    pub attn_softcap: f32,
+    pub sliding_window: i32,
 }
 
 #[link(name = "qeng")]
@@ -124,6 +126,7 @@ extern "C" {
     pub fn qeng_kv_pool_pages(pool: *const qeng_kv_pool) -> i64;
     pub fn qeng_kv_append(ctx: *mut qeng_ctx, pool: *mut qeng_kv_pool, k: *const f32, v: *const f32, page_table: *const i32, max_pages: i64, pos: *const i32, B: i64, stream: *mut c_void) -> i32;
     pub fn qeng_attn_decode(ctx: *mut qeng_ctx, pool: *const qeng_kv_pool, q_f16: *const u16, page_table: *const i32, max_pages: i64, lens: *const i32, B: i64, Hq: i64, scale: f32, out: *mut f32, stream: *mut c_void) -> i32;
+    pub fn qeng_attn_decode_ex(ctx: *mut qeng_ctx, pool: *const qeng_kv_pool, q_f16: *const u16, page_table: *const i32, max_pages: i64, lens: *const i32, B: i64, Hq: i64, scale: f32, softcap: f32, window: i32, out: *mut f32, stream: *mut c_void) -> i32;
     pub fn qeng_attn_decode_noalloc(ctx: *mut qeng_ctx, pool: *const qeng_kv_pool, q_f16: *const u16, page_table: *const i32, max_pages: i64, lens: *const i32, B: i64, Hq: i64, scale: f32, out: *mut f32, stream: *mut c_void) -> i32;
     pub fn qeng_decoder_create(ctx: *mut qeng_ctx, cfg: *const qeng_model_cfg, out: *mut *mut qeng_decoder) -> i32;
     pub fn qeng_decoder_free(ctx: *mut qeng_ctx, dec: *mut qeng_decoder) -> i32;

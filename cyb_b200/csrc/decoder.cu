@@ -339,8 +339,9 @@ int32_t run_layer_prefill(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, c
   d->view.pages = d->pages; d->view.kv_heads = d->Hkv; d->view.hd = kHD; d->view.data = pool;
   for (int64_t r0 = 0; r0 < rows; r0 += kAttnRowsPerCall) {
     const int64_t nr = rows - r0 < kAttnRowsPerCall ? rows - r0 : kAttnRowsPerCall;
-    rc = qeng_attn_decode(ctx, &d->view, reinterpret_cast<const uint16_t*>(d->q16 + r0 * nq), table + r0 * d->max_pages,
-                          d->max_pages, d->lens + r0, nr, d->Hq, 1.0f / sqrtf((float)kHD), d->att + r0 * nq, st);
+    rc = qeng_attn_decode_ex(ctx, &d->view, reinterpret_cast<const uint16_t*>(d->q16 + r0 * nq), table + r0 * d->max_pages,
+                             d->max_pages, d->lens + r0, nr, d->Hq, 1.0f / sqrtf((float)kHD), d->cfg.attn_softcap,
+                             d->cfg.sliding_window, d->att + r0 * nq, st);
     if (rc != QENG_OK) return rc;
   }
   const int64_t n = rows * dm;
@@ -404,8 +405,8 @@ int32_t run_layer(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, const int
   }
   if (f.tp_gather_kind >= 0) x = other(x);  // the gathered rows are the residual stream from here on
   d->view.pages = d->pages; d->view.kv_heads = d->Hkv; d->view.hd = kHD; d->view.data = pool;
-  rc = qeng_attn_decode(ctx, &d->view, reinterpret_cast<const uint16_t*>(d->q16), table, d->max_pages, d->lens, rows,
-                        d->Hq, 1.0f / sqrtf((float)kHD), d->att, st);
+  rc = qeng_attn_decode_ex(ctx, &d->view, reinterpret_cast<const uint16_t*>(d->q16), table, d->max_pages, d->lens, rows,
+                           d->Hq, 1.0f / sqrtf((float)kHD), d->cfg.attn_softcap, d->cfg.sliding_window, d->att, st);
   if (rc != QENG_OK) return rc;
   d->launches += 1;
   qeng_gemm_fuse fg;
@@ -503,7 +504,7 @@ int32_t tail(qeng_ctx* ctx, qeng_decoder* d, const float* x_last, int B, bool fi
 // rank (the sharded step still runs operator by operator), unusual widths.
 int32_t plan_step(qeng_ctx* ctx, qeng_decoder* d) {
   d->step_planned = true;
-  if (d->cfg.tp_world != 1) return QENG_OK;
+  if (d->cfg.tp_world != 1 || d->cfg.attn_softcap > 0.f || d->cfg.sliding_window > 0) return QENG_OK;
   qeng_step_desc desc;
   for (int l = 0; l < d->cfg.layers; ++l) {
     Layer& L = d->layers[l];
@@ -570,6 +571,7 @@ int32_t qeng_decoder_create(qeng_ctx* ctx, const qeng_model_cfg* cfg, qeng_decod
   if (cfg->kv_heads % t != 0 || cfg->ffn % (16 * t) != 0 || cfg->d_model % 32 != 0 || (cfg->ffn / t) % 32 != 0 ||
       (cfg->heads * kHD / t) % 32 != 0)
     return qeng_fail(ctx, QENG_ERR_SHAPE, "decoder_create: shapes do not shard evenly over %d ranks", t);
+  if (cfg->attn_softcap < 0.f || cfg->sliding_window < 0) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_create: attn_softcap and sliding_window must not be negative");
   if (cfg->max_batch < 1 || cfg->max_batch > 16 || cfg->max_seq < 1)
     return qeng_fail(ctx, QENG_ERR_SHAPE, "decoder_create: max_batch must be 1..16 and max_seq positive");
   if (t > 1 && (ctx->tp_world != t || ctx->tp_rank != cfg->tp_rank))

@@ -237,6 +237,8 @@ typedef struct qeng_model_cfg {
   int32_t max_batch; /* sequences decoded together */
   int32_t max_seq;   /* tokens per sequence the KV pool is sized for */
   int32_t tp_rank, tp_world; /* tensor-parallel position of this context */
+  float attn_softcap;        /* > 0: attention logits are soft-capped, softcap * tanh(logit / softcap) */
+  int32_t sliding_window;    /* > 0: every layer attends only the last `sliding_window` tokens */
 } qeng_model_cfg;
 
 /* matrices of one layer, in the order of the decode loop */

@@ -251,10 +251,11 @@ def config4(seed=4, B=16, Hq=32, Hkv=8, hd=128, lo=512, hi=4096, page=16):
 # --------------------------------------------------------------------------
 class DecoderConfig:
     def __init__(self, layers=32, d=4096, ffn=11008, heads=32, kv_heads=8, hd=128,
-                 vocab=32000, eps=1e-5, rope_base=10000.0):
+                 vocab=32000, eps=1e-5, rope_base=10000.0, attn_softcap=0.0, sliding_window=0):
         self.layers, self.d, self.ffn = layers, d, ffn
         self.heads, self.kv_heads, self.hd = heads, kv_heads, hd
         self.vocab, self.eps, self.rope_base = vocab, eps, rope_base
+        self.attn_softcap, self.sliding_window = attn_softcap, sliding_window
 
     @property
     def qkv_rows(self):
@@ -317,7 +318,8 @@ class Decoder:
             self.v[l][b] = np.concatenate([self.v[l][b], vr[b]], 0)
             for t in range(T):
                 n = base + t + 1
-                att[b, t] = attn_decode(qr[b, t][None], [self.k[l][b][:n]], [self.v[l][b][:n]])[0]
+                att[b, t] = attn_decode(qr[b, t][None], [self.k[l][b][:n]], [self.v[l][b][:n]],
+                                        softcap=cfg.attn_softcap, window=cfg.sliding_window)[0]
         h = x + self.mm(att.reshape(B * T, -1), *lw["wo"]).reshape(B, T, d)
         n2 = rmsnorm(h, lw["norm2"], cfg.eps).reshape(B * T, d)
         act = swiglu(self.mm(n2, *lw["wgate"]), self.mm(n2, *lw["wup"]))
