@@ -64,6 +64,7 @@ pub struct qeng_options {
     pub attn_ctas_per_sm: i32,
     pub stream_groups: i32,
     pub step_kernel: i32,
+    pub stream_stage_chunks: i32,
 }
 
 #[repr(C)]

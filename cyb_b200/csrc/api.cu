@@ -15,6 +15,12 @@ int32_t qeng_fail(qeng_ctx* ctx, int32_t code, const char* fmt, ...) {
   return code;
 }
 
+#ifdef QENG_TRACE
+static const size_t kStatusBytes = 256 + 8 * (8 + 30000 * 8);
+#else
+static const size_t kStatusBytes = 256;
+#endif
+
 extern "C" {
 
 int32_t qeng_version(void) { return 100; }
@@ -31,6 +37,7 @@ int32_t qeng_create_opts(int32_t device, const qeng_options* opts, qeng_ctx** ou
   }
   if (o.attn_ctas_per_sm < 0 || o.attn_ctas_per_sm > 64) return QENG_ERR_ARG;
   if (o.stream_groups != 0 && o.stream_groups != 1 && o.stream_groups != 2 && o.stream_groups != 4) return QENG_ERR_ARG;
+  if (o.stream_stage_chunks != 0 && (o.stream_stage_chunks < 4 || o.stream_stage_chunks > 64)) return QENG_ERR_ARG;
   int count = 0;
   if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) return QENG_ERR_CUDA;  // no CPU fallback
   if (device < 0 || device >= count) return QENG_ERR_ARG;
@@ -53,7 +60,8 @@ int32_t qeng_create_opts(int32_t device, const qeng_options* opts, qeng_ctx** ou
   ctx->step_kernel = o.step_kernel != 0;
   ctx->attn_ctas_per_sm = o.attn_ctas_per_sm > 0 ? o.attn_ctas_per_sm : 8;
   ctx->stream_groups = o.stream_groups;
-  if (cudaMalloc(&ctx->status, 64) != cudaSuccess || cudaMemset(ctx->status, 0, 64) != cudaSuccess) {
+  ctx->stream_stage_chunks = o.stream_stage_chunks & ~1;  // a two-chunk work item never straddles stages
+  if (cudaMalloc(&ctx->status, kStatusBytes) != cudaSuccess || cudaMemset(ctx->status, 0, kStatusBytes) != cudaSuccess) {
     delete ctx;
     return QENG_ERR_CUDA;
   }
@@ -101,10 +109,24 @@ int32_t qeng_device_status(qeng_ctx* ctx) {
 int32_t qeng_sm_count(const qeng_ctx* ctx) { return ctx ? ctx->sm_count : 0; }
 
 #ifdef QENG_TRACE
-// tuning builds only: the 64 bytes behind the status pointer (status word + 7 timestamps)
-int32_t qeng_debug_status_words(qeng_ctx* ctx, unsigned long long* out8) {
+// tuning builds only: the 256 bytes behind the status pointer (status word, timestamps, cycle counters);
+// the counters are cleared after the read
+int32_t qeng_debug_status_words(qeng_ctx* ctx, unsigned long long* out32) {
   cudaDeviceSynchronize();
-  return cudaMemcpy(out8, ctx->status, 64, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -4;
+  if (cudaMemcpy(out32, ctx->status, 256, cudaMemcpyDeviceToHost) != cudaSuccess) return -4;
+  return cudaMemset(reinterpret_cast<char*>(ctx->status) + 64, 0, 192) == cudaSuccess ? 0 : -4;
+}
+// the launch log: records of 8 u64 (kind, stamps); cleared after the read
+int32_t qeng_debug_trace(qeng_ctx* ctx, unsigned long long* out, int32_t max_records, int32_t* n) {
+  cudaDeviceSynchronize();
+  unsigned long long cnt = 0;
+  char* base = reinterpret_cast<char*>(ctx->status) + 256;
+  if (cudaMemcpy(&cnt, base, 8, cudaMemcpyDeviceToHost) != cudaSuccess) return -4;
+  if (cnt > 30000) cnt = 30000;
+  if (cnt > (unsigned long long)max_records) cnt = (unsigned long long)max_records;
+  if (cnt && cudaMemcpy(out, base + 64, cnt * 64, cudaMemcpyDeviceToHost) != cudaSuccess) return -4;
+  *n = (int32_t)cnt;
+  return cudaMemset(base, 0, 64) == cudaSuccess ? 0 : -4;
 }
 #endif
 

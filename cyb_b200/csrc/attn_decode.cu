@@ -424,7 +424,14 @@ __global__ void __launch_bounds__(kAT) attn_decode_kernel(const AttnParams p) { 
 
 // launched with a cluster dimension of (p.S, 1, 1) = (gridDim.x, 1, 1)
 __global__ void __launch_bounds__(kAT) attn_decode_cluster_kernel(const AttnParams p) {
+#ifdef QENG_TRACE
+  unsigned long long* rec = nullptr;
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) rec = qeng_trace_open(p.status, 2);
+#endif
   attn_decode_body<true>(p);
+#ifdef QENG_TRACE
+  if (rec) rec[4] = qeng_trace_now();
+#endif
 }
 
 __global__ void __launch_bounds__(kHD) attn_combine_kernel(const AttnParams p) {

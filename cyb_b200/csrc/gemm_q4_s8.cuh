@@ -29,13 +29,23 @@
 #define QENG_G4_UNROLL 2
 #endif
 
+#ifndef QENG_DIAG
+#define QENG_DIAG 0
+#endif
+#ifndef QENG_SPLIT_ACC
+#define QENG_SPLIT_ACC 0
+#endif
+#ifndef QENG_L3_UNROLL
+#define QENG_L3_UNROLL 2
+#endif
 namespace q4s8 {
+constexpr int kL3Unroll = QENG_L3_UNROLL;
 constexpr int kG4Unroll = QENG_G4_UNROLL;  // items of the one-row loop in flight per warp
 
 constexpr int kCW = 16;               // consumer warps
 constexpr int kCT = kCW * 32;         // consumer threads
 constexpr int kThreads = kCT + 32;    // + producer warp
-constexpr int kMaxStages = 24;
+constexpr int kMaxStages = 48;
 constexpr uint32_t kBias = 0x4B400000u;   // float 12582912: bits kBias + d read as a float are 12582912 + d for |d| < 2^22
 constexpr float kBiasF = 12582912.0f;
 
@@ -256,10 +266,20 @@ __device__ __forceinline__ void consume_g4(float (&acc)[2], uint32_t wbase, uint
     const uint2 f2 = lds64(fex + (uint32_t)it * 16u);
     const uint2 b = lds64(xa + (uint32_t)it * 128u);
     int d[4] = {(int)z2.x, (int)z2.y, (int)z2.x, (int)z2.y};
+#if QENG_SPLIT_ACC
+    // blocks 0 and 2 feed the even columns, 1 and 3 the odd ones: two independent chains of two
+    int e[4] = {(int)z2.x, (int)z2.y, (int)z2.x, (int)z2.y};
+    block_mma(d, wA.x, wA.y, b.x & k0, b.y & k0);
+    block_mma(e, wA.z, wA.w, b.x & k1, b.y & k1);
+    block_mma(d, wB.x, wB.y, b.x & k2, b.y & k2);
+    block_mma(e, wB.z, wB.w, b.x & k3, b.y & k3);
+    d[1] = e[1]; d[3] = e[3];
+#else
     block_mma(d, wA.x, wA.y, b.x & k0, b.y & k0);
     block_mma(d, wA.z, wA.w, b.x & k1, b.y & k1);
     block_mma(d, wB.x, wB.y, b.x & k2, b.y & k2);
     block_mma(d, wB.z, wB.w, b.x & k3, b.y & k3);
+#endif
     const float2 se = __half22float2(*reinterpret_cast<const __half2*>(&s2.x));  // (row g, row g+8) of the even block
     const float2 so = __half22float2(*reinterpret_cast<const __half2*>(&s2.y));  // ... of the odd block
     const float fe = __uint_as_float(f2.x), fo = __uint_as_float(f2.y);
@@ -286,19 +306,45 @@ __device__ __forceinline__ void consume_m1l3(float (&acc)[2], uint32_t wbase, ui
   const uint32_t zin = xbase + L.zin + (uint32_t)limb * L.zs + (uint32_t)blk0 * 4u;
   const uint32_t fex = xbase + L.fex + (uint32_t)limb * L.zs + (uint32_t)blk0 * 4u;
   const float live = t < 3 ? 1.f : 0.f;
-#pragma unroll 2
+#pragma unroll kL3Unroll
   for (int it = wi; it < nc; it += NW) {
     const uint4 w = lds128(wbase + (uint32_t)it * 512u + (uint32_t)lane * 16u);
+#if QENG_DIAG & 8
+    const uint2 s2 = make_uint2(0x3c003c00u + it, 0x3c003c00u), z2 = make_uint2(kBias, kBias), f2 = make_uint2(0x3f800000u, 0x3f800000u);
+#else
     const uint2 s2 = lds64(sbase + (uint32_t)it * 64u + (uint32_t)g * 8u);
     const uint2 z2 = lds64(zin + (uint32_t)it * 8u);
     const uint2 f2 = lds64(fex + (uint32_t)it * 8u);
+#endif
     int d[4] = {(int)z2.x, (int)z2.y, (int)z2.x, (int)z2.y};
     const uint32_t xo = (uint32_t)it * 64u;
-    uint2 b;
+    uint2 b, b2;
+#if QENG_DIAG & 16
+    b = make_uint2(0x01020304u + it, 0x01020304u); b2 = b;
+#else
     b = lds64(xa[0] + xo);
+    b2 = lds64(xa[1] + xo);
+#endif
+#if QENG_DIAG & 2
+    imma(d, w.x, w.y, w.x, w.y, b.x, b.y);
+    imma(d, w.z, w.w, w.z, w.w, b2.x, b2.y);
+#elif QENG_DIAG & 4
+    d[0] ^= (w.x & 0x0f0f0f0fu) + b.x; d[1] ^= (w.y & 0x0f0f0f0fu) + b.y; d[2] ^= ((w.x >> 4) & 0x0f0f0f0fu) + b2.x; d[3] ^= ((w.y >> 4) & 0x0f0f0f0fu) + b2.y;
+    d[0] ^= (w.z & 0x0f0f0f0fu) + b.x; d[1] ^= (w.w & 0x0f0f0f0fu) + b.y; d[2] ^= ((w.z >> 4) & 0x0f0f0f0fu) + b2.x; d[3] ^= ((w.w >> 4) & 0x0f0f0f0fu) + b2.y;
+#elif QENG_SPLIT_ACC
+    // the two blocks feed different columns: two accumulators make the MMAs independent
+    int e[4] = {(int)z2.x, (int)z2.y, (int)z2.x, (int)z2.y};
     block_mma(d, w.x, w.y, b.x, b.y);
-    b = lds64(xa[1] + xo);
-    block_mma(d, w.z, w.w, b.x, b.y);
+    block_mma(e, w.z, w.w, b2.x, b2.y);
+    d[1] = e[1]; d[3] = e[3];
+#else
+    block_mma(d, w.x, w.y, b.x, b.y);
+    block_mma(d, w.z, w.w, b2.x, b2.y);
+#endif
+#if QENG_DIAG & 1
+    acc[0] += __int_as_float(d[0] ^ d[1] ^ (int)s2.x ^ (int)f2.x);
+    acc[1] += __int_as_float(d[2] ^ d[3] ^ (int)s2.y ^ (int)f2.y);
+#else
     const float2 se = __half22float2(*reinterpret_cast<const __half2*>(&s2.x));
     const float2 so = __half22float2(*reinterpret_cast<const __half2*>(&s2.y));
     const float fe = __uint_as_float(f2.x) * live, fo = __uint_as_float(f2.y) * live;
@@ -306,6 +352,7 @@ __device__ __forceinline__ void consume_m1l3(float (&acc)[2], uint32_t wbase, ui
     acc[0] = fmaf(so.x * fo, unbias(d[1]), acc[0]);
     acc[1] = fmaf(se.y * fe, unbias(d[2]), acc[1]);
     acc[1] = fmaf(so.y * fo, unbias(d[3]), acc[1]);
+#endif
   }
 }
 

@@ -1,12 +1,12 @@
 // Streaming decode GEMV/GEMM over 4-bit block weights: the bandwidth kernel.
 //
-// One persistent CTA per SM: a producer warp and 16 consumer warps around a
-// ring of shared-memory stages.  The producer walks this CTA's row tiles
-// (16 rows x K, contiguous in the packed layout) and copies them stage by
-// stage (up to 64 chunks: 32 KB of nibbles + 4 KB of scales) with bulk
-// asynchronous copies (cp.async.bulk, completion counted on an mbarrier), so
-// ~170 KB per SM are in flight without holding registers and independent of
-// what the consumers are doing.  Consumers take the chunks of a stage
+// One persistent CTA per SM: 16 consumer warps in up to four tile groups, each
+// group with a producer warp and a ring of shared-memory stages of its own.  A
+// producer walks its group's row tiles (16 rows x K, contiguous in the packed
+// layout) and copies them stage by stage (16 chunks: 8 KB of nibbles + 1 KB of
+// scales) with bulk asynchronous copies (cp.async.bulk, completion counted on
+// an mbarrier), so ~200 KB per SM are in flight without holding registers and
+// independent of what the consumers are doing.  Consumers take the chunks of a stage
 // round-robin, read them with conflict-free 128-bit shared loads, unpack in
 // registers and contract on the tensor pipe with integer MMAs against the
 // activations quantised to two signed bytes per value (gemm_q4_s8.cuh has the
@@ -26,6 +26,8 @@
 namespace {
 using namespace q4s8;
 
+constexpr int kStageChunks = 64;  // 64-wide K chunks per ring stage (36 KB: a whole row tile of K = 4096)
+constexpr int kDeferTiles = 16;   // tiles whose partial sums a CTA parks before it meets to reduce them
 constexpr int kGroups = 3;  // groups of 8 k one consumer thread stages in the single-slice mode: K <= 8 * kGroups * kCT
 
 struct StreamParams {
@@ -171,8 +173,13 @@ __device__ __forceinline__ void group_sync(int gi) { asm volatile("bar.sync %0, 
 //   kMN  : NT tiles of four rows in two limbs, one block per fragment
 enum { kM1L3 = 0, kM1L2 = 1, kM2L2 = 2, kMN = 3 };
 template <int MODE, int NT, int kTG>
-__global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const StreamParams p) {
-  constexpr int kGW = kCW / kTG;        // warps per tile group
+__global__ void __launch_bounds__(kCT + 32 * (kTG == 0 ? 1 : kTG), 1) gemv_q4_stream_kernel(const StreamParams p) {
+  // kTG = 0: all 16 warps work on every tile and the per-tile reduction is deferred: each warp parks its
+  // partial sums of a tile in shared memory and moves on; the CTA meets once at the end (or every
+  // kDeferTiles tiles), where the warps sum the partials and run the epilogues of the tiles in parallel
+  constexpr bool kDefer = kTG == 0;
+  constexpr int kTGe = kDefer ? 1 : kTG;  // tile groups (rings, producer warps)
+  constexpr int kGW = kCW / kTGe;         // warps per tile group
   constexpr int kMR = MODE == kMN ? 4 * NT : (MODE == kM2L2 ? 2 : 1);  // activation rows the fragment layout holds
   constexpr int kLimbs = MODE == kM1L3 ? 3 : 2;
   constexpr bool kZeroed = MODE != kMN;
@@ -186,9 +193,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
   unsigned char* ring = smem;
   unsigned char* xreg = smem + (((size_t)NS * stage_bytes + 127) & ~(size_t)127);
   const bool two_areas = MODE == kMN && p.ximage != nullptr;
-  float* red = reinterpret_cast<float*>(xreg + (two_areas ? 2u * ((L.bytes + 127u) & ~127u) : L.bytes));  // [kTG][2][kGW][kMR * 16]
+  float* red = reinterpret_cast<float*>(xreg + (two_areas ? 2u * ((L.bytes + 127u) & ~127u) : L.bytes));  // [kTG][2][kGW][kMR * 16], deferred: [kDeferTiles][kCW][kMR * 16]
   constexpr int red_stride = kMR * 16;
-  float* accsm = red + kTG * 2 * kGW * red_stride;                 // [tiles of this CTA][kMR * 16] (several slices only)
+  float* accsm = red + (kDefer ? kDeferTiles * kCW : kTGe * 2 * kGW) * red_stride;                 // [tiles of this CTA][kMR * 16] (several slices only)
   const int my_tiles = p.ntiles > (int)blockIdx.x ? (p.ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
   const int max_tiles = (p.ntiles + (int)gridDim.x - 1) / (int)gridDim.x;
   uint64_t* full = reinterpret_cast<uint64_t*>(accsm + (p.nslices > 1 ? (size_t)max_tiles * red_stride : 0));
@@ -203,10 +210,26 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
 #ifdef QENG_TRACE
   unsigned long long* trace = reinterpret_cast<unsigned long long*>(p.status) + 1;  // 7 stamps behind the status word
 #define QENG_STAMP(i) do { if (blockIdx.x == 0 && tid == 0) trace[i] = globaltimer(); } while (0)
+  long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // cycle counters kept in registers, written once at the end
+#define QENG_TICK(v) const long long v = clock64()
+#define QENG_TOCK(v, i, cond) do { tacc[(i) - 8] += clock64() - v; } while (0)
+#define QENG_COUNT(i, cond) do { tacc[(i) - 8] += 1; } while (0)
+#define QENG_FLUSH(i, cond) do { if (blockIdx.x == 0 && lane == 0 && (cond)) trace[i] += (unsigned long long)tacc[(i) - 8]; } while (0)
 #else
 #define QENG_STAMP(i) do { } while (0)
+#define QENG_TICK(v) do { } while (0)
+#define QENG_TOCK(v, i, cond) do { } while (0)
+#define QENG_COUNT(i, cond) do { } while (0)
+#define QENG_FLUSH(i, cond) do { } while (0)
 #endif
   QENG_STAMP(0);
+#ifdef QENG_TRACE
+  unsigned long long* rec = nullptr;
+  if (blockIdx.x == 0 && tid == 0) { rec = qeng_trace_open(p.status, 1000000ull * (unsigned)MODE + 1000ull * (unsigned)p.M + (unsigned)(p.ntiles / 16) + ((unsigned long long)p.nchunks << 32)); }
+#define QENG_REC(i) do { if (rec) rec[i] = qeng_trace_now(); } while (0)
+#else
+#define QENG_REC(i) do { } while (0)
+#endif
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");  // the next kernel may start its own weight stream
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
@@ -219,23 +242,26 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
   }
   __syncthreads();
 
-  const int NSg = NS / kTG;  // ring slots per tile group; group gi owns slots [gi * NSg, (gi + 1) * NSg)
+  const int NSg = NS / kTGe;  // ring slots per tile group; group gi owns slots [gi * NSg, (gi + 1) * NSg)
 
-  if (warp == kCW) {
-    // ===== producer: stream this CTA's row tiles through the ring, slice by slice ==========
+  if (warp >= kCW) {
+    // ===== producers: stream this CTA's row tiles through the ring, slice by slice ==========
+    // One producer warp per tile group (a wait on a group's barrier suspends only that group's
+    // feeder): each ring fills as its own consumers free slots, however far the groups drift apart.
+    const int pg = warp - kCW;
     if (lane == 0) {
       bool failed = false;
-      int tcount = 0;
-      int use[4] = {0, 0, 0, 0};  // stage uses per tile group
+      int tcount = 0, use = 0;
       for (int sl = 0; sl < p.nslices; ++sl) {
         const int cs0 = sl * p.slice_chunks, cs1 = min(p.nchunks, cs0 + p.slice_chunks);
         for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++tcount) {
-          const int grp = tcount % kTG;
-          for (int c0 = cs0; c0 < cs1; c0 += p.stage_chunks) {
-            const int u = use[grp]++;
-            const int s = grp * NSg + u % NSg;
-            const uint32_t ph = (uint32_t)(u / NSg) & 1u;
+          if (tcount % kTGe != pg) continue;
+          for (int c0 = cs0; c0 < cs1; c0 += p.stage_chunks, ++use) {
+            const int s = pg * NSg + use % NSg;
+            const uint32_t ph = (uint32_t)(use / NSg) & 1u;
+            QENG_TICK(tp0);
             if (!failed && !mbar_wait(smem_u32(empty + s), ph ^ 1u)) failed = true;
+            QENG_TOCK(tp0, 12, pg == 0);
             const int nc = min(p.stage_chunks, cs1 - c0);
             const uint32_t bar = smem_u32(full + s);
             const uint32_t dst = smem_u32(ring) + (uint32_t)s * stage_bytes;
@@ -247,11 +273,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
         }
       }
       if (failed) atomicExch(p.status, 4);
+      QENG_FLUSH(12, pg == 0);
     }
     __syncwarp();
     // Own loads are all in flight: ask L2 for this CTA's share of the next matrix, so that HBM
     // does not idle while the consumers drain the ring and the next kernel starts up.
-    if (p.pf_qs != nullptr) {
+    if (pg == 0 && p.pf_qs != nullptr) {
       const uint32_t qb = (uint32_t)p.pf_nchunks * 512u, sb = (uint32_t)p.pf_nchunks * 64u;
       for (int tile = blockIdx.x + gridDim.x * lane; tile < p.pf_ntiles; tile += gridDim.x * 32) {
         const char* q = reinterpret_cast<const char*>(p.pf_qs) + (size_t)tile * qb;
@@ -266,19 +293,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
   // The weights never change, so only the consumers wait for the kernel that produced the
   // activations (a no-op unless launched with programmatic stream serialization).
   QENG_STAMP(1);
+  const XLayout& Lz = L;
+  // Work that does not depend on the kernel before: the zero region other blocks' lanes read (several
+  // blocks per fragment), and the norm gains of this thread's groups, requested into L1 so that the
+  // loads behind the reduction below find them there.
+  if (kZeroed)
+    for (uint32_t o = (uint32_t)tid * 16u; o < x_zero_bytes(Lz); o += kCT * 16u)
+      asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(xbase + Lz.zero + o), "r"(0u) : "memory");
+  if (p.gamma != nullptr && p.ximage == nullptr)
+    for (int k0 = tid * 8; k0 < p.K; k0 += kCT * 8) asm volatile("prefetch.global.L1 [%0];\n" ::"l"(p.gamma + k0));
   asm volatile("griddepcontrol.wait;\n" ::: "memory");
   QENG_STAMP(2);
+  QENG_REC(2);
   // tags of this call's pushes and gathers (the step counter is only stable behind the wait above)
   const unsigned tp_step = p.tp_seq != nullptr ? *p.tp_seq : 0u;
   const unsigned tag_push = tp_step * p.tp_tags_per_step + p.push_tag_off + 1u;
   const unsigned tag_gather = tp_step * p.tp_tags_per_step + p.gather_tag_off + 1u;
   Waits TW;
   (void)tag_gather;
-  // the zero region other blocks' lanes read (several blocks per fragment)
-  if (kZeroed)
-    for (uint32_t o = (uint32_t)tid * 16u; o < x_zero_bytes(L); o += kCT * 16u)
-      asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(xbase + L.zero + o), "r"(0u) : "memory");
-
   const bool vec_ok = p.x_dtype == QENG_F32 && ((reinterpret_cast<uintptr_t>(p.x) | (uintptr_t)(p.ldx * 4)) & 15) == 0 &&
                       (p.gamma == nullptr || (reinterpret_cast<uintptr_t>(p.gamma) & 15) == 0) && (p.K & 7) == 0;
   // eight consecutive activations of row m starting at k0 (zero beyond K)
@@ -411,6 +443,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
   }
   consumer_sync();
   QENG_STAMP(3);
+  QENG_REC(3);
 
   // ---- main loop: slices x this CTA's row tiles --------------------------------------------
   // The consumer warps form kTG independent groups that take the CTA's tiles in turn: while one
@@ -420,6 +453,134 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
   const int gi = warp / kGW, wi = warp % kGW;
   bool failed = false;
   int tcount = 0, buf = 0, use = 0;
+
+  // the fused epilogue of one row tile, run by one warp; total(a, r) = the finished sum for activation
+  // row a and weight row r of the tile
+  auto finish = [&](int tile, auto total) {
+    if (p.epilogue == QENG_EPI_QKV) {
+      const qeng_qkv_epi& E = p.qkv;
+      const int head = tile >> 3, i = ((tile & 7) << 3);
+      for (int e = lane; e < p.M * 8; e += 32) {
+        const int a = e >> 3, r = e & 7;
+        float lo = total(a, r), hi = total(a, r + 8);  // dims i+r and i+r+64 of this head
+        const int ps = E.pos[a];
+        if (ps < 0 || ps >= E.max_seq || (ps >> 4) >= E.max_pages) {
+          atomicExch(p.status, 2);
+          continue;
+        }
+        const int d = i + r;
+        if (head < E.Hq + E.Hkv) {
+          const float c = E.cs[(size_t)ps * 128 + d], sn = E.cs[(size_t)ps * 128 + 64 + d];
+          const float a0 = lo * c - hi * sn, a1 = hi * c + lo * sn;
+          lo = a0;
+          hi = a1;
+        }
+        if (head < E.Hq) {
+          __half* dst = E.q16 + ((size_t)a * E.Hq + head) * 128 + d;
+          dst[0] = __float2half_rn(lo);
+          dst[64] = __float2half_rn(hi);
+        } else {
+          const int pid = E.table[(size_t)a * E.max_pages + (ps >> 4)];
+          if ((unsigned)pid >= (unsigned)E.pages) {
+            atomicExch(p.status, 1);
+            continue;
+          }
+          const int kh = head - E.Hq;
+          const int isv = kh >= E.Hkv ? 1 : 0;
+          __half* dst = E.pool + (((size_t)pid * E.Hkv + (kh - isv * E.Hkv)) * 2 + isv) * (16 * 128) + (ps & 15) * 128 + d;
+          dst[0] = __float2half_rn(lo);
+          dst[64] = __float2half_rn(hi);
+        }
+      }
+    } else if (p.epilogue == QENG_EPI_SWIGLU) {
+      for (int e = lane; e < p.M * 8; e += 32) {
+        const int a = e >> 3, r = e & 7;
+        const float gate = total(a, r), up = total(a, r + 8);
+        p.y[(size_t)a * p.ldy + (size_t)tile * 8 + r] = gate / (1.0f + __expf(-gate)) * up;
+      }
+    } else if (p.push_world > 0) {
+      // this rank's part of the residual update, tagged, into every rank's inbox (own included)
+      for (int e = lane; e < p.M * 16; e += 32) {
+        const int a = e >> 4, r = e & 15;
+        const float v = total(a, r);
+        const size_t o = ((size_t)p.push_rank * kTpFuseRows + a) * kTpFuseDm + (size_t)tile * 16 + r;
+        for (int rr = 0; rr < p.push_world; ++rr) st_pair(p.push_inbox[(p.push_rank + rr) % p.push_world] + o, v, tag_push);
+      }
+    } else {
+      for (int e = lane; e < p.M * 16; e += 32) {
+        const int a = e >> 4, r = e & 15;
+        float v = total(a, r);
+        const size_t o = (size_t)a * p.ldy + (size_t)tile * 16 + r;
+        if (p.epilogue == QENG_EPI_ACCUM) v += p.y[o];
+        else if (p.epilogue == QENG_EPI_RESID) v += p.resid[o];
+        p.y[o] = v;
+      }
+    }
+  };
+  // this lane's partial accumulators of a tile -> `dst` ([row a][16]) (one or two activation rows)
+  auto park = [&](float* dst, float (&acc1)[2]) {
+    if (MODE == kM1L3 || MODE == kM1L2) {
+      acc1[0] += __shfl_xor_sync(0xffffffffu, acc1[0], 1);
+      acc1[1] += __shfl_xor_sync(0xffffffffu, acc1[1], 1);
+      acc1[0] += __shfl_xor_sync(0xffffffffu, acc1[0], 2);
+      acc1[1] += __shfl_xor_sync(0xffffffffu, acc1[1], 2);
+      if (t == 0) { dst[g] = acc1[0]; dst[g + 8] = acc1[1]; }
+    } else {
+      acc1[0] += __shfl_xor_sync(0xffffffffu, acc1[0], 1);
+      acc1[1] += __shfl_xor_sync(0xffffffffu, acc1[1], 1);
+      if ((t & 1) == 0) { dst[(t >> 1) * 16 + g] = acc1[0]; dst[(t >> 1) * 16 + g + 8] = acc1[1]; }
+    }
+  };
+
+  if constexpr (kDefer) {
+    // ---- one activation slice, up to two rows: no per-tile meeting -------------------------------
+    int tl = 0, rot = 0;
+    for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++tl) {
+      float acc1[2] = {0.f, 0.f};
+      for (int c0 = 0; c0 < p.nchunks; c0 += p.stage_chunks, ++use) {
+        const int s = use % NS;
+        const uint32_t ph = (uint32_t)(use / NS) & 1u;
+        QENG_TICK(tc0);
+        if (!failed && !mbar_wait(smem_u32(full + s), ph)) failed = true;
+        QENG_TOCK(tc0, 8, warp == 0);
+        QENG_TICK(tc1);
+        const int nc = min(p.stage_chunks, p.nchunks - c0);
+        const uint32_t wb = smem_u32(ring) + (uint32_t)s * stage_bytes;
+        const uint32_t sb = wb + (uint32_t)p.stage_chunks * 512u;
+        const int blk0 = c0 * 2;
+        // the warp that takes a stage's first item rotates, so that stages whose item count is not a
+        // multiple of 16 load the warps evenly over a tile
+        const int wr = (warp + kCW - rot) & (kCW - 1);
+        if (MODE == kM1L3) consume_m1l3<kCW>(acc1, wb, sb, nc, blk0, L, xbase, wr, lane);
+        else if (MODE == kM1L2) consume_g4<kCW>(acc1, wb, sb, nc, blk0, L, xbase, wr, lane);
+        else consume_g2<kCW>(acc1, wb, sb, nc, blk0, L, xbase, wr, lane);
+        rot = (rot + (MODE == kM1L2 ? (nc + 1) >> 1 : nc)) & (kCW - 1);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(empty + s));
+        QENG_TOCK(tc1, 9, warp == 0);
+        QENG_COUNT(11, warp == 0);
+      }
+      QENG_TICK(tc2);
+      const int slot = tl % kDeferTiles;
+      park(red + ((size_t)slot * kCW + warp) * red_stride, acc1);
+      const bool last_tile = tile + (int)gridDim.x >= p.ntiles;
+      if (slot == kDeferTiles - 1 || last_tile) {
+        consumer_sync();
+        if (tl < kDeferTiles) QENG_STAMP(4);
+        for (int j = warp; j <= slot; j += kCW) {
+          const float* rb = red + (size_t)j * kCW * red_stride;
+          finish(tile - (slot - j) * (int)gridDim.x, [&](int a, int r) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < kCW; ++w) v += rb[w * red_stride + a * 16 + r];
+            return v;
+          });
+        }
+        if (!last_tile) consumer_sync();  // the parking area is free again
+      }
+      QENG_TOCK(tc2, 10, warp == 0);
+    }
+  } else {
   for (int sl = 0; sl < p.nslices; ++sl) {
     const int cs0 = sl * p.slice_chunks, cs1 = min(p.nchunks, cs0 + p.slice_chunks);
     uint32_t xb = xbase;  // this slice's staging area
@@ -451,7 +612,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
     }
     int tl = 0;  // index of the tile among this CTA's tiles
     for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++tcount, ++tl) {
-      if ((tcount % kTG) != gi) continue;  // another group's tile
+      if ((tcount % kTGe) != gi) continue;  // another group's tile
       float acc1[2] = {0.f, 0.f};
       float accn[NT][2];
 #pragma unroll
@@ -459,7 +620,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
       for (int c0 = cs0; c0 < cs1; c0 += p.stage_chunks, ++use) {
         const int s = gi * NSg + use % NSg;
         const uint32_t ph = (uint32_t)(use / NSg) & 1u;
+        QENG_TICK(tc0);
         if (!failed && !mbar_wait(smem_u32(full + s), ph)) failed = true;
+        QENG_TOCK(tc0, 8, warp == 0);
+        QENG_TICK(tc1);
         const int nc = min(p.stage_chunks, cs1 - c0);
         const uint32_t wb = smem_u32(ring) + (uint32_t)s * stage_bytes;
         const uint32_t sb = wb + (uint32_t)p.stage_chunks * 512u;
@@ -470,22 +634,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
         else consume_g1<kGW, NT>(accn, wb, sb, nc, blk0, L, xb, p.cols, wi, lane);
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(empty + s));  // this warp is done with the stage
+        QENG_TOCK(tc1, 9, warp == 0);
+        QENG_COUNT(11, warp == 0);
       }
+      QENG_TICK(tc2);
 
       // ---- the partial accumulators of the group's warps meet in shared memory ------------------
       // red[group][buf][warp][row m][16]; the reader of buffer `buf` finishes before it arrives at
       // the next tile's barrier, and buffer `buf` is written again only after that barrier
       float* myred = red + (((size_t)gi * 2 + buf) * kGW + wi) * red_stride;
-      if (MODE == kM1L3 || MODE == kM1L2) {
-        acc1[0] += __shfl_xor_sync(0xffffffffu, acc1[0], 1);
-        acc1[1] += __shfl_xor_sync(0xffffffffu, acc1[1], 1);
-        acc1[0] += __shfl_xor_sync(0xffffffffu, acc1[0], 2);
-        acc1[1] += __shfl_xor_sync(0xffffffffu, acc1[1], 2);
-        if (t == 0) { myred[g] = acc1[0]; myred[g + 8] = acc1[1]; }
-      } else if (MODE == kM2L2) {
-        acc1[0] += __shfl_xor_sync(0xffffffffu, acc1[0], 1);
-        acc1[1] += __shfl_xor_sync(0xffffffffu, acc1[1], 1);
-        if ((t & 1) == 0) { myred[(t >> 1) * 16 + g] = acc1[0]; myred[(t >> 1) * 16 + g + 8] = acc1[1]; }
+      if (MODE != kMN) {
+        park(myred, acc1);
       } else {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
@@ -495,7 +654,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
       }
       group_sync<kGW>(gi);
       if (tcount == 0) QENG_STAMP(4);
-      if (wi == ((tcount / kTG) % kGW)) {
+      if (wi == ((tcount / kTGe) % kGW)) {
         const float* rb = red + ((size_t)gi * 2 + buf) * kGW * red_stride;
         float* at = accsm + (size_t)tl * red_stride;
         const bool first = sl == 0, last = sl + 1 == p.nslices;
@@ -509,70 +668,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_q4_stream_kernel(const Strea
         };
         if (!last) {
           for (int e = lane; e < p.M * 16; e += 32) at[e] = total(e >> 4, e & 15);
-        } else if (p.epilogue == QENG_EPI_QKV) {
-          const qeng_qkv_epi& E = p.qkv;
-          const int head = tile >> 3, i = ((tile & 7) << 3);
-          for (int e = lane; e < p.M * 8; e += 32) {
-            const int a = e >> 3, r = e & 7;
-            float lo = total(a, r), hi = total(a, r + 8);  // dims i+r and i+r+64 of this head
-            const int ps = E.pos[a];
-            if (ps < 0 || ps >= E.max_seq || (ps >> 4) >= E.max_pages) {
-              atomicExch(p.status, 2);
-              continue;
-            }
-            const int d = i + r;
-            if (head < E.Hq + E.Hkv) {
-              const float c = E.cs[(size_t)ps * 128 + d], sn = E.cs[(size_t)ps * 128 + 64 + d];
-              const float a0 = lo * c - hi * sn, a1 = hi * c + lo * sn;
-              lo = a0;
-              hi = a1;
-            }
-            if (head < E.Hq) {
-              __half* dst = E.q16 + ((size_t)a * E.Hq + head) * 128 + d;
-              dst[0] = __float2half_rn(lo);
-              dst[64] = __float2half_rn(hi);
-            } else {
-              const int pid = E.table[(size_t)a * E.max_pages + (ps >> 4)];
-              if ((unsigned)pid >= (unsigned)E.pages) {
-                atomicExch(p.status, 1);
-                continue;
-              }
-              const int kh = head - E.Hq;
-              const int isv = kh >= E.Hkv ? 1 : 0;
-              __half* dst = E.pool + (((size_t)pid * E.Hkv + (kh - isv * E.Hkv)) * 2 + isv) * (16 * 128) + (ps & 15) * 128 + d;
-              dst[0] = __float2half_rn(lo);
-              dst[64] = __float2half_rn(hi);
-            }
-          }
-        } else if (p.epilogue == QENG_EPI_SWIGLU) {
-          for (int e = lane; e < p.M * 8; e += 32) {
-            const int a = e >> 3, r = e & 7;
-            const float gate = total(a, r), up = total(a, r + 8);
-            p.y[(size_t)a * p.ldy + (size_t)tile * 8 + r] = gate / (1.0f + __expf(-gate)) * up;
-          }
-        } else if (p.push_world > 0) {
-          // this rank's part of the residual update, tagged, into every rank's inbox (own included)
-          for (int e = lane; e < p.M * 16; e += 32) {
-            const int a = e >> 4, r = e & 15;
-            const float v = total(a, r);
-            const size_t o = ((size_t)p.push_rank * kTpFuseRows + a) * kTpFuseDm + (size_t)tile * 16 + r;
-            for (int rr = 0; rr < p.push_world; ++rr) st_pair(p.push_inbox[(p.push_rank + rr) % p.push_world] + o, v, tag_push);
-          }
         } else {
-          for (int e = lane; e < p.M * 16; e += 32) {
-            const int a = e >> 4, r = e & 15;
-            float v = total(a, r);
-            const size_t o = (size_t)a * p.ldy + (size_t)tile * 16 + r;
-            if (p.epilogue == QENG_EPI_ACCUM) v += p.y[o];
-            else if (p.epilogue == QENG_EPI_RESID) v += p.resid[o];
-            p.y[o] = v;
-          }
+          finish(tile, total);
         }
       }
       buf ^= 1;
+      QENG_TOCK(tc2, 10, warp == 0);
     }
   }
+  }
   QENG_STAMP(5);
+  QENG_REC(4);
+  QENG_FLUSH(8, warp == 0); QENG_FLUSH(9, warp == 0); QENG_FLUSH(10, warp == 0); QENG_FLUSH(11, warp == 0);
   if (failed && lane == 0) atomicExch(p.status, 4);
 }
 
@@ -589,7 +696,7 @@ int32_t launch_stream(qeng_ctx* ctx, const StreamParams& p, size_t smem, cudaStr
   // running; everything that depends on the predecessor sits behind griddepcontrol.wait
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(kCT + 32 * (kTG == 0 ? 1 : kTG));
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -605,6 +712,7 @@ struct StreamFit {
   bool ok;
   int mode, NT, cols, nstages, stage_chunks, slice_chunks, nslices;
   bool imaged;
+  bool defer;  // all 16 warps on every tile, the per-tile reduction deferred (kTG = 0)
   uint32_t image_slice_bytes;
   size_t smem;
 };
@@ -631,12 +739,14 @@ StreamFit stream_fit(const qeng_ctx* ctx, const qeng_weight* w, int64_t M, bool 
     if (!f.imaged && nsl == 1 && nch * 64 > 8 * kGroups * kCT) return false;  // single-slice staging goes through registers: K <= 12288
     const int alloc = f.mode == kM1L2 ? (slice + 1) & ~1 : slice;
     const XLayout L = x_layout(f.cols, alloc, f.mode != kMN);
-    const size_t red = (size_t)2 * kCW * kMR * 16 * 4;  // the same for every number of tile groups
+    f.defer = f.mode != kMN && nsl == 1 && ctx->stream_groups == 0;
+    const size_t red = (size_t)(f.defer ? kDeferTiles : 2) * kCW * kMR * 16 * 4;  // grouped: the same for every number of groups
     const size_t accs = nsl > 1 ? (size_t)tiles_per_cta * kMR * 16 * 4 : 0;
     const size_t xarea = f.imaged ? 2 * (((size_t)L.bytes + 127) & ~(size_t)127) : L.bytes;
     const size_t fixed = xarea + red + accs + bars + 256;
     f.image_slice_bytes = (L.bytes + 127u) & ~127u;
-    const int sc = slice < 64 ? slice : 64;
+    const int cap = ctx->stream_stage_chunks > 0 ? ctx->stream_stage_chunks : kStageChunks;
+    const int sc = slice < cap ? slice : cap;
     const size_t slot = (size_t)sc * 576;
     if (fixed + 2 * slot > budget) return false;
     int ns = (int)((budget - fixed) / slot);
@@ -758,8 +868,7 @@ int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
   // (a tile worked on by 4 warps takes ~1.8 us, by 8 warps ~0.9: with only two tiles per CTA two groups of
   // 8 warps finish sooner than two of four groups of 4)
   int tg = per_cta >= 3 ? 4 : (per_cta == 2 ? 2 : 1);
-  // a group needs a ring of its own at least as long as one row tile (a tile may span several
-  // stages, and a group whose ring is shorter than its tile stalls the producer)
+  // a group needs a ring of its own at least as long as one row tile
   const int spt = (f.slice_chunks + f.stage_chunks - 1) / f.stage_chunks;
   while (tg > 1 && f.nstages / tg < spt) tg >>= 1;
   if (ctx->stream_groups == 1 || ctx->stream_groups == 2 || ctx->stream_groups == 4) tg = ctx->stream_groups;
@@ -767,6 +876,11 @@ int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
 #define QENG_STREAM_CASE(MODE_, NT_)                                                   \
   (tg == 4 ? launch_stream<MODE_, NT_, 4>(ctx, p, f.smem, stream)                      \
            : (tg == 2 ? launch_stream<MODE_, NT_, 2>(ctx, p, f.smem, stream) : launch_stream<MODE_, NT_, 1>(ctx, p, f.smem, stream)))
+  if (f.defer) {
+    if (f.mode == kM1L3) return launch_stream<kM1L3, 1, 0>(ctx, p, f.smem, stream);
+    if (f.mode == kM1L2) return launch_stream<kM1L2, 1, 0>(ctx, p, f.smem, stream);
+    return launch_stream<kM2L2, 1, 0>(ctx, p, f.smem, stream);
+  }
   if (f.mode == kM1L3) return QENG_STREAM_CASE(kM1L3, 1);
   if (f.mode == kM1L2) return QENG_STREAM_CASE(kM1L2, 1);
   if (f.mode == kM2L2) return QENG_STREAM_CASE(kM2L2, 1);

@@ -65,7 +65,7 @@ struct qeng_ctx {
   bool pdl = true;            // launch the streaming matmul with programmatic stream serialization
   // remaining switches of qeng_options
   bool p2p_allowed = true, attn_cluster = true, step_kernel = false;
-  int attn_ctas_per_sm = 8, stream_groups = 0;
+  int attn_ctas_per_sm = 8, stream_groups = 0, stream_stage_chunks = 0;
   // bumped whenever attn_scratch moves: a captured graph that holds the old address is stale
   uint64_t scratch_gen = 0;
   // per-CTA argmax partials and the arrival counter of the fused LM head
@@ -218,3 +218,23 @@ int32_t qeng_tp_fuse_advance(qeng_ctx* ctx, cudaStream_t stream);
 int32_t qeng_gemm_q4_prefill(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t x_dtype, int64_t M, int64_t ldx,
                              float* y, int64_t ldy, int accumulate, cudaStream_t stream);
 constexpr int64_t kPrefillRows = 256;  // from this many rows on, matmuls take the tensor-core path
+
+#if defined(QENG_TRACE) && defined(__CUDACC__)
+// tuning builds only: a launch log behind the status word (status + 256 bytes: a counter, then records
+// of 8 u64: kind, then %globaltimer stamps)
+__device__ __forceinline__ unsigned long long qeng_trace_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ unsigned long long* qeng_trace_open(int32_t* status, unsigned long long kind) {
+  unsigned long long* log = reinterpret_cast<unsigned long long*>(status) + 32;
+  const unsigned long long idx = atomicAdd(log, 1ull);
+  if (idx >= 30000ull) return log + 8;  // overflow: everything lands in record 0
+  unsigned long long* rec = log + 8 + idx * 8;
+  rec[0] = kind;
+  rec[1] = qeng_trace_now();
+  return rec;
+}
+#endif
+

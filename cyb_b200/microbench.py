@@ -26,7 +26,8 @@ def _events(torch):
 def gemv(args):
     import torch
     from cyb_b200 import qeng
-    ctx = qeng.Context(0, stream_groups=args.groups) if args.groups else qeng.Context(0)
+    opts = {k: v for k, v in (("stream_groups", args.groups), ("stream_stage_chunks", args.stage_chunks)) if v}
+    ctx = qeng.Context(0, **opts)
     n, k, m = args.n, args.k, args.m
     wbytes = n * k * 0.5625
     pool = args.pool or max(2, int(160e6 // wbytes) + 1)
@@ -223,6 +224,7 @@ def main(argv=None):
     g.add_argument("--iters", type=int, default=20)
     g.add_argument("--flags", type=int, default=0)
     g.add_argument("--groups", type=int, default=0, help="tile groups of the streaming kernel (1, 2, 4; 0 = by shape)")
+    g.add_argument("--stage-chunks", type=int, default=0, help="K chunks per ring stage (0 = default)")
     a = sub.add_parser("attn")
     a.add_argument("--batch", type=int, default=16)
     a.add_argument("--lo", type=int, default=512)

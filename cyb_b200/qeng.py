@@ -53,7 +53,7 @@ class Options(C.Structure):
     """qeng_options: tuning switches fixed when a context is created (0 keeps the default)."""
     _fields_ = [("struct_size", C.c_int32), ("no_pdl", C.c_int32), ("no_l2_prefetch", C.c_int32),
                 ("no_p2p_allreduce", C.c_int32), ("no_attn_cluster", C.c_int32), ("attn_ctas_per_sm", C.c_int32),
-                ("stream_groups", C.c_int32), ("step_kernel", C.c_int32)]
+                ("stream_groups", C.c_int32), ("step_kernel", C.c_int32), ("stream_stage_chunks", C.c_int32)]
 
 
 class ModelCfg(C.Structure):
@@ -147,7 +147,7 @@ class Context:
 
     def __init__(self, device=0, **options):
         """`options`: fields of qeng_options (no_pdl, no_l2_prefetch, no_p2p_allreduce, no_attn_cluster,
-        attn_ctas_per_sm, stream_groups, step_kernel)."""
+        attn_ctas_per_sm, stream_groups, step_kernel, stream_stage_chunks)."""
         h = _vp()
         if options:
             o = Options(struct_size=C.sizeof(Options), **{k: int(v) for k, v in options.items()})

@@ -76,6 +76,8 @@ typedef struct qeng_options {
   int32_t stream_groups;     /* tile groups of the streaming matmul: 1, 2 or 4 (default: by shape) */
   int32_t step_kernel;       /* 1: decode steps of 1 or 2 sequences run all layers in one persistent cooperative
                                 kernel (tagged data flow between the operators) instead of one kernel per operator */
+  int32_t stream_stage_chunks; /* 64-wide K chunks per shared-memory ring stage of the streaming matmul: 4..64
+                                  (default 16) */
 } qeng_options;
 int32_t qeng_create_opts(int32_t device, const qeng_options* opts, qeng_ctx** out);
 int32_t qeng_destroy(qeng_ctx* ctx);
