@@ -130,6 +130,15 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
   __shared__ int slot_ok[kRing];
   const int s = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  // Without a window the first 32 page-table entries of this CTA do not depend on the sequence
+  // length: the producer asks for them together with the length instead of after it (one memory
+  // round trip less on the way to the first page).  Entries past the sequence are read (the table
+  // row is max_pages long) and never used.
+  int pid_spec = -1;
+  if (warp == kAW && p.window == 0) {
+    const int idx = kCl ? s + lane * p.S : s * p.pps + lane;
+    if (idx < p.max_pages && (kCl || lane < p.pps)) pid_spec = p.table[(size_t)b * p.max_pages + idx];
+  }
   if (tid == 0) {
     for (int i = 0; i < kRing; ++i) {
       mbar_init(smem_u32(full + i), 1);
@@ -172,7 +181,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
     for (int base = 0; base < n_mine; base += 32) {
       const int i = base + lane;
       int pid = -1;
-      if (i < n_mine) pid = p.table[(size_t)b * p.max_pages + first + i * pstep];
+      if (i < n_mine) pid = (base == 0 && p.window == 0) ? pid_spec : p.table[(size_t)b * p.max_pages + first + i * pstep];
       const int cnt = min(32, n_mine - base);
       for (int j = 0; j < cnt; ++j) {
         const int pj = __shfl_sync(0xffffffffu, pid, j);

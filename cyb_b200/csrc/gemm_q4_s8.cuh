@@ -29,17 +29,7 @@
 #define QENG_G4_UNROLL 2
 #endif
 
-#ifndef QENG_DIAG
-#define QENG_DIAG 0
-#endif
-#ifndef QENG_SPLIT_ACC
-#define QENG_SPLIT_ACC 0
-#endif
-#ifndef QENG_L3_UNROLL
-#define QENG_L3_UNROLL 2
-#endif
 namespace q4s8 {
-constexpr int kL3Unroll = QENG_L3_UNROLL;
 constexpr int kG4Unroll = QENG_G4_UNROLL;  // items of the one-row loop in flight per warp
 
 constexpr int kCW = 16;               // consumer warps
@@ -186,9 +176,12 @@ __device__ __forceinline__ void quantise_group(const float (&v)[8], bool valid, 
                                                uint32_t zin0, uint32_t fex0, uint32_t zs, int blk_off32, int t) {
   constexpr int kBits = LIMBS == 3 ? 20 : 13;          // the block's largest magnitude lands in [2^kBits, 2^(kBits+1))
   constexpr int kMaxQ = LIMBS == 3 ? 2097151 : 16383;
-  float amax = 0.f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  // Every thread of every CTA runs this once per matmul before the first MMA can issue, so the
+  // code is written for a short dependency chain: tree reductions, rounding by a magic add, bytes
+  // gathered with PRMT, byte sums with dp4a, the low limbs' sums sharing one shuffle.
+  const float a01 = fmaxf(fabsf(v[0]), fabsf(v[1])), a23 = fmaxf(fabsf(v[2]), fabsf(v[3]));
+  const float a45 = fmaxf(fabsf(v[4]), fabsf(v[5])), a67 = fmaxf(fabsf(v[6]), fabsf(v[7]));
+  float amax = fmaxf(fmaxf(a01, a23), fmaxf(a45, a67));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
   // 2^-e with e = exponent(amax) - kBits; a zero, denormal-tiny or non-finite block quantises to zeros
@@ -196,27 +189,41 @@ __device__ __forceinline__ void quantise_group(const float (&v)[8], bool valid, 
   const bool ok = ex >= 32 && ex <= 230;
   const float inv = ok ? __uint_as_float((uint32_t)(254 + kBits - ex) << 23) : 0.f;  // 2^(kBits - (ex - 127))
   const float step = ok ? __uint_as_float((uint32_t)(ex - kBits) << 23) : 0.f;      // 2^(ex - 127 - kBits)
-  int sum[LIMBS];
+  // q = rint(v 2^-e): v * inv is exact and below 2^22 in magnitude, so adding 1.5 * 2^23 rounds it to an
+  // integer (ties to even) in the low mantissa bits.  |q| <= kMaxQ + 1 by construction: only the upper
+  // clamp can bite.
+  int q[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) q[i] = min(__float_as_int(fmaf(v[i], inv, kBiasF)) - (int)kBias, kMaxQ);
   uint32_t w0[LIMBS], w1[LIMBS];  // bytes of k = 0,2,4,6 and of k = 1,3,5,7, per limb
-#pragma unroll
-  for (int l = 0; l < LIMBS; ++l) { sum[l] = 0; w0[l] = 0u; w1[l] = 0u; }
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    int q = __float2int_rn(v[i] * inv);
-    q = max(-kMaxQ - 1, min(kMaxQ, q));
-#pragma unroll
-    for (int l = 0; l < LIMBS; ++l) {
-      const int sh = 7 * (LIMBS - 1 - l);
-      const int d = l == 0 ? (q >> sh) : ((q >> sh) & 127);
-      sum[l] += d;
-      const uint32_t byte = ((uint32_t)d & 0xffu) << (8 * (i >> 1));
-      if (i & 1) w1[l] |= byte; else w0[l] |= byte;
-    }
-  }
+  int sum[LIMBS];
 #pragma unroll
   for (int l = 0; l < LIMBS; ++l) {
-    sum[l] += __shfl_xor_sync(0xffffffffu, sum[l], 1);
-    sum[l] += __shfl_xor_sync(0xffffffffu, sum[l], 2);
+    const int sh = 7 * (LIMBS - 1 - l);
+    uint32_t d[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) d[i] = l == 0 ? (uint32_t)(q[i] >> sh) : (uint32_t)((q[i] >> sh) & 127);
+    w0[l] = __byte_perm(__byte_perm(d[0], d[2], 0x0040), __byte_perm(d[4], d[6], 0x0040), 0x5410);
+    w1[l] = __byte_perm(__byte_perm(d[1], d[3], 0x0040), __byte_perm(d[5], d[7], 0x0040), 0x5410);
+    sum[l] = __dp4a((int)w0[l], 0x01010101, __dp4a((int)w1[l], 0x01010101, 0));
+  }
+  // sums over the quad: the most significant limb is signed and (with three limbs) travels alone; the
+  // lower limbs are 0..4064 per block and share a register, 16 bits each
+  if (LIMBS == 2) {
+    int s = (sum[0] << 16) + sum[1];
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    sum[1] = s & 0xffff;
+    sum[0] = s >> 16;
+  } else {
+    int s = (sum[1] << 16) + sum[LIMBS - 1], h = sum[0];
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    h += __shfl_xor_sync(0xffffffffu, h, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    h += __shfl_xor_sync(0xffffffffu, h, 2);
+    sum[0] = h;
+    sum[1] = s >> 16;
+    sum[LIMBS - 1] = s & 0xffff;
   }
   if (valid) {
     const int b4 = blk_off32 >> 3;  // block index * 4 bytes
@@ -266,20 +273,11 @@ __device__ __forceinline__ void consume_g4(float (&acc)[2], uint32_t wbase, uint
     const uint2 f2 = lds64(fex + (uint32_t)it * 16u);
     const uint2 b = lds64(xa + (uint32_t)it * 128u);
     int d[4] = {(int)z2.x, (int)z2.y, (int)z2.x, (int)z2.y};
-#if QENG_SPLIT_ACC
-    // blocks 0 and 2 feed the even columns, 1 and 3 the odd ones: two independent chains of two
-    int e[4] = {(int)z2.x, (int)z2.y, (int)z2.x, (int)z2.y};
-    block_mma(d, wA.x, wA.y, b.x & k0, b.y & k0);
-    block_mma(e, wA.z, wA.w, b.x & k1, b.y & k1);
-    block_mma(d, wB.x, wB.y, b.x & k2, b.y & k2);
-    block_mma(e, wB.z, wB.w, b.x & k3, b.y & k3);
-    d[1] = e[1]; d[3] = e[3];
-#else
     block_mma(d, wA.x, wA.y, b.x & k0, b.y & k0);
     block_mma(d, wA.z, wA.w, b.x & k1, b.y & k1);
     block_mma(d, wB.x, wB.y, b.x & k2, b.y & k2);
     block_mma(d, wB.z, wB.w, b.x & k3, b.y & k3);
-#endif
+
     const float2 se = __half22float2(*reinterpret_cast<const __half2*>(&s2.x));  // (row g, row g+8) of the even block
     const float2 so = __half22float2(*reinterpret_cast<const __half2*>(&s2.y));  // ... of the odd block
     const float fe = __uint_as_float(f2.x), fo = __uint_as_float(f2.y);
@@ -306,45 +304,19 @@ __device__ __forceinline__ void consume_m1l3(float (&acc)[2], uint32_t wbase, ui
   const uint32_t zin = xbase + L.zin + (uint32_t)limb * L.zs + (uint32_t)blk0 * 4u;
   const uint32_t fex = xbase + L.fex + (uint32_t)limb * L.zs + (uint32_t)blk0 * 4u;
   const float live = t < 3 ? 1.f : 0.f;
-#pragma unroll kL3Unroll
+#pragma unroll 2
   for (int it = wi; it < nc; it += NW) {
     const uint4 w = lds128(wbase + (uint32_t)it * 512u + (uint32_t)lane * 16u);
-#if QENG_DIAG & 8
-    const uint2 s2 = make_uint2(0x3c003c00u + it, 0x3c003c00u), z2 = make_uint2(kBias, kBias), f2 = make_uint2(0x3f800000u, 0x3f800000u);
-#else
     const uint2 s2 = lds64(sbase + (uint32_t)it * 64u + (uint32_t)g * 8u);
     const uint2 z2 = lds64(zin + (uint32_t)it * 8u);
     const uint2 f2 = lds64(fex + (uint32_t)it * 8u);
-#endif
     int d[4] = {(int)z2.x, (int)z2.y, (int)z2.x, (int)z2.y};
     const uint32_t xo = (uint32_t)it * 64u;
     uint2 b, b2;
-#if QENG_DIAG & 16
-    b = make_uint2(0x01020304u + it, 0x01020304u); b2 = b;
-#else
     b = lds64(xa[0] + xo);
     b2 = lds64(xa[1] + xo);
-#endif
-#if QENG_DIAG & 2
-    imma(d, w.x, w.y, w.x, w.y, b.x, b.y);
-    imma(d, w.z, w.w, w.z, w.w, b2.x, b2.y);
-#elif QENG_DIAG & 4
-    d[0] ^= (w.x & 0x0f0f0f0fu) + b.x; d[1] ^= (w.y & 0x0f0f0f0fu) + b.y; d[2] ^= ((w.x >> 4) & 0x0f0f0f0fu) + b2.x; d[3] ^= ((w.y >> 4) & 0x0f0f0f0fu) + b2.y;
-    d[0] ^= (w.z & 0x0f0f0f0fu) + b.x; d[1] ^= (w.w & 0x0f0f0f0fu) + b.y; d[2] ^= ((w.z >> 4) & 0x0f0f0f0fu) + b2.x; d[3] ^= ((w.w >> 4) & 0x0f0f0f0fu) + b2.y;
-#elif QENG_SPLIT_ACC
-    // the two blocks feed different columns: two accumulators make the MMAs independent
-    int e[4] = {(int)z2.x, (int)z2.y, (int)z2.x, (int)z2.y};
-    block_mma(d, w.x, w.y, b.x, b.y);
-    block_mma(e, w.z, w.w, b2.x, b2.y);
-    d[1] = e[1]; d[3] = e[3];
-#else
     block_mma(d, w.x, w.y, b.x, b.y);
     block_mma(d, w.z, w.w, b2.x, b2.y);
-#endif
-#if QENG_DIAG & 1
-    acc[0] += __int_as_float(d[0] ^ d[1] ^ (int)s2.x ^ (int)f2.x);
-    acc[1] += __int_as_float(d[2] ^ d[3] ^ (int)s2.y ^ (int)f2.y);
-#else
     const float2 se = __half22float2(*reinterpret_cast<const __half2*>(&s2.x));
     const float2 so = __half22float2(*reinterpret_cast<const __half2*>(&s2.y));
     const float fe = __uint_as_float(f2.x) * live, fo = __uint_as_float(f2.y) * live;
@@ -352,7 +324,6 @@ __device__ __forceinline__ void consume_m1l3(float (&acc)[2], uint32_t wbase, ui
     acc[0] = fmaf(so.x * fo, unbias(d[1]), acc[0]);
     acc[1] = fmaf(se.y * fe, unbias(d[2]), acc[1]);
     acc[1] = fmaf(so.y * fo, unbias(d[3]), acc[1]);
-#endif
   }
 }
 

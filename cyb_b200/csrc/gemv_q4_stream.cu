@@ -362,8 +362,14 @@ __global__ void __launch_bounds__(kCT + 32 * (kTG == 0 ? 1 : kTG), 1) gemv_q4_st
     // The raw values of row m + 1 are requested before row m is reduced and converted, so with
     // several activation rows only the first one waits for memory.
     float nv[kGroups][8];
+    QENG_TICK(ts0);
 #pragma unroll
     for (int j = 0; j < kGroups; ++j) load8(0, (tid + j * kCT) * 8, nv[j]);
+#ifdef QENG_TRACE
+    { float probe = nv[0][0]; asm volatile("" ::"f"(probe)); }  // the first value has arrived
+    QENG_TOCK(ts0, 13, warp == 0);
+#endif
+    QENG_TICK(ts1);
     for (int m = 0; m < p.M; ++m) {
       float v[kGroups][8];
 #pragma unroll
@@ -411,6 +417,8 @@ __global__ void __launch_bounds__(kCT + 32 * (kTG == 0 ? 1 : kTG), 1) gemv_q4_st
         for (int w = 0; w < kCW; ++w) tot += wp[w];
         rs = rsqrtf(tot / (float)p.K + p.eps);
       }
+      QENG_TOCK(ts1, 14, warp == 0);
+      QENG_TICK(ts2);
 #pragma unroll
       for (int j = 0; j < kGroups; ++j) {
         const int grp = tid + j * kCT;
@@ -419,6 +427,7 @@ __global__ void __launch_bounds__(kCT + 32 * (kTG == 0 ? 1 : kTG), 1) gemv_q4_st
           put(m, grp, v[j], grp < ngroups);
         }
       }
+      QENG_TOCK(ts2, 15, warp == 0);
     }
   } else if (p.gamma != nullptr) {
     // ---- several slices: 1/rms of every row first (the slices are quantised as they come)
@@ -679,6 +688,10 @@ __global__ void __launch_bounds__(kCT + 32 * (kTG == 0 ? 1 : kTG), 1) gemv_q4_st
   }
   QENG_STAMP(5);
   QENG_REC(4);
+#ifdef QENG_TRACE
+  if (rec) { rec[5] = (unsigned long long)tacc[5]; rec[6] = (unsigned long long)tacc[6]; rec[7] = (unsigned long long)tacc[7]; }
+#endif
+  QENG_FLUSH(13, warp == 0); QENG_FLUSH(14, warp == 0); QENG_FLUSH(15, warp == 0);
   QENG_FLUSH(8, warp == 0); QENG_FLUSH(9, warp == 0); QENG_FLUSH(10, warp == 0); QENG_FLUSH(11, warp == 0);
   if (failed && lane == 0) atomicExch(p.status, 4);
 }
