@@ -25,7 +25,11 @@ namespace {
 
 constexpr int kAW = 4;  // consumer warps per CTA (one more warp produces)
 constexpr int kAT = (kAW + 1) * 32;  // threads per CTA
-constexpr int kRing = 10;            // ring slots of one page tile (K and V of 16 tokens: 8 KB)
+constexpr int kRing = 8;             // ring slots of one page tile (K and V of 16 tokens: 8 KB)
+// A slot must always be consumed by the same warp (page i goes to warp i % kAW and slot i % kRing):
+// a warp that consumed round r of a slot cannot then wait for round r + 2 before round r + 1 has
+// landed, which a parity wait could not tell from round r + 2 being there.
+static_assert(kRing % kAW == 0, "every ring slot belongs to one consumer warp");
 constexpr int kSlotBytes = 2 * 16 * 128 * 2;
 constexpr int kHD = 128;
 constexpr int kCS = 8;  // largest cluster: CTAs (splits) per sequence and kv head; the launch picks 1, 2, 4 or 8
