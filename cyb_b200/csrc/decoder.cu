@@ -795,6 +795,15 @@ int32_t qeng_decoder_load_head(qeng_ctx* ctx, qeng_decoder* d, const uint16_t* e
 int32_t qeng_decoder_reset(qeng_ctx* ctx, qeng_decoder* d, int32_t batch) {
   if (!ctx || !d) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_reset: null argument");
   if (batch < 1 || batch > d->cfg.max_batch) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_reset: batch outside 1..max_batch");
+  if (d->tp_pairs && batch != d->batch) {
+    // the slot of a rank's (max, index) pair depends on the batch (rank * batch + sequence): pairs left
+    // from another batch size would be added to another rank's slot
+    QENG_CUDA(ctx, cudaSetDevice(ctx->device));
+    const size_t pb = (size_t)2 * d->cfg.tp_world * d->cfg.max_batch * sizeof(float);
+    QENG_CUDA(ctx, cudaStreamSynchronize(d->stream));
+    QENG_CUDA(ctx, cudaMemsetAsync(d->tp_pairs, 0, pb, d->stream));
+    QENG_CUDA(ctx, cudaMemsetAsync(d->tp_gath, 0, pb, d->stream));
+  }
   d->batch = batch;
   d->len.assign(batch, 0);
   d->have_logits = false;

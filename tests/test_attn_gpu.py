@@ -38,6 +38,23 @@ def test_config4(ctx):
     assert e < 1e-4, e
 
 
+def test_config4_repeated_with_a_cold_cache(ctx):
+    """The same call several times, the cache overwritten in between (page copies then land out of
+    order): every repetition must give the same, correct result."""
+    import torch
+    lens, q, ks, vs, pool_np, table = ref.config4()
+    want = ref.attn_decode(q, ks, vs)
+    pool = ctx.kv_pool(pool_np.shape[0], pool_np.shape[1])
+    pool.tensor().copy_(_t(pool_np))
+    tq, tt, tl = _t(q), _t(table), _t(lens)
+    for rep in range(12):
+        if rep % 3 == 0:
+            torch.empty(1 << 28, dtype=torch.uint8, device="cuda").random_()
+        out = ctx.attn_decode(pool, tq, tt, tl).cpu().numpy()
+        assert ref.err_inf(out, want) < 1e-4, rep
+    pool.free()
+
+
 def test_known_answers(ctx):
     rng = ref.rng_of(21)
     # len 1 -> V[0]; empty sequence -> zeros

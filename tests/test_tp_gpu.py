@@ -184,7 +184,7 @@ def _wide_rank_main(rank, world, port, out):
     ctx.tp_init(rank, world, exchange, allgather)
     cfg = ref.DecoderConfig(layers=2, d=256, ffn=512, heads=8, kv_heads=8, vocab=320)
     W = ref.make_decoder_weights(cfg, seed=6)
-    dec = ctx.decoder(layers=2, d_model=256, ffn=512, heads=8, kv_heads=8, vocab=320, max_batch=2, max_seq=64,
+    dec = ctx.decoder(layers=2, d_model=256, ffn=512, heads=8, kv_heads=8, vocab=320, max_batch=16, max_seq=64,
                       tp_rank=rank, tp_world=world)
     qeng.load_decoder_weights(dec, W, cfg)
     prompt = ref.rng_of(17).integers(0, 320, (2, 9)).astype(np.int32)
@@ -194,6 +194,21 @@ def _wide_rank_main(rank, world, port, out):
     e_log = ref.err_inf(dec.logits(), logs[0])
     toks = dec.decode(6)
     ctx.device_status()
+    # 3..4 rows (activations staged by the matmul itself) and 5..16 rows (quantised images): the
+    # partial sums travel through the matmul epilogues here too
+    batches = []
+    for bn in (3, 5, 16):
+        pb = ref.rng_of(170 + bn).integers(0, 320, (bn, 7)).astype(np.int32)
+        wb, lb = ref.Decoder(cfg, W).generate(pb, 5)
+        try:
+            dec.reset(bn)
+            dec.prefill(pb)
+            eb = ref.err_inf(dec.logits(), lb[0])
+            tb = dec.decode(5).tolist()
+            ctx.device_status()
+        except qeng.QengError as e:  # reported per batch size; the ranks stay in step
+            eb, tb = float("inf"), str(e)
+        batches.append((bn, eb, tb, wb.tolist()))
     dec.free()
     # one full-width layer, 5 prompt rows then a decode row
     cfgw = ref.DecoderConfig(layers=1, d=4096, ffn=11008, heads=32, kv_heads=8, vocab=256)
@@ -218,10 +233,31 @@ def _wide_rank_main(rank, world, port, out):
     allb = [None] * world
     dist.all_gather_object(allb, mine.tobytes())
     same = all(b == allb[0] for b in allb)
-    out.put((rank, e_log, toks.tolist(), want.tolist(), e_l, e_1, same))
+    out.put((rank, e_log, toks.tolist(), want.tolist(), e_l, e_1, same, batches))
     dist.barrier()
     decw.free()
     dist.destroy_process_group()
+
+
+def _collect(out, procs, world, limit_s=600):
+    """One result per rank; gives up as soon as a rank has died instead of waiting out the limit."""
+    import queue
+    import time
+    res, t0 = [], time.time()
+    while len(res) < world:
+        try:
+            res.append(out.get(timeout=2))
+        except queue.Empty:
+            dead = [p.exitcode for p in procs if p.exitcode not in (None, 0)]
+            if dead or time.time() - t0 > limit_s:
+                for p in procs:
+                    if p.is_alive():
+                        p.kill()
+                raise AssertionError("rank processes failed: exit codes %s" % [p.exitcode for p in procs])
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    return res
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
@@ -236,12 +272,12 @@ def test_sharded_decoder_against_the_teacher(built_lib, world):
     procs = [ctx.Process(target=_wide_rank_main, args=(r, world, port, out)) for r in range(world)]
     for p in procs:
         p.start()
-    res = [out.get(timeout=600) for _ in range(world)]
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
-    for rank, e_log, toks, want, e_l, e_1, same in res:
+    res = _collect(out, procs, world)
+    for rank, e_log, toks, want, e_l, e_1, same, batches in res:
         assert e_log < 2e-3, (rank, e_log)
         assert toks == want, rank
+        for bn, eb, tb, wb in batches:
+            assert eb < 2e-3, (rank, bn, eb)
+            assert tb == wb, (rank, bn, tb)
         assert e_l < 2e-3 and e_1 < 2e-3, (rank, e_l, e_1)
         assert same, rank
