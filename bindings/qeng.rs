@@ -107,10 +107,14 @@ extern "C" {
     pub fn qeng_weight_unpack_q4(ctx: *mut qeng_ctx, w: *const qeng_weight, q: *mut u8, s: *mut u16) -> i32;
     pub fn qeng_weight_dequant_f32(ctx: *mut qeng_ctx, w: *const qeng_weight, out: *mut f32, stream: *mut c_void) -> i32;
     pub fn qeng_weight_quantize_q4(ctx: *mut qeng_ctx, w_dev: *const c_void, x_dtype: i32, N: i64, K: i64, ld: i64, out: *mut *mut qeng_weight, stream: *mut c_void) -> i32;
+    pub fn qeng_weight_pack_q8(ctx: *mut qeng_ctx, q: *const i8, s: *const u16, N: i64, K: i64, out: *mut *mut qeng_weight) -> i32;
+    pub fn qeng_weight_unpack_q8(ctx: *mut qeng_ctx, w: *const qeng_weight, q: *mut i8, s: *mut u16) -> i32;
+    pub fn qeng_weight_quantize_q8(ctx: *mut qeng_ctx, w_dev: *const c_void, x_dtype: i32, N: i64, K: i64, ld: i64, out: *mut *mut qeng_weight, stream: *mut c_void) -> i32;
     pub fn qeng_weight_free(ctx: *mut qeng_ctx, w: *mut qeng_weight) -> i32;
     pub fn qeng_weight_rows(w: *const qeng_weight) -> i64;
     pub fn qeng_weight_cols(w: *const qeng_weight) -> i64;
     pub fn qeng_weight_device_bytes(w: *const qeng_weight) -> i64;
+    pub fn qeng_weight_format(w: *const qeng_weight) -> i32;
     pub fn qeng_weight_set_next(ctx: *mut qeng_ctx, w: *mut qeng_weight, next: *const qeng_weight) -> i32;
     pub fn qeng_gemm_q4(ctx: *mut qeng_ctx, w: *const qeng_weight, x: *const c_void, x_dtype: i32, M: i64, ldx: i64, y: *mut f32, ldy: i64, flags: i32, stream: *mut c_void) -> i32;
     pub fn qeng_gemv_q4(ctx: *mut qeng_ctx, w: *const qeng_weight, x: *const f32, y: *mut f32, stream: *mut c_void) -> i32;
@@ -132,6 +136,7 @@ extern "C" {
     pub fn qeng_decoder_create(ctx: *mut qeng_ctx, cfg: *const qeng_model_cfg, out: *mut *mut qeng_decoder) -> i32;
     pub fn qeng_decoder_free(ctx: *mut qeng_ctx, dec: *mut qeng_decoder) -> i32;
     pub fn qeng_decoder_load_matrix(ctx: *mut qeng_ctx, dec: *mut qeng_decoder, layer: i32, which: i32, q: *const u8, s: *const u16, N: i64, K: i64) -> i32;
+    pub fn qeng_decoder_load_matrix_q8(ctx: *mut qeng_ctx, dec: *mut qeng_decoder, layer: i32, which: i32, q: *const i8, s: *const u16, N: i64, K: i64) -> i32;
     pub fn qeng_decoder_load_norm(ctx: *mut qeng_ctx, dec: *mut qeng_decoder, layer: i32, which: i32, gamma: *const f32) -> i32;
     pub fn qeng_decoder_load_head(ctx: *mut qeng_ctx, dec: *mut qeng_decoder, emb: *const u16, lm_head: *const u16, final_gamma: *const f32) -> i32;
     pub fn qeng_decoder_config(ctx: *mut qeng_ctx, dec: *const qeng_decoder, out: *mut qeng_model_cfg) -> i32;

@@ -22,6 +22,7 @@ constexpr int kHD = 128;
 constexpr int kPage = 16;
 
 struct HostMat {
+  int fmt = QENG_FMT_Q4;
   std::vector<uint8_t> q;
   std::vector<uint16_t> s;
   int64_t N = 0, K = 0;
@@ -372,7 +373,10 @@ int32_t run_layer(qeng_ctx* ctx, qeng_decoder* d, int l, int64_t rows, const int
   Layer& L = d->layers[l];
   if (!L.wqkv || !L.wo || !L.wgu || !L.wdown || !L.norm1 || !L.norm2)
     return qeng_fail(ctx, QENG_ERR_STATE, "decoder: layer %d is not fully loaded", l);
-  if (rows >= kPrefillRows) return run_layer_prefill(ctx, d, l, rows, table, st);
+  // the tensor-core prompt path dequantises 4-bit blocks; a layer with 8-bit blocks takes its prompt rows
+  // through the decode kernels in passes of 16
+  const bool all_q4 = L.wqkv->fmt == QENG_FMT_Q4 && L.wo->fmt == QENG_FMT_Q4 && L.wgu->fmt == QENG_FMT_Q4 && L.wdown->fmt == QENG_FMT_Q4;
+  if (rows >= kPrefillRows && all_q4) return run_layer_prefill(ctx, d, l, rows, table, st);
   const int64_t dm = d->cfg.d_model;
   const bool fused = px != nullptr;
   float* x = fused ? *px : d->x;
@@ -509,6 +513,7 @@ int32_t plan_step(qeng_ctx* ctx, qeng_decoder* d) {
   for (int l = 0; l < d->cfg.layers; ++l) {
     Layer& L = d->layers[l];
     if (!L.wqkv || !L.wo || !L.wgu || !L.wdown || !L.norm1 || !L.norm2 || L.qnorm || L.knorm) return QENG_OK;
+    if (L.wqkv->fmt != QENG_FMT_Q4 || L.wo->fmt != QENG_FMT_Q4 || L.wgu->fmt != QENG_FMT_Q4 || L.wdown->fmt != QENG_FMT_Q4) return QENG_OK;
     qeng_step_layer_desc ld;
     ld.w[0] = L.wqkv; ld.w[1] = L.wo; ld.w[2] = L.wgu; ld.w[3] = L.wdown;
     ld.norm1 = L.norm1; ld.norm2 = L.norm2;
@@ -678,8 +683,15 @@ static void link_weights(qeng_decoder* d) {
   }
 }
 
-int32_t qeng_decoder_load_matrix(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, int32_t which, const uint8_t* q,
-                                 const uint16_t* s, int64_t N, int64_t K) {
+static int32_t pack_fmt(qeng_ctx* ctx, int fmt, const uint8_t* q, const uint16_t* s, int64_t N, int64_t K, qeng_weight** out) {
+  if (fmt == QENG_FMT_Q8) return qeng_weight_pack_q8(ctx, reinterpret_cast<const int8_t*>(q), s, N, K, out);
+  return qeng_weight_pack_q4(ctx, q, s, N, K, out);
+}
+
+// one matrix of a layer in either block format: q holds one code (4-bit: 0..15) or one signed byte
+// (8-bit) per weight; sharding, the rotary row order and the q|k|v / gate|up fusion work on bytes
+static int32_t load_matrix_fmt(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, int32_t which, int fmt, const uint8_t* q,
+                               const uint16_t* s, int64_t N, int64_t K) {
   if (!ctx || !d || !q || !s) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_load_matrix: null argument");
   if (layer < 0 || layer >= d->cfg.layers || which < 0 || which > QENG_W_DOWN)
     return qeng_fail(ctx, QENG_ERR_ARG, "decoder_load_matrix: bad layer/which");
@@ -699,12 +711,19 @@ int32_t qeng_decoder_load_matrix(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, 
                      (long long)eN, (long long)eK, (long long)N, (long long)K);
   Layer& L = d->layers[layer];
   HostMat& hm = L.pend[which];
+  // the matrices fused into one (q|k|v, gate|up) must come in one format
+  const int lo = which <= QENG_W_V ? QENG_W_Q : QENG_W_GATE, hi = which <= QENG_W_V ? QENG_W_V : QENG_W_UP;
+  if (which <= QENG_W_V || which == QENG_W_GATE || which == QENG_W_UP)
+    for (int i = lo; i <= hi; ++i)
+      if (i != which && L.pend[i].N && L.pend[i].fmt != fmt)
+        return qeng_fail(ctx, QENG_ERR_ARG, "decoder_load_matrix: layer %d mixes 4-bit and 8-bit blocks inside a fused matrix", layer);
   const bool row_split = which == QENG_W_O || which == QENG_W_DOWN;  // split along K, partial sums
   if (row_split) take_shard(q, s, K, 0, N, K / t * r, K / t * (r + 1), hm);
   else take_shard(q, s, K, N / t * r, N / t * (r + 1), 0, K, hm);
+  hm.fmt = fmt;
   if (which <= QENG_W_V) {  // rotary pairs (i, i+64) of every head become MMA rows g / g+8 of one tile
     HostMat pm;
-    pm.N = hm.N; pm.K = hm.K;
+    pm.N = hm.N; pm.K = hm.K; pm.fmt = fmt;
     pm.q.resize(hm.q.size());
     pm.s.resize(hm.s.size());
     for (int64_t row = 0; row < hm.N; ++row) {
@@ -719,7 +738,7 @@ int32_t qeng_decoder_load_matrix(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, 
   if (row_split) {
     qeng_weight** dst = which == QENG_W_O ? &L.wo : &L.wdown;
     qeng_weight_free(ctx, *dst); *dst = nullptr;
-    rc = qeng_weight_pack_q4(ctx, hm.q.data(), hm.s.data(), hm.N, hm.K, dst);
+    rc = pack_fmt(ctx, fmt, hm.q.data(), hm.s.data(), hm.N, hm.K, dst);
     hm = HostMat();
   } else if (which <= QENG_W_V) {
     if (L.pend[QENG_W_Q].N && L.pend[QENG_W_K].N && L.pend[QENG_W_V].N) {
@@ -732,7 +751,7 @@ int32_t qeng_decoder_load_matrix(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, 
         L.pend[i] = HostMat();
       }
       qeng_weight_free(ctx, L.wqkv); L.wqkv = nullptr;
-      rc = qeng_weight_pack_q4(ctx, f.q.data(), f.s.data(), f.N, f.K, &L.wqkv);
+      rc = pack_fmt(ctx, fmt, f.q.data(), f.s.data(), f.N, f.K, &L.wqkv);
     }
   } else {
     if (L.pend[QENG_W_GATE].N && L.pend[QENG_W_UP].N) {
@@ -753,13 +772,23 @@ int32_t qeng_decoder_load_matrix(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, 
       L.pend[QENG_W_GATE] = HostMat();
       L.pend[QENG_W_UP] = HostMat();
       qeng_weight_free(ctx, L.wgu); L.wgu = nullptr;
-      rc = qeng_weight_pack_q4(ctx, f.q.data(), f.s.data(), f.N, f.K, &L.wgu);
+      rc = pack_fmt(ctx, fmt, f.q.data(), f.s.data(), f.N, f.K, &L.wgu);
     }
   }
   link_weights(d);
   if (d->graph) { cudaGraphExecDestroy(d->graph); d->graph = nullptr; }
   qeng_step_free(d->fused); d->fused = nullptr; d->step_planned = false;
   return rc;
+}
+
+int32_t qeng_decoder_load_matrix(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, int32_t which, const uint8_t* q,
+                                 const uint16_t* s, int64_t N, int64_t K) {
+  return load_matrix_fmt(ctx, d, layer, which, QENG_FMT_Q4, q, s, N, K);
+}
+
+int32_t qeng_decoder_load_matrix_q8(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, int32_t which, const int8_t* q,
+                                    const uint16_t* s, int64_t N, int64_t K) {
+  return load_matrix_fmt(ctx, d, layer, which, QENG_FMT_Q8, reinterpret_cast<const uint8_t*>(q), s, N, K);
 }
 
 int32_t qeng_decoder_load_norm(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, int32_t which, const float* gamma) {

@@ -114,6 +114,42 @@ __device__ __forceinline__ void block_mma(int (&d)[4], uint32_t w0, uint32_t w1,
   const uint32_t m = 0x0f0f0f0fu;
   imma(d, w0 & m, w1 & m, (w0 >> 4) & m, (w1 >> 4) & m, b0, b1);
 }
+// the same contraction for 8-bit block weights (signed bytes): no unpacking, no zero point
+__device__ __forceinline__ void imma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// Weight format of a matmul: Q4 = 4-bit codes (two 32-blocks per uint4 and lane, 512 B per 64-wide
+// chunk of a row tile); Q8 = signed bytes (one 32-block per uint4 and lane: the bytes of row g at
+// k = 8t + 0,2,4,6, of row g+8 likewise, then k = 8t + 1,3,5,7 of both rows, i.e. the A registers of
+// the MMA in the k order the staged activations use; 1024 B per chunk).  Both carry the same scale
+// plane.  `WBlocks` holds the two blocks of one chunk for this lane.
+template <bool Q8>
+struct WBlocks {
+  uint4 lo, hi;  // Q4: lo holds both blocks (hi unused); Q8: block 0, block 1
+};
+template <bool Q8>
+__device__ __forceinline__ uint32_t chunk_bytes() { return Q8 ? 1024u : 512u; }
+template <bool Q8>
+__device__ __forceinline__ WBlocks<Q8> load_chunk(uint32_t chunk_addr, int lane) {
+  WBlocks<Q8> w;
+  w.lo = lds128(chunk_addr + (uint32_t)lane * 16u);
+  if (Q8) w.hi = lds128(chunk_addr + 512u + (uint32_t)lane * 16u);
+  return w;
+}
+// d += block j (0 or 1) of the chunk times the activation bytes (b0, b1)
+template <bool Q8>
+__device__ __forceinline__ void chunk_mma(int (&d)[4], const WBlocks<Q8>& w, int j, uint32_t b0, uint32_t b1) {
+  if (Q8) {
+    const uint4& a = j == 0 ? w.lo : w.hi;
+    imma_s8(d, a.x, a.y, a.z, a.w, b0, b1);
+  } else {
+    if (j == 0) block_mma(d, w.lo.x, w.lo.y, b0, b1);
+    else block_mma(d, w.lo.z, w.lo.w, b0, b1);
+  }
+}
 __device__ __forceinline__ float unbias(int d) { return __int_as_float(d) - kBiasF; }
 
 __device__ __forceinline__ float act_f32(const void* x, int dtype, long long i) {
@@ -246,7 +282,7 @@ __device__ __forceinline__ void quantise_group(const float (&v)[8], bool valid, 
 // work items wi, wi + NW, ...; an item is max(G/2, 1) chunks.
 
 // G = 4: one activation row.  acc[0] += row g, acc[1] += row g+8 (partial over this lane's columns).
-template <int NW>
+template <int NW, bool Q8 = false>
 __device__ __forceinline__ void consume_g4(float (&acc)[2], uint32_t wbase, uint32_t sbase, int nc, int blk0,
                                            const XLayout& L, uint32_t xbase, int wi, int lane) {
   const int g = lane >> 2, t = lane & 3;
@@ -263,9 +299,8 @@ __device__ __forceinline__ void consume_g4(float (&acc)[2], uint32_t wbase, uint
   const int nitems = (nc + 1) >> 1;
 #pragma unroll kG4Unroll
   for (int it = wi; it < nitems; it += NW) {
-    const uint32_t wo = wbase + (uint32_t)it * 1024u + (uint32_t)lane * 16u;
-    const uint4 wA = lds128(wo);
-    const uint4 wB = lds128(wo + 512u);
+    const WBlocks<Q8> wA = load_chunk<Q8>(wbase + (uint32_t)(2 * it) * chunk_bytes<Q8>(), lane);
+    const WBlocks<Q8> wB = load_chunk<Q8>(wbase + (uint32_t)(2 * it + 1) * chunk_bytes<Q8>(), lane);
     const int ch = 2 * it + (t & 1);
     uint2 s2 = lds64(sbase + (uint32_t)ch * 64u + (uint32_t)g * 8u);
     if (ch >= nc) s2 = make_uint2(0u, 0u);  // a chunk past the stage's data: whatever the slot holds must not count
@@ -273,10 +308,11 @@ __device__ __forceinline__ void consume_g4(float (&acc)[2], uint32_t wbase, uint
     const uint2 f2 = lds64(fex + (uint32_t)it * 16u);
     const uint2 b = lds64(xa + (uint32_t)it * 128u);
     int d[4] = {(int)z2.x, (int)z2.y, (int)z2.x, (int)z2.y};
-    block_mma(d, wA.x, wA.y, b.x & k0, b.y & k0);
-    block_mma(d, wA.z, wA.w, b.x & k1, b.y & k1);
-    block_mma(d, wB.x, wB.y, b.x & k2, b.y & k2);
-    block_mma(d, wB.z, wB.w, b.x & k3, b.y & k3);
+    if (Q8) d[0] = d[1] = d[2] = d[3] = (int)kBias;  // signed bytes: no zero point
+    chunk_mma<Q8>(d, wA, 0, b.x & k0, b.y & k0);
+    chunk_mma<Q8>(d, wA, 1, b.x & k1, b.y & k1);
+    chunk_mma<Q8>(d, wB, 0, b.x & k2, b.y & k2);
+    chunk_mma<Q8>(d, wB, 1, b.x & k3, b.y & k3);
 
     const float2 se = __half22float2(*reinterpret_cast<const __half2*>(&s2.x));  // (row g, row g+8) of the even block
     const float2 so = __half22float2(*reinterpret_cast<const __half2*>(&s2.y));  // ... of the odd block
@@ -291,7 +327,7 @@ __device__ __forceinline__ void consume_g4(float (&acc)[2], uint32_t wbase, uint
 // One activation row in three limbs (22 bits): the 8 columns hold (limb, block) for the TWO blocks of
 // a chunk (6 used); lane t < 3 owns limb t of both blocks, lane t = 3 idles.  acc[0] += row g,
 // acc[1] += row g+8.
-template <int NW>
+template <int NW, bool Q8 = false>
 __device__ __forceinline__ void consume_m1l3(float (&acc)[2], uint32_t wbase, uint32_t sbase, int nc, int blk0,
                                              const XLayout& L, uint32_t xbase, int wi, int lane) {
   const int g = lane >> 2, t = lane & 3;
@@ -306,17 +342,18 @@ __device__ __forceinline__ void consume_m1l3(float (&acc)[2], uint32_t wbase, ui
   const float live = t < 3 ? 1.f : 0.f;
 #pragma unroll 2
   for (int it = wi; it < nc; it += NW) {
-    const uint4 w = lds128(wbase + (uint32_t)it * 512u + (uint32_t)lane * 16u);
+    const WBlocks<Q8> w = load_chunk<Q8>(wbase + (uint32_t)it * chunk_bytes<Q8>(), lane);
     const uint2 s2 = lds64(sbase + (uint32_t)it * 64u + (uint32_t)g * 8u);
     const uint2 z2 = lds64(zin + (uint32_t)it * 8u);
     const uint2 f2 = lds64(fex + (uint32_t)it * 8u);
     int d[4] = {(int)z2.x, (int)z2.y, (int)z2.x, (int)z2.y};
+    if (Q8) d[0] = d[1] = d[2] = d[3] = (int)kBias;
     const uint32_t xo = (uint32_t)it * 64u;
     uint2 b, b2;
     b = lds64(xa[0] + xo);
     b2 = lds64(xa[1] + xo);
-    block_mma(d, w.x, w.y, b.x, b.y);
-    block_mma(d, w.z, w.w, b2.x, b2.y);
+    chunk_mma<Q8>(d, w, 0, b.x, b.y);
+    chunk_mma<Q8>(d, w, 1, b2.x, b2.y);
     const float2 se = __half22float2(*reinterpret_cast<const __half2*>(&s2.x));
     const float2 so = __half22float2(*reinterpret_cast<const __half2*>(&s2.y));
     const float fe = __uint_as_float(f2.x) * live, fo = __uint_as_float(f2.y) * live;
@@ -329,7 +366,7 @@ __device__ __forceinline__ void consume_m1l3(float (&acc)[2], uint32_t wbase, ui
 
 // G = 2: two activation rows; columns = (row, limb) x 2 blocks; an item is one chunk.
 // This lane's output columns: column pair t = (row t>>1, limb t&1), blocks 0 and 1 of the chunk.
-template <int NW>
+template <int NW, bool Q8 = false>
 __device__ __forceinline__ void consume_g2(float (&acc)[2], uint32_t wbase, uint32_t sbase, int nc, int blk0,
                                            const XLayout& L, uint32_t xbase, int wi, int lane) {
   const int g = lane >> 2, t = lane & 3;
@@ -343,17 +380,18 @@ __device__ __forceinline__ void consume_g2(float (&acc)[2], uint32_t wbase, uint
   const uint32_t fex = xbase + L.fex + (uint32_t)t * L.zs + (uint32_t)blk0 * 4u;
 #pragma unroll 2
   for (int it = wi; it < nc; it += NW) {
-    const uint4 w = lds128(wbase + (uint32_t)it * 512u + (uint32_t)lane * 16u);
+    const WBlocks<Q8> w = load_chunk<Q8>(wbase + (uint32_t)it * chunk_bytes<Q8>(), lane);
     const uint2 s2 = lds64(sbase + (uint32_t)it * 64u + (uint32_t)g * 8u);
     const uint2 z2 = lds64(zin + (uint32_t)it * 8u);
     const uint2 f2 = lds64(fex + (uint32_t)it * 8u);
     int d[4] = {(int)z2.x, (int)z2.y, (int)z2.x, (int)z2.y};
+    if (Q8) d[0] = d[1] = d[2] = d[3] = (int)kBias;
     const uint32_t xo = (uint32_t)it * 64u;
     uint2 b;
     b = lds64(xa[0] + xo);
-    block_mma(d, w.x, w.y, b.x, b.y);
+    chunk_mma<Q8>(d, w, 0, b.x, b.y);
     b = lds64(xa[1] + xo);
-    block_mma(d, w.z, w.w, b.x, b.y);
+    chunk_mma<Q8>(d, w, 1, b.x, b.y);
     const float2 se = __half22float2(*reinterpret_cast<const __half2*>(&s2.x));
     const float2 so = __half22float2(*reinterpret_cast<const __half2*>(&s2.y));
     const float fe = __uint_as_float(f2.x), fo = __uint_as_float(f2.y);
@@ -366,7 +404,7 @@ __device__ __forceinline__ void consume_g2(float (&acc)[2], uint32_t wbase, uint
 
 // G = 1: NT tiles of 8 columns = 4 activation rows each; lane t of tile nt owns row 4 nt + t, both
 // limbs.  acc[nt][0] += row g of the weights, acc[nt][1] += row g+8.  An item is one chunk.
-template <int NW, int NT>
+template <int NW, int NT, bool Q8 = false>
 __device__ __forceinline__ void consume_g1(float (&acc)[NT][2], uint32_t wbase, uint32_t sbase, int nc, int blk0,
                                            const XLayout& L, uint32_t xbase, int cols, int wi, int lane) {
   const int g = lane >> 2, t = lane & 3;
@@ -383,13 +421,17 @@ __device__ __forceinline__ void consume_g1(float (&acc)[NT][2], uint32_t wbase, 
   const uint32_t lo_off = L.zs;  // column + 1
 #pragma unroll 2
   for (int it = wi; it < nc; it += NW) {
-    const uint4 w = lds128(wbase + (uint32_t)it * 512u + (uint32_t)lane * 16u);
+    const WBlocks<Q8> wq = load_chunk<Q8>(wbase + (uint32_t)it * chunk_bytes<Q8>(), lane);
+    const uint4 w = wq.lo;
     const uint2 s2 = lds64(sbase + (uint32_t)it * 64u + (uint32_t)g * 8u);
     const float2 se = __half22float2(*reinterpret_cast<const __half2*>(&s2.x));
     const float2 so = __half22float2(*reinterpret_cast<const __half2*>(&s2.y));
     const uint32_t m = 0x0f0f0f0fu;
-    const uint32_t e0 = w.x & m, e1 = w.y & m, e2 = (w.x >> 4) & m, e3 = (w.y >> 4) & m;
-    const uint32_t o0 = w.z & m, o1 = w.w & m, o2 = (w.z >> 4) & m, o3 = (w.w >> 4) & m;
+    // the A registers of the even and of the odd block: unpacked once per chunk, used by every n-tile
+    const uint32_t e0 = Q8 ? wq.lo.x : w.x & m, e1 = Q8 ? wq.lo.y : w.y & m, e2 = Q8 ? wq.lo.z : (w.x >> 4) & m,
+                   e3 = Q8 ? wq.lo.w : (w.y >> 4) & m;
+    const uint32_t o0 = Q8 ? wq.hi.x : w.z & m, o1 = Q8 ? wq.hi.y : w.w & m, o2 = Q8 ? wq.hi.z : (w.z >> 4) & m,
+                   o3 = Q8 ? wq.hi.w : (w.w >> 4) & m;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const uint32_t zo = za[nt] + (uint32_t)it * 8u;
@@ -399,8 +441,14 @@ __device__ __forceinline__ void consume_g1(float (&acc)[NT][2], uint32_t wbase, 
       const uint2 bo = lds64(xa[nt] + (uint32_t)it * 64u + 32u);
       int de[4] = {(int)zh.x, (int)zl.x, (int)zh.x, (int)zl.x};
       int dd[4] = {(int)zh.y, (int)zl.y, (int)zh.y, (int)zl.y};
-      imma(de, e0, e1, e2, e3, be.x, be.y);
-      imma(dd, o0, o1, o2, o3, bo.x, bo.y);
+      if (Q8) {
+        de[0] = de[1] = de[2] = de[3] = dd[0] = dd[1] = dd[2] = dd[3] = (int)kBias;
+        imma_s8(de, e0, e1, e2, e3, be.x, be.y);
+        imma_s8(dd, o0, o1, o2, o3, bo.x, bo.y);
+      } else {
+        imma(de, e0, e1, e2, e3, be.x, be.y);
+        imma(dd, o0, o1, o2, o3, bo.x, bo.y);
+      }
       const float fe = __uint_as_float(fh.x), fo = __uint_as_float(fh.y);
       // 128 hi + lo, in units of 2^e / 128 ... fe already carries the 128: v = fe * (hi + lo / 128)
       const float ve0 = fmaf(unbias(de[1]), 0.0078125f, unbias(de[0])), ve1 = fmaf(unbias(de[3]), 0.0078125f, unbias(de[2]));

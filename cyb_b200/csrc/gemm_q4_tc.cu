@@ -327,6 +327,7 @@ __global__ void f32_to_bf16_kernel(const float* __restrict__ x, long long ldx, _
 // (a scratch of M*K*2 bytes owned by the context; grown outside the steady state).
 int32_t qeng_gemm_q4_prefill(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t x_dtype, int64_t M, int64_t ldx,
                              float* y, int64_t ldy, int accumulate, cudaStream_t stream) {
+  if (w && w->fmt != QENG_FMT_Q4) return qeng_fail(ctx, QENG_ERR_SHAPE, "gemm_q4_prefill: 4-bit blocks only");
   if (x_dtype == QENG_F16) return qeng_fail(ctx, QENG_ERR_SHAPE, "gemm_q4 (prefill): f16 activations are not supported, use f32 or bf16");
   const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
   long long ldb = ldx;

@@ -305,6 +305,9 @@ int32_t qeng_gemm_q4_decode(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
     int32_t rc = qeng_gemm_q4_stream(ctx, w, x, x_dtype, M, ldx, y, ldy, fuse, stream, &handled);
     if (handled || rc != QENG_OK) return rc;
   }
+  if (w->fmt != QENG_FMT_Q4)
+    return qeng_fail(ctx, QENG_ERR_SHAPE, "gemm_q4: this shape (M=%lld, N=%lld, K=%lld) is outside what the streaming kernel takes for 8-bit blocks",
+                     (long long)M, (long long)w->N, (long long)w->K);
   const int split = (x_dtype == QENG_F32 && split_f32) ? 1 : 0;
   const int max_m = split ? 16 : 32;
   if (M < 1 || M > max_m) return qeng_fail(ctx, QENG_ERR_SHAPE, "gemm_q4_decode: M=%lld outside 1..%d", (long long)M, max_m);
@@ -346,7 +349,7 @@ int32_t qeng_gemm_q4(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t
   if (M < 1) return qeng_fail(ctx, QENG_ERR_SHAPE, "gemm_q4: M=%lld", (long long)M);
   if (ldx < w->K || ldy < w->N) return qeng_fail(ctx, QENG_ERR_SHAPE, "gemm_q4: leading dimension smaller than the row");
   QENG_ENTER(ctx);
-  if (M >= kPrefillRows)  // dense contraction: dequantise to bf16 in shared memory, tcgen05 MMA
+  if (M >= kPrefillRows && w->fmt == QENG_FMT_Q4)  // dense contraction: dequantise to bf16 in shared memory, tcgen05 MMA
     return qeng_gemm_q4_prefill(ctx, w, x, x_dtype, M, ldx, y, ldy, (flags & QENG_GEMM_ACCUMULATE) ? 1 : 0, (cudaStream_t)stream);
   qeng_gemm_fuse fuse;
   fuse.epilogue = (flags & QENG_GEMM_ACCUMULATE) ? QENG_EPI_ACCUM : QENG_EPI_STORE;

@@ -23,11 +23,14 @@
 //    an m16n8k16 MMA over that chunk;
 //  * scale plane: [tile][chunk][g 0..7] one uint2 = four f16:
 //       (row g, blk 2c), (row g+8, blk 2c), (row g, blk 2c+1), (row g+8, blk 2c+1).
+enum { QENG_FMT_Q4 = 0, QENG_FMT_Q8 = 1 };
+
 struct qeng_weight {
+  int fmt = QENG_FMT_Q4;  // Q4: 4-bit codes, w = (c - 8) s; Q8: signed bytes, w = q s (both: one f16 s per 32-block)
   int64_t N, K;        // logical shape
   int64_t ntiles;      // N / 16
   int64_t nchunks;     // Kp / 64
-  uint4* qs;           // nibble plane, ntiles*nchunks*32 uint4
+  uint4* qs;           // weight plane: Q4 ntiles*nchunks*32 uint4 (nibbles), Q8 ntiles*nchunks*64 uint4 (bytes)
   uint2* sc;           // scale plane,  ntiles*nchunks*8 uint2
   int64_t bytes;       // device bytes held
   const qeng_weight* next = nullptr;  // matrix the caller multiplies by after this one (L2 prefetch hint)
@@ -218,6 +221,8 @@ int32_t qeng_tp_fuse_advance(qeng_ctx* ctx, cudaStream_t stream);
 int32_t qeng_gemm_q4_prefill(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t x_dtype, int64_t M, int64_t ldx,
                              float* y, int64_t ldy, int accumulate, cudaStream_t stream);
 constexpr int64_t kPrefillRows = 256;  // from this many rows on, matmuls take the tensor-core path
+
+void qeng_weight_dequant_q8(const qeng_weight* w, float* out, cudaStream_t stream);
 
 #if defined(QENG_TRACE) && defined(__CUDACC__)
 // tuning builds only: a launch log behind the status word (status + 256 bytes: a counter, then records

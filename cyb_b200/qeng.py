@@ -88,11 +88,15 @@ _sig("qeng_weight_pack_q4", _i32, _vp, _vp, _vp, _i64, _i64, C.POINTER(_vp))
 _sig("qeng_weight_unpack_q4", _i32, _vp, _vp, _vp, _vp)
 _sig("qeng_weight_dequant_f32", _i32, _vp, _vp, _vp, _vp)
 _sig("qeng_weight_quantize_q4", _i32, _vp, _vp, _i32, _i64, _i64, _i64, C.POINTER(_vp), _vp)
+_sig("qeng_weight_pack_q8", _i32, _vp, _vp, _vp, _i64, _i64, C.POINTER(_vp))
+_sig("qeng_weight_unpack_q8", _i32, _vp, _vp, _vp, _vp)
+_sig("qeng_weight_quantize_q8", _i32, _vp, _vp, _i32, _i64, _i64, _i64, C.POINTER(_vp), _vp)
 _sig("qeng_weight_free", _i32, _vp, _vp)
 _sig("qeng_weight_set_next", _i32, _vp, _vp, _vp)
 _sig("qeng_weight_rows", _i64, _vp)
 _sig("qeng_weight_cols", _i64, _vp)
 _sig("qeng_weight_device_bytes", _i64, _vp)
+_sig("qeng_weight_format", _i32, _vp)
 _sig("qeng_gemm_q4", _i32, _vp, _vp, _vp, _i32, _i64, _i64, _vp, _i64, _i32, _vp)
 _sig("qeng_gemv_q4", _i32, _vp, _vp, _vp, _vp, _vp)
 _sig("qeng_rmsnorm", _i32, _vp, _vp, _vp, _i64, _i64, _f32, _vp, _vp)
@@ -113,6 +117,7 @@ _sig("qeng_attn_decode_noalloc", _i32, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64
 _sig("qeng_decoder_create", _i32, _vp, C.POINTER(ModelCfg), C.POINTER(_vp))
 _sig("qeng_decoder_free", _i32, _vp, _vp)
 _sig("qeng_decoder_load_matrix", _i32, _vp, _vp, _i32, _i32, _vp, _vp, _i64, _i64)
+_sig("qeng_decoder_load_matrix_q8", _i32, _vp, _vp, _i32, _i32, _vp, _vp, _i64, _i64)
 _sig("qeng_decoder_load_norm", _i32, _vp, _vp, _i32, _i32, _vp)
 _sig("qeng_decoder_load_head", _i32, _vp, _vp, _vp, _vp, _vp)
 _sig("qeng_decoder_reset", _i32, _vp, _vp, _i32)
@@ -225,6 +230,27 @@ class Context:
         h = _vp()
         self.check(_lib.qeng_weight_pack_q4(self.h, _np_ptr(q), _np_ptr(s), n, k, C.byref(h)))
         return Weight(self, h)
+
+    def pack_q8(self, q, s):
+        """q int8 [N,K] signed bytes, s float16 [N,K/32] (host numpy): w = q * s."""
+        q = np.ascontiguousarray(q, dtype=np.int8)
+        s = np.ascontiguousarray(s, dtype=np.float16)
+        n, k = q.shape
+        if s.shape != (n, k // 32):
+            raise QengError(-2, "scale shape %s does not match bytes %s" % (s.shape, q.shape))
+        h = _vp()
+        self.check(_lib.qeng_weight_pack_q8(self.h, _np_ptr(q), _np_ptr(s), n, k, C.byref(h)))
+        return Weight(self, h, q8=True)
+
+    def quantize_q8(self, w):
+        """Quantise a CUDA matrix [N,K] (float32 / float16 / bfloat16) into packed 8-bit blocks on the device."""
+        import torch
+        dt = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}[w.dtype]
+        assert w.is_cuda and w.dim() == 2 and w.stride(1) == 1
+        h = _vp()
+        self.check(_lib.qeng_weight_quantize_q8(self.h, _dev_ptr(w), dt, w.shape[0], w.shape[1], w.stride(0),
+                                                C.byref(h), _cur_stream()))
+        return Weight(self, h, q8=True)
 
     def quantize_q4(self, w):
         """Quantise a CUDA matrix [N,K] (float32 / float16 / bfloat16) into a packed weight on the device."""
@@ -347,16 +373,18 @@ class Context:
 
 
 class Weight:
-    def __init__(self, ctx, h):
+    def __init__(self, ctx, h, q8=None):
         self.ctx, self.h = ctx, h
+        self.q8 = _lib.qeng_weight_format(h) == 8
         self.rows = _lib.qeng_weight_rows(h)
         self.cols = _lib.qeng_weight_cols(h)
         self.device_bytes = _lib.qeng_weight_device_bytes(h)
 
     def unpack(self):
-        q = np.empty((self.rows, self.cols), np.uint8)
+        q = np.empty((self.rows, self.cols), np.int8 if self.q8 else np.uint8)
         s = np.empty((self.rows, self.cols // 32), np.float16)
-        self.ctx.check(_lib.qeng_weight_unpack_q4(self.ctx.h, self.h, _np_ptr(q), _np_ptr(s)))
+        fn = _lib.qeng_weight_unpack_q8 if self.q8 else _lib.qeng_weight_unpack_q4
+        self.ctx.check(fn(self.ctx.h, self.h, _np_ptr(q), _np_ptr(s)))
         return q, s
 
     def dequant(self):
@@ -425,10 +453,12 @@ class Decoder:
         self.batch = 0
 
     def load_matrix(self, layer, which, q, s):
-        q = np.ascontiguousarray(q, dtype=np.uint8)
+        """q uint8 codes 0..15 (4-bit blocks) or int8 bytes (8-bit blocks), s float16 scales."""
+        q8 = np.asarray(q).dtype == np.int8
+        q = np.ascontiguousarray(q, dtype=np.int8 if q8 else np.uint8)
         s = np.ascontiguousarray(s, dtype=np.float16)
-        self.ctx.check(_lib.qeng_decoder_load_matrix(self.ctx.h, self.h, layer, which, _np_ptr(q), _np_ptr(s),
-                                                     q.shape[0], q.shape[1]))
+        fn = _lib.qeng_decoder_load_matrix_q8 if q8 else _lib.qeng_decoder_load_matrix
+        self.ctx.check(fn(self.ctx.h, self.h, layer, which, _np_ptr(q), _np_ptr(s), q.shape[0], q.shape[1]))
 
     def load_file(self, path):
         """Load all weights from a `.model` container (qeng_decoder_load_file)."""
@@ -478,6 +508,7 @@ class Decoder:
         w.ctx, w.h = self.ctx, h
         w.rows, w.cols = _lib.qeng_weight_rows(h), _lib.qeng_weight_cols(h)
         w.device_bytes = _lib.qeng_weight_device_bytes(h)
+        w.q8 = _lib.qeng_weight_format(h) == 8
         w.free = lambda: None  # borrowed
         return w
 

@@ -135,10 +135,25 @@ int32_t qeng_weight_dequant_f32(qeng_ctx* ctx, const qeng_weight* w, float* out,
  * released once the stream has passed this call.  K % 32 == 0, N % 16 == 0. */
 int32_t qeng_weight_quantize_q4(qeng_ctx* ctx, const void* w_dev, int32_t x_dtype, int64_t N, int64_t K, int64_t ld,
                                 qeng_weight** out, void* stream);
+/* ---- 8-bit block weights ("tensor data (Q4/Q8/F16/F32)", decide/pipeline.md:28; the default
+ *      model of the reference's catalog was imported as q8, shell/src/worlds/models/mod.rs:68-73)
+ * w = q * s with q a signed byte and one f16 scale per 32 consecutive K (the published Q8_0 block).
+ * A weight handle of this format is taken by qeng_gemm_q4 / qeng_gemv_q4 (any M: rows in passes of
+ * 16 through the decode kernel; the tensor-core prefill kernel is for 4-bit blocks only),
+ * qeng_weight_dequant_f32, qeng_weight_set_next and the getters.  Same shape rules as the 4-bit calls. */
+int32_t qeng_weight_pack_q8(qeng_ctx* ctx, const int8_t* q, const uint16_t* s, int64_t N, int64_t K, qeng_weight** out);
+/* Inverse, computed ON THE DEVICE from the packed layout: N*K bytes and N*K/32 scales to HOST buffers. */
+int32_t qeng_weight_unpack_q8(qeng_ctx* ctx, const qeng_weight* w, int8_t* q, uint16_t* s);
+/* Import-time quantiser on the device: per 32-block d = max|x| / 127 in f32 (stored as f16),
+ * q = round-half-away(x * (1/d)).  Asynchronous on `stream`. */
+int32_t qeng_weight_quantize_q8(qeng_ctx* ctx, const void* w_dev, int32_t x_dtype, int64_t N, int64_t K, int64_t ld,
+                                qeng_weight** out, void* stream);
 int32_t qeng_weight_free(qeng_ctx* ctx, qeng_weight* w);
 int64_t qeng_weight_rows(const qeng_weight* w);
 int64_t qeng_weight_cols(const qeng_weight* w);
 int64_t qeng_weight_device_bytes(const qeng_weight* w);
+/* Bits per weight of the block format held: 4 or 8. */
+int32_t qeng_weight_format(const qeng_weight* w);
 /* Hint: the matmul the caller runs after one over `w` is over `next` (NULL clears the hint).
  * The decode kernel then asks L2 for `next` while it finishes `w`, so that HBM keeps
  * streaming across the kernel boundary.  Results never depend on the hint.  `next` must stay
@@ -252,6 +267,11 @@ int32_t qeng_decoder_free(qeng_ctx* ctx, qeng_decoder* dec);
  * (unsharded) matrix [N,K]; the decoder keeps this rank's shard only. */
 int32_t qeng_decoder_load_matrix(qeng_ctx* ctx, qeng_decoder* dec, int32_t layer, int32_t which,
                                  const uint8_t* q, const uint16_t* s, int64_t N, int64_t K);
+/* The same for 8-bit blocks (q: one signed byte per weight).  The matrices that the executor fuses
+ * (q, k, v of a layer; gate, up of a layer) must come in one format; prompts of layers with 8-bit
+ * blocks run through the decode kernels in passes of 16 rows. */
+int32_t qeng_decoder_load_matrix_q8(qeng_ctx* ctx, qeng_decoder* dec, int32_t layer, int32_t which,
+                                    const int8_t* q, const uint16_t* s, int64_t N, int64_t K);
 /* RMSNorm gains of a layer (which = 0: before attention, 1: before FFN), HOST f32[d_model].
  * which = 2 / 3: optional per-head gains of q / k, HOST f32[head_dim] ("QK-norm", named as a
  * blocker for the catalog's Qwen3 models in decide/model-lifecycle.md:173-176): every q and k head

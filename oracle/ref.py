@@ -79,10 +79,42 @@ def config2(index, m, n, k):
 # --------------------------------------------------------------------------
 # block format
 # --------------------------------------------------------------------------
+def centred(q):
+    """The integer a weight stands for: code - 8 for 4-bit blocks (uint8 codes), the byte itself for
+    8-bit blocks (int8)."""
+    q = np.asarray(q)
+    return q.astype(np.int32) if q.dtype == np.int8 else q.astype(np.int32) - ZERO_POINT
+
+
 def dequant(q, s, dtype=np.float64):
-    """w = (q-8)*s, exact in f32 and f64."""
-    w = q.astype(np.int32) - ZERO_POINT
-    return w.astype(dtype) * np.repeat(s.astype(dtype), BLOCK, axis=1)
+    """w = (q-8)*s for 4-bit codes (uint8), w = q*s for 8-bit blocks (int8); exact in f32 and f64."""
+    return centred(q).astype(dtype) * np.repeat(s.astype(dtype), BLOCK, axis=1)
+
+
+def quantize_q8(w):
+    """Import-time quantiser to 8-bit blocks ("tensor data (Q4/Q8/F16/F32)", decide/pipeline.md:28), the
+    published Q8_0 rule, all in float32: per 32-block d = max|x| / 127, scale = f16(d),
+    q = round-half-away-from-zero(x * (1/d)) (1/d = 0 when d = 0).  Integer outputs: the device
+    quantiser must match bit for bit."""
+    w = np.asarray(w, dtype=np.float32)
+    n, k = w.shape
+    assert k % BLOCK == 0
+    b = w.reshape(n, k // BLOCK, BLOCK)
+    d = (np.abs(b).max(axis=2) / np.float32(127.0)).astype(np.float32)
+    with np.errstate(divide="ignore"):
+        inv = np.where(d != 0, np.float32(1.0) / d, np.float32(0.0)).astype(np.float32)
+    v = (b * inv[..., None]).astype(np.float32)
+    t = np.trunc(v)
+    q = t + np.where(np.abs(v - t) >= np.float32(0.5), np.sign(v), np.float32(0.0))  # roundf
+    return q.astype(np.int8).reshape(n, k), d.astype(np.float16)
+
+
+def make_q8(rng, n, k):
+    """Synthetic 8-bit block weights: bytes uniform in -127..127, scales like make_q4's / 16 (so that
+    the dequantised magnitudes match the 4-bit matrices')."""
+    q = rng.integers(-127, 128, (n, k), dtype=np.int8)
+    s = (rng.uniform(0.002, 0.02, (n, k // BLOCK)) / 16.0).astype(np.float16)
+    return q, s
 
 
 def quantize_q4(w):
@@ -117,7 +149,7 @@ def gemm_q4(x, q, s):
     n = q.shape[0]
     nb = k // BLOCK
     xi = x.astype(np.float64).reshape(m, nb, BLOCK)
-    qi = (q.astype(np.int32) - ZERO_POINT).astype(np.float64).reshape(n, nb, BLOCK)
+    qi = centred(q).astype(np.float64).reshape(n, nb, BLOCK)
     # block partial sums then scale; chunk n to bound memory
     y = np.empty((m, n), np.float64)
     step = max(1, (1 << 24) // (nb * BLOCK * max(m, 1)))
@@ -262,9 +294,9 @@ class DecoderConfig:
         return (self.heads + 2 * self.kv_heads) * self.hd
 
 
-def make_decoder_weights(cfg, seed=5):
-    """All linear weights as 4-bit blocks (independent streams per matrix);
-    embeddings and lm_head bf16 ~N(0,0.02); RMSNorm gains 1."""
+def make_decoder_weights(cfg, seed=5, fmt="q4"):
+    """All linear weights as 4-bit blocks (or 8-bit blocks with fmt="q8"; independent streams per
+    matrix); embeddings and lm_head bf16 ~N(0,0.02); RMSNorm gains 1."""
     ss = np.random.SeedSequence(seed)
     kids = ss.spawn(2 + 7 * cfg.layers)
     g = lambda i: np.random.Generator(np.random.PCG64(kids[i]))
@@ -277,7 +309,7 @@ def make_decoder_weights(cfg, seed=5):
     for l in range(cfg.layers):
         lw = {"norm1": np.ones(cfg.d, np.float32), "norm2": np.ones(cfg.d, np.float32)}
         for j, (name, n, k) in enumerate(shapes):
-            lw[name] = make_q4(g(2 + 7 * l + j), n, k)
+            lw[name] = (make_q8 if fmt == "q8" else make_q4)(g(2 + 7 * l + j), n, k)
         W["layers"].append(lw)
     return W
 

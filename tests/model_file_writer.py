@@ -19,6 +19,15 @@ def q4_blocks(q, s):
     return out.tobytes()
 
 
+def q8_blocks(q, s):
+    """bytes [N,K] int8 + f16 scales [N,K/32] -> row-major 34-byte blocks (scale, then the 32 bytes)."""
+    n, k = q.shape
+    out = np.empty((n * k // 32, 34), np.uint8)
+    out[:, :2] = np.ascontiguousarray(s, np.float16).reshape(-1, 1).view(np.uint8)
+    out[:, 2:] = np.ascontiguousarray(q, np.int8).reshape(-1, 32).view(np.uint8)
+    return out.tobytes()
+
+
 def bf16_bits(x):
     u = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
     return (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) & 0xFFFF).astype(np.uint16)
@@ -38,7 +47,9 @@ def write_model(path, cfg, W, linear_dtype="Q4", tie_head=False, name="sample"):
         off += len(data)
 
     def linear(tname, q, s):
-        if linear_dtype == "Q4":
+        if np.asarray(q).dtype == np.int8:  # 8-bit blocks are stored as they are
+            add(tname, "Q8", list(q.shape), q8_blocks(q, s))
+        elif linear_dtype == "Q4":
             add(tname, "Q4", list(q.shape), q4_blocks(q, s))
         else:
             w = ref.dequant(q, s, np.float32)

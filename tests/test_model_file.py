@@ -51,16 +51,16 @@ def test_malformed_containers_are_rejected(built_lib, tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("linear_dtype,tie", [("Q4", False), ("F32", False), ("F16", True)])
+@pytest.mark.parametrize("linear_dtype,tie", [("Q4", False), ("F32", False), ("F16", True), ("Q8", False)])
 def test_decoder_loaded_from_a_file_equals_one_loaded_from_arrays(ctx, tmp_path, linear_dtype, tie):
     from cyb_b200 import qeng
     cfg = ref.DecoderConfig(**CFG)
-    W = ref.make_decoder_weights(cfg, seed=5)
+    W = ref.make_decoder_weights(cfg, seed=5, fmt="q8" if linear_dtype == "Q8" else "q4")
     if tie:
         W["lm_head"] = W["emb"]
     path = os.path.join(tmp_path, "toy.model")
     mfw.write_model(path, cfg, W, linear_dtype=linear_dtype, tie_head=tie)
-    if linear_dtype != "Q4":
+    if linear_dtype not in ("Q4", "Q8"):
         # float weights are quantised at load: what the decoder must then hold is the oracle's
         # quantisation of the stored (rounded) matrix, not the codes the file was made from
         W = dict(W, layers=[dict(lw) for lw in W["layers"]])

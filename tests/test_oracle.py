@@ -163,3 +163,26 @@ def test_quantizer_matches_the_gguf_package_if_present():
     assert np.array_equal(d.view(np.uint16), s.view(np.uint16))
     assert np.array_equal(codes, q)
     assert np.allclose(quants.dequantize(b.reshape(n, -1), gguf.GGMLQuantizationType.Q4_0), ref.dequant(q, s, np.float32))
+
+
+def test_q8_quantizer_known_answers_and_gguf_pin():
+    """8-bit blocks: d = max|x| / 127, q = round-half-away(x / d); w = q * s.  Where the third-party
+    `gguf` package is present its Q8_0 (34-byte blocks: f16 scale, 32 signed bytes) must give the same
+    bytes and scale bits."""
+    x = _quantizer_cases()
+    q, s = ref.quantize_q8(x)
+    assert q.dtype == np.int8 and q.min() >= -127 and q.max() <= 127
+    b = x.reshape(x.shape[0], -1, 32)
+    amax = np.abs(b).max(2)
+    assert np.array_equal(np.abs(q.reshape(b.shape)).max(2)[amax > 0], np.full((amax > 0).sum(), 127))
+    assert np.all(q.reshape(b.shape)[amax == 0] == 0) and np.all(s[amax == 0] == 0)
+    w = ref.dequant(q, s, np.float32)
+    assert np.all(np.abs(w - x).reshape(b.shape) <= (amax / 127 * 0.51 + np.abs(amax) * 2e-3)[..., None])
+    assert np.array_equal(ref.gemm_q4(x[:2], q, s), ref.gemm_q4(x[:2], q, s))
+    assert np.allclose(ref.gemm_q4(x[:3], q, s), ref.gemm_q4_fast(x[:3], q, s), rtol=1e-12, atol=1e-9)
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    g = quants.quantize(x, gguf.GGMLQuantizationType.Q8_0).reshape(x.shape[0], -1, 34)
+    assert np.array_equal(g[..., :2].copy().view(np.uint16)[..., 0], s.view(np.uint16))
+    assert np.array_equal(g[..., 2:].copy().view(np.int8).reshape(q.shape), q)
+
