@@ -296,12 +296,13 @@ def kernel_legs(ctx, torch, peaks):
     out = []
     L2 = 160e6  # a pool at least this large never fits the 126 MB L2
 
-    def wpool(n, k, count):
-        return [ctx.quantize_q4(torch.randn(n, k, device="cuda") * 0.05) for _ in range(count)]
+    def wpool(n, k, count, q8=False):
+        quant = ctx.quantize_q8 if q8 else ctx.quantize_q4
+        return [quant(torch.randn(n, k, device="cuda") * 0.05) for _ in range(count)]
 
-    def gemm_leg(name, m, n, k, dt):
-        wb = n * k * 0.5625
-        ws = wpool(n, k, max(2, int(L2 // wb) + 1))
+    def gemm_leg(name, m, n, k, dt, q8=False):
+        wb = n * k * (1.0625 if q8 else 0.5625)
+        ws = wpool(n, k, max(2, int(L2 // wb) + 1), q8)
         x = torch.randn(m, k, device="cuda").to(dt)
         y = torch.empty(m, n, device="cuda")
         us = _time_graph(torch, [lambda w=w: ctx.gemm_q4(w, x, out=y) for w in ws])
@@ -316,6 +317,9 @@ def kernel_legs(ctx, torch, peaks):
     for (n, k) in [(4096, 4096), (11008, 4096), (4096, 11008)]:
         for m in (1, 8, 32):
             gemm_leg("configs[1] decode-batch gemm", m, n, k, torch.bfloat16)
+    # 8-bit blocks ("tensor data (Q4/Q8/F16/F32)"): the same kernel on signed bytes, 1.0625 B per weight
+    for (n, k) in [(4096, 4096), (11008, 4096)]:
+        gemm_leg("8-bit blocks, decode gemv", 1, n, k, torch.float32, q8=True)
     # prefill: tensor-bound
     for (n, k) in [(11008, 4096), (4096, 11008)]:
         w0 = wpool(n, k, 1)[0]

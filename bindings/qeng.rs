@@ -85,6 +85,7 @@ pub struct qeng_model_cfg {
     pub tp_world: i32,
     pub attn_softcap: f32,
     pub sliding_window: i32,
+    pub final_softcap: f32,
 }
 
 #[link(name = "qeng")]

@@ -447,7 +447,7 @@ int32_t tail_sharded(qeng_ctx* ctx, qeng_decoder* d, const float* x_last, int B,
     qeng_lm_tail t;
     t.table = d->lm_head; t.x = x_last + (size_t)m0 * dm; t.M = B - m0 < 4 ? B - m0 : 4; t.D = dm; t.V = d->vloc;
     t.logits = d->logits + (size_t)m0 * V; t.v0 = d->v0; t.Vtot = V; t.ldl = V;
-    t.gamma = d->final_norm; t.eps = d->cfg.rms_eps;
+    t.gamma = d->final_norm; t.eps = d->cfg.rms_eps; t.softcap = d->cfg.final_softcap;
     if (finalize) { t.pairs = d->tp_pairs; t.pair_slot = R * B + m0; }
     d->launches += 1;
     int32_t rc = qeng_lm_head_fused(ctx, t, st);
@@ -480,7 +480,7 @@ int32_t tail(qeng_ctx* ctx, qeng_decoder* d, const float* x_last, int B, bool fi
   if (B <= 4) {
     qeng_lm_tail t;
     t.table = d->lm_head; t.x = x_last; t.M = B; t.D = d->cfg.d_model; t.V = d->cfg.vocab; t.logits = d->logits;
-    t.gamma = d->final_norm; t.eps = d->cfg.rms_eps;
+    t.gamma = d->final_norm; t.eps = d->cfg.rms_eps; t.softcap = d->cfg.final_softcap;
     if (finalize) {
       t.next = d->next; t.emb = d->emb; t.xout = d->x; t.pos = d->pos; t.lens = d->lens;
       t.out_tokens = d->out_tokens; t.step = d->step;
@@ -490,8 +490,14 @@ int32_t tail(qeng_ctx* ctx, qeng_decoder* d, const float* x_last, int B, bool fi
   }
   int32_t rc = qeng_rmsnorm(ctx, x_last, d->final_norm, B, d->cfg.d_model, d->cfg.rms_eps, d->xn, st);
   if (rc != QENG_OK) return rc;
-  rc = qeng_lm_head(ctx, d->lm_head, d->xn, B, d->cfg.d_model, d->cfg.vocab, d->logits, st);
-  if (rc != QENG_OK) return rc;
+  for (int m0 = 0; m0 < B; m0 += 4) {  // the LM head takes 4 rows per launch
+    qeng_lm_tail t;
+    t.table = d->lm_head; t.x = d->xn + (size_t)m0 * d->cfg.d_model; t.M = B - m0 < 4 ? B - m0 : 4;
+    t.D = d->cfg.d_model; t.V = d->cfg.vocab; t.logits = d->logits + (size_t)m0 * d->cfg.vocab;
+    t.softcap = d->cfg.final_softcap;
+    rc = qeng_lm_head_fused(ctx, t, st);
+    if (rc != QENG_OK) return rc;
+  }
   d->launches += 1 + (B + 3) / 4;
   if (!finalize) return QENG_OK;
   rc = qeng_argmax(ctx, d->logits, B, d->cfg.vocab, d->next, st);
@@ -576,7 +582,8 @@ int32_t qeng_decoder_create(qeng_ctx* ctx, const qeng_model_cfg* cfg, qeng_decod
   if (cfg->kv_heads % t != 0 || cfg->ffn % (16 * t) != 0 || cfg->d_model % 32 != 0 || (cfg->ffn / t) % 32 != 0 ||
       (cfg->heads * kHD / t) % 32 != 0)
     return qeng_fail(ctx, QENG_ERR_SHAPE, "decoder_create: shapes do not shard evenly over %d ranks", t);
-  if (cfg->attn_softcap < 0.f || cfg->sliding_window < 0) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_create: attn_softcap and sliding_window must not be negative");
+  if (cfg->attn_softcap < 0.f || cfg->sliding_window < 0 || cfg->final_softcap < 0.f)
+    return qeng_fail(ctx, QENG_ERR_ARG, "decoder_create: attn_softcap, final_softcap and sliding_window must not be negative");
   if (cfg->max_batch < 1 || cfg->max_batch > 16 || cfg->max_seq < 1)
     return qeng_fail(ctx, QENG_ERR_SHAPE, "decoder_create: max_batch must be 1..16 and max_seq positive");
   if (t > 1 && (ctx->tp_world != t || ctx->tp_rank != cfg->tp_rank))

@@ -10,7 +10,7 @@
 //
 //   ~~~config    TOML: hidden_size, intermediate_size, num_hidden_layers, num_attention_heads,
 //                num_key_value_heads, head_dim, vocab_size, rms_norm_eps, rope_theta; optional
-//                attn_logit_softcapping, sliding_window
+//                attn_logit_softcapping, sliding_window, final_logit_softcapping
 //   ~~~tensors   TOML array of tables [[tensor]]: name, dtype ("Q4" | "Q8" | "F32" | "F16" | "BF16"),
 //                shape = [rows, cols] (or [n]), offset and size in bytes inside `weights`
 //   ~~~weights   binary.  Q4 = row-major 32-blocks of 18 bytes: f16 scale, then 16 bytes holding the
@@ -308,6 +308,7 @@ bool model_cfg(ModelFile& m, qeng_model_cfg* c) {
   if (!cfg_float(m, "rope_theta", &c->rope_base)) c->rope_base = 10000.f;
   if (!cfg_float(m, "attn_logit_softcapping", &c->attn_softcap)) c->attn_softcap = 0.f;
   c->sliding_window = cfg_int(m, "sliding_window", &v) && v > 0 && v <= INT32_MAX ? (int32_t)v : 0;
+  if (!cfg_float(m, "final_logit_softcapping", &c->final_softcap)) c->final_softcap = 0.f;
   c->max_batch = 1;
   c->max_seq = 0;
   c->tp_rank = 0;
@@ -363,7 +364,7 @@ int32_t qeng_decoder_load_file(qeng_ctx* ctx, qeng_decoder* dec, const char* pat
   int32_t rc = qeng_decoder_config(ctx, dec, &dc);
   if (rc != QENG_OK) return rc;
   if (fc.layers != dc.layers || fc.d_model != dc.d_model || fc.ffn != dc.ffn || fc.heads != dc.heads ||
-      fc.kv_heads != dc.kv_heads || fc.head_dim != dc.head_dim || fc.vocab != dc.vocab || fc.attn_softcap != dc.attn_softcap ||
+      fc.kv_heads != dc.kv_heads || fc.head_dim != dc.head_dim || fc.vocab != dc.vocab || fc.attn_softcap != dc.attn_softcap || fc.final_softcap != dc.final_softcap ||
       fc.sliding_window != dc.sliding_window)
     return qeng_fail(ctx, QENG_ERR_SHAPE, "model file %s: its config (layers %d, d %d, ffn %d, heads %d/%d, head_dim %d, vocab %d) differs from the decoder's",
                      path, fc.layers, fc.d_model, fc.ffn, fc.heads, fc.kv_heads, fc.head_dim, fc.vocab);

@@ -159,7 +159,7 @@ __global__ void __launch_bounds__(256) lm_head_kernel(const qeng_lm_tail t, floa
     for (int m = 0; m < kLmM; ++m) {
       if (m < M) {
         const float tot = warp_sum(acc[m]);
-        if (lane == 0) t.logits[(size_t)m * ldl + v0 + v] = tot;
+        if (lane == 0) t.logits[(size_t)m * ldl + v0 + v] = t.softcap > 0.f ? t.softcap * tanhf(tot / t.softcap) : tot;
         if (better(tot, v0 + v, bestv[m], besti[m])) { bestv[m] = tot; besti[m] = v0 + v; }
       }
     }

@@ -175,6 +175,8 @@ struct qeng_lm_tail {
   int v0 = 0, Vtot = 0, ldl = 0;    // Vtot = 0 means unsharded (Vtot = ldl = V)
   float* pairs = nullptr;           // instead of finalising: pairs[2 * (pair_slot + m)] = (max, index as f32)
   int pair_slot = 0;
+  float softcap = 0.f;              // > 0: the logits written are softcap * tanh(logit / softcap); the
+                                    // sampling compares the raw values (the map is monotonic)
 };
 int32_t qeng_lm_head_fused(qeng_ctx* ctx, const qeng_lm_tail& t, cudaStream_t stream);
 

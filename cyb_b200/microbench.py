@@ -29,9 +29,10 @@ def gemv(args):
     opts = {k: v for k, v in (("stream_groups", args.groups), ("stream_stage_chunks", args.stage_chunks)) if v}
     ctx = qeng.Context(0, **opts)
     n, k, m = args.n, args.k, args.m
-    wbytes = n * k * 0.5625
+    wbytes = n * k * (1.0625 if args.q8 else 0.5625)
     pool = args.pool or max(2, int(160e6 // wbytes) + 1)
-    ws = [ctx.quantize_q4(torch.randn(n, k, device="cuda") * 0.05) for _ in range(pool)]  # timing only: any weights do
+    quant = ctx.quantize_q8 if args.q8 else ctx.quantize_q4
+    ws = [quant(torch.randn(n, k, device="cuda") * 0.05) for _ in range(pool)]  # timing only: any weights do
     dt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[args.dtype]
     x = torch.randn(m, k, device="cuda").to(dt)
     y = torch.empty(m, n, device="cuda")
@@ -224,6 +225,7 @@ def main(argv=None):
     g.add_argument("--iters", type=int, default=20)
     g.add_argument("--flags", type=int, default=0)
     g.add_argument("--groups", type=int, default=0, help="tile groups of the streaming kernel (1, 2, 4; 0 = by shape)")
+    g.add_argument("--q8", action="store_true", help="8-bit blocks instead of 4-bit")
     g.add_argument("--stage-chunks", type=int, default=0, help="K chunks per ring stage (0 = default)")
     a = sub.add_parser("attn")
     a.add_argument("--batch", type=int, default=16)

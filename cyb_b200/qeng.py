@@ -60,7 +60,7 @@ class ModelCfg(C.Structure):
     _fields_ = [("layers", _i32), ("d_model", _i32), ("ffn", _i32), ("heads", _i32), ("kv_heads", _i32),
                 ("head_dim", _i32), ("vocab", _i32), ("rms_eps", _f32), ("rope_base", _f32),
                 ("max_batch", _i32), ("max_seq", _i32), ("tp_rank", _i32), ("tp_world", _i32),
-                ("attn_softcap", _f32), ("sliding_window", _i32)]
+                ("attn_softcap", _f32), ("sliding_window", _i32), ("final_softcap", _f32)]
 
 
 def _sig(name, res, *args):
@@ -443,10 +443,11 @@ class Decoder:
     """The layer executor behind the C ABI (qeng_decoder_*)."""
 
     def __init__(self, ctx, layers, d_model, ffn, heads, kv_heads, vocab, head_dim=128, rms_eps=1e-5,
-                 rope_base=10000.0, max_batch=1, max_seq=1024, tp_rank=0, tp_world=1, attn_softcap=0.0, sliding_window=0):
+                 rope_base=10000.0, max_batch=1, max_seq=1024, tp_rank=0, tp_world=1, attn_softcap=0.0, sliding_window=0,
+                 final_softcap=0.0):
         self.ctx = ctx
         self.cfg = ModelCfg(layers, d_model, ffn, heads, kv_heads, head_dim, vocab, rms_eps, rope_base, max_batch,
-                            max_seq, tp_rank, tp_world, attn_softcap, sliding_window)
+                            max_seq, tp_rank, tp_world, attn_softcap, sliding_window, final_softcap)
         h = _vp()
         ctx.check(_lib.qeng_decoder_create(ctx.h, C.byref(self.cfg), C.byref(h)))
         self.h = h

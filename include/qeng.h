@@ -256,6 +256,8 @@ typedef struct qeng_model_cfg {
   int32_t tp_rank, tp_world; /* tensor-parallel position of this context */
   float attn_softcap;        /* > 0: attention logits are soft-capped, softcap * tanh(logit / softcap) */
   int32_t sliding_window;    /* > 0: every layer attends only the last `sliding_window` tokens */
+  float final_softcap;       /* > 0: the logits returned are final_softcap * tanh(logit / final_softcap) (Gemma);
+                                greedy sampling is unchanged (the map is monotonic) */
 } qeng_model_cfg;
 
 /* matrices of one layer, in the order of the decode loop */
@@ -301,7 +303,11 @@ int32_t qeng_decoder_load_file(qeng_ctx* ctx, qeng_decoder* dec, const char* pat
 /* Forget all sequences (KV lengths to zero). */
 int32_t qeng_decoder_reset(qeng_ctx* ctx, qeng_decoder* dec, int32_t batch);
 /* Prompt phase: tokens HOST int32 [batch, T]; fills the KV cache and leaves the
- * logits of the last prompt position.  Synchronous. */
+ * logits of the last prompt position.  Synchronous.  batch * T rows are processed at once (buffers
+ * grow to that size on first use: about 150 KB per row at the 7B shape); from 256 rows on, layers of
+ * 4-bit blocks take the tensor-core matmul.  Attention runs the decode kernel over the prompt rows in
+ * launches of 2048 rows, so its KV traffic grows with T^2; feed long prompts in chunks (successive
+ * calls append) to bound memory and to report progress. */
 int32_t qeng_decoder_prefill(qeng_ctx* ctx, qeng_decoder* dec, const int32_t* tokens, int32_t batch, int32_t T);
 /* Greedy decode: runs `steps` steps; each step samples from the current logits,
  * feeds the sampled token and computes the next logits.  Writes the sampled

@@ -283,11 +283,11 @@ def config4(seed=4, B=16, Hq=32, Hkv=8, hd=128, lo=512, hi=4096, page=16):
 # --------------------------------------------------------------------------
 class DecoderConfig:
     def __init__(self, layers=32, d=4096, ffn=11008, heads=32, kv_heads=8, hd=128,
-                 vocab=32000, eps=1e-5, rope_base=10000.0, attn_softcap=0.0, sliding_window=0):
+                 vocab=32000, eps=1e-5, rope_base=10000.0, attn_softcap=0.0, sliding_window=0, final_softcap=0.0):
         self.layers, self.d, self.ffn = layers, d, ffn
         self.heads, self.kv_heads, self.hd = heads, kv_heads, hd
         self.vocab, self.eps, self.rope_base = vocab, eps, rope_base
-        self.attn_softcap, self.sliding_window = attn_softcap, sliding_window
+        self.attn_softcap, self.sliding_window, self.final_softcap = attn_softcap, sliding_window, final_softcap
 
     @property
     def qkv_rows(self):
@@ -366,7 +366,10 @@ class Decoder:
         for l in range(self.cfg.layers):
             x = self.layer(l, x, pos, trace)
         xn = rmsnorm(x[:, -1], self.W["final_norm"], self.cfg.eps)
-        return xn @ self.W["lm_head"].astype(np.float64).T
+        logits = xn @ self.W["lm_head"].astype(np.float64).T
+        if self.cfg.final_softcap > 0:
+            logits = self.cfg.final_softcap * np.tanh(logits / self.cfg.final_softcap)
+        return logits
 
     def generate(self, prompt, steps):
         """prompt [B,P] -> (tokens [B,steps], logits per step list)."""

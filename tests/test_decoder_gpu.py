@@ -307,19 +307,21 @@ def test_fused_step_kernel_matches_the_teacher(built_lib, batch):
 
 
 def test_softcap_and_sliding_window_decoder(ctx):
-    """A decoder with soft-capped attention logits and a sliding window of 8 tokens (the Gemma-family
-    deltas): prompt logits and greedy tokens against the float64 teacher with the same switches."""
+    """A decoder with soft-capped attention logits, a sliding window of 8 tokens and soft-capped final
+    logits (the Gemma-family deltas): prompt logits and greedy tokens against the float64 teacher with
+    the same switches."""
     from cyb_b200 import qeng
-    cfg = ref.DecoderConfig(**CFG, attn_softcap=20.0, sliding_window=8)
+    cfg = ref.DecoderConfig(**CFG, attn_softcap=20.0, sliding_window=8, final_softcap=3.0)
     W = ref.make_decoder_weights(cfg, seed=5)
     dec = ctx.decoder(layers=cfg.layers, d_model=cfg.d, ffn=cfg.ffn, heads=cfg.heads, kv_heads=cfg.kv_heads,
-                      vocab=cfg.vocab, max_batch=2, max_seq=64, attn_softcap=20.0, sliding_window=8)
+                      vocab=cfg.vocab, max_batch=2, max_seq=64, attn_softcap=20.0, sliding_window=8, final_softcap=3.0)
     qeng.load_decoder_weights(dec, W, cfg)
     prompt = ref.rng_of(77).integers(0, cfg.vocab, (2, 21)).astype(np.int32)
     want, logs = ref.Decoder(cfg, W).generate(prompt, 8)
     dec.reset(2)
     dec.prefill(prompt)
     assert ref.err_inf(dec.logits(), logs[0]) < 2e-3
+    assert np.abs(dec.logits()).max() <= 3.0
     assert np.array_equal(dec.decode(8), want)
     plain, _ = ref.Decoder(ref.DecoderConfig(**CFG), W).generate(prompt, 8)
     assert not np.array_equal(plain, want)  # the switches change the continuation on this input
