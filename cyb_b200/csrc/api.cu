@@ -58,7 +58,7 @@ int32_t qeng_create_opts(int32_t device, const qeng_options* opts, qeng_ctx** ou
   ctx->p2p_allowed = !o.no_p2p_allreduce;
   ctx->attn_cluster = !o.no_attn_cluster;
   ctx->step_kernel = o.step_kernel != 0;
-  ctx->attn_ctas_per_sm = o.attn_ctas_per_sm > 0 ? o.attn_ctas_per_sm : 8;
+  ctx->attn_ctas_per_sm = o.attn_ctas_per_sm > 0 ? o.attn_ctas_per_sm : 3;
   ctx->stream_groups = o.stream_groups;
   ctx->stream_stage_chunks = o.stream_stage_chunks & ~1;  // a two-chunk work item never straddles stages
   if (cudaMalloc(&ctx->status, kStatusBytes) != cudaSuccess || cudaMemset(ctx->status, 0, kStatusBytes) != cudaSuccess) {

@@ -169,8 +169,13 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
     return;
   }
 
-  __shared__ float sm_o[kAW][8][kHD];
-  __shared__ float sm_m[kAW][8], sm_l[kAW][8];
+  // merge buffers: they live in the ring, which is free once every page of this CTA is consumed
+  float (*sm_o)[8][kHD] = reinterpret_cast<float (*)[8][kHD]>(ring);                                   // [kAW][8][kHD]
+  float (*c_o)[kHD] = reinterpret_cast<float (*)[kHD]>(ring + sizeof(float) * kAW * 8 * kHD);           // [8][kHD]
+  float (*sm_m)[8] = reinterpret_cast<float (*)[8]>(ring + sizeof(float) * (kAW + 1) * 8 * kHD);        // [kAW][8]
+  float (*sm_l)[8] = sm_m + kAW;                                                                        // [kAW][8]
+  float* c_m = &sm_l[kAW][0];                                                                           // [8]
+  float* c_l = c_m + 8;                                                                                 // [8]
 
   float m_run = -INFINITY, l_run = 0.f;
   float o[16][4];
@@ -217,7 +222,14 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) qa[i] = qp[i * 4 + t];
     }
-    auto compute_tile = [&](int pg, uint4 (&kq)[2][4], uint4 (&vv)[4][2]) {
+    auto compute_tile = [&](int pg, uint32_t kt, uint32_t vt) {
+      // K rows of tokens g and g+8: the 16 bytes at d = 32i + 8t .. +7.  V is fetched only after the
+      // scores are done, so that the K and V fragments never hold registers at the same time.
+      uint4 kq[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) kq[nt][i] = lds128(kt + (uint32_t)(((nt * 8 + g) * 16 + i * 4 + t) * 16));
       // S = Q K^T for 16 tokens: two n-tiles of 8 tokens
       float sacc[2][4];
 #pragma unroll
@@ -263,6 +275,14 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
       const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&ph0));
       const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&ph1));
       const uint32_t pl0 = pack_h2(pr[0] - f0.x, pr[1] - f0.y), pl1 = pack_h2(pr[2] - f1.x, pr[3] - f1.y);
+      // V rows of tokens 2t, 2t+1, 2t+8, 2t+9: d = 8g..8g+7 and 64+8g..64+8g+7
+      uint4 vv[4][2];
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const int tk = 2 * t + (x & 1) + ((x >> 1) << 3);
+#pragma unroll
+        for (int r = 0; r < 2; ++r) vv[x][r] = lds128(vt + (uint32_t)((tk * 16 + r * 8 + g) * 16));
+      }
       // zero V rows that are not attended (their probability is 0, but 0 * garbage may be NaN)
       if (tok0 + 16 > len || tok0 < win0) {
 #pragma unroll
@@ -292,20 +312,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
       if (!failed && !mbar_wait(smem_u32(full + slot), (uint32_t)(it / kRing) & 1u)) failed = true;
       if (slot_ok[slot]) {
         const uint32_t kt = smem_u32(ring) + (uint32_t)slot * kSlotBytes, vt = kt + 16 * kHD * 2;
-        uint4 kq[2][4], vv[4][2];
-        // K rows of tokens g and g+8: the 16 bytes at d = 32i + 8t .. +7
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) kq[nt][i] = lds128(kt + (uint32_t)(((nt * 8 + g) * 16 + i * 4 + t) * 16));
-        // V rows of tokens 2t, 2t+1, 2t+8, 2t+9: d = 8g..8g+7 and 64+8g..64+8g+7
-#pragma unroll
-        for (int x = 0; x < 4; ++x) {
-          const int tk = 2 * t + (x & 1) + ((x >> 1) << 3);
-#pragma unroll
-          for (int r = 0; r < 2; ++r) vv[x][r] = lds128(vt + (uint32_t)((tk * 16 + r * 8 + g) * 16));
-        }
-        compute_tile(first + it * pstep, kq, vv);
+        compute_tile(first + it * pstep, kt, vt);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(empty + slot));  // the slot may be refilled
@@ -314,6 +321,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
   }
 
   // ---- merge the warps of this CTA ------------------------------------------
+  __syncthreads();  // every warp is done with the ring: it becomes the merge buffers
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
   if (warp < kAW && g < p.grp) {
@@ -331,7 +339,6 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
   __syncthreads();
   const int ns = kCl ? cs : (npages - pg_first + p.pps - 1) / p.pps;  // splits that hold pages
   const bool direct = !kCl && p.counters != nullptr && ns == 1;  // a single split: no partials needed
-  __shared__ float c_o[8][kHD], c_m[8], c_l[8];  // this CTA's partial per query head (cluster merge)
   for (int hh = 0; hh < p.grp && tid < kHD; ++hh) {
     float M = -INFINITY;
 #pragma unroll
@@ -433,7 +440,8 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
   if (tid == 0) p.counters[b * p.Hkv + h] = 0;  // ready for the next call
 }
 
-__global__ void __launch_bounds__(kAT) attn_decode_kernel(const AttnParams p) { attn_decode_body<false>(p); }
+// three CTAs per SM (<= 136 registers): this path is chosen when there are many pages per SM to cover
+__global__ void __launch_bounds__(kAT, 3) attn_decode_kernel(const AttnParams p) { attn_decode_body<false>(p); }
 
 // launched with a cluster dimension of (p.S, 1, 1) = (gridDim.x, 1, 1)
 __global__ void __launch_bounds__(kAT) attn_decode_cluster_kernel(const AttnParams p) {
@@ -504,11 +512,15 @@ constexpr int kMaxAttnCounters = 1 << 16;  // (sequence, kv head) pairs per call
 
 // Splits: enough CTAs to fill the machine several times over, at least one page per warp.
 static int pages_per_split(const qeng_ctx* ctx, int64_t B, int64_t Hkv, int64_t max_pages) {
-  int64_t target = (int64_t)ctx->sm_count * (ctx->attn_ctas_per_sm > 0 ? ctx->attn_ctas_per_sm : 8);
-  int64_t pps = (B * Hkv * max_pages + target - 1) / target;
+  // the fixed-split kernel keeps three CTAs per SM resident: one full wave of them is the target
+  int64_t target = (int64_t)ctx->sm_count * (ctx->attn_ctas_per_sm > 0 ? ctx->attn_ctas_per_sm : 3);
+  // splits per (sequence, kv head) that fill the wave, then equal page ranges for the longest sequence
+  int64_t S = (target + B * Hkv - 1) / (B * Hkv);
+  if (S < 1) S = 1;
+  int64_t pps = (max_pages + S - 1) / S;
   pps = (pps + kAW - 1) / kAW * kAW;
   if (pps < kAW) pps = kAW;
-  if (pps > 64) pps = 64;
+  if (pps > 128) pps = 128;
   return (int)pps;
 }
 

@@ -68,7 +68,7 @@ struct qeng_ctx {
   bool pdl = true;            // launch the streaming matmul with programmatic stream serialization
   // remaining switches of qeng_options
   bool p2p_allowed = true, attn_cluster = true, step_kernel = false;
-  int attn_ctas_per_sm = 8, stream_groups = 0, stream_stage_chunks = 0;
+  int attn_ctas_per_sm = 3, stream_groups = 0, stream_stage_chunks = 0;
   // bumped whenever attn_scratch moves: a captured graph that holds the old address is stale
   uint64_t scratch_gen = 0;
   // per-CTA argmax partials and the arrival counter of the fused LM head

@@ -72,7 +72,7 @@ typedef struct qeng_options {
   int32_t no_l2_prefetch;    /* 1: ignore qeng_weight_set_next hints */
   int32_t no_p2p_allreduce;  /* 1: small all-reduces go through NCCL instead of the peer-store kernel */
   int32_t no_attn_cluster;   /* 1: decode attention always uses fixed splits + scratch */
-  int32_t attn_ctas_per_sm;  /* CTAs per SM the split-KV attention aims for (default 8) */
+  int32_t attn_ctas_per_sm;  /* CTAs per SM the split-KV attention aims for (default 3: one resident wave) */
   int32_t stream_groups;     /* tile groups of the streaming matmul: 1, 2 or 4 (default: by shape) */
   int32_t step_kernel;       /* 1: decode steps of 1 or 2 sequences run all layers in one persistent cooperative
                                 kernel (tagged data flow between the operators) instead of one kernel per operator */
