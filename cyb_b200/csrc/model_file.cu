@@ -6,7 +6,7 @@
 // before binary).  What a model container holds is "config (TOML), graph IR, tensor index, tensor
 // data (Q4/Q8/F16/F32)" with HuggingFace tensor names (decide/pipeline.md:28-30); the page that
 // would fix the tensor-index schema (`cyb-model`) is not part of the reference checkout, so the
-// schema read here is this engine's own and is written down in INTEGRATION.md:
+// schema read here is this engine's own:
 //
 //   ~~~config    TOML: hidden_size, intermediate_size, num_hidden_layers, num_attention_heads,
 //                num_key_value_heads, head_dim, vocab_size, rms_norm_eps, rope_theta; optional

@@ -290,7 +290,11 @@ int32_t qeng_decoder_config(qeng_ctx* ctx, const qeng_decoder* dec, qeng_model_c
 /* ---- `.model` containers (".cyb -> graph IR ... tensor index, tensor data (Q4/Q8/F16/F32)",
  *      decide/pipeline.md:28-30; container rules reference/format.md:16-18,110-117; the reference
  *      maps its model files, shell/src/lib.rs:31-33).  The tensor-index schema is this engine's own
- *      (the `cyb-model` page is not in the reference checkout); INTEGRATION.md writes it down.
+ *      (the `cyb-model` page is not in the reference checkout): sections `config` (TOML keys
+ *      hidden_size, intermediate_size, num_hidden_layers, num_attention_heads, num_key_value_heads,
+ *      head_dim, vocab_size, rms_norm_eps, rope_theta, optional attn_logit_softcapping,
+ *      sliding_window, final_logit_softcapping), `tensors` ([[tensor]] tables: name, dtype
+ *      "Q4" | "Q8" | "F32" | "F16" | "BF16", shape, offset, size) and `weights` (binary).
  * Read a container's `config` into a qeng_model_cfg (max_batch = 1, max_seq = 0, tp = 1/0: the
  * caller sets those before qeng_decoder_create) and count its tensors.  ctx may be NULL. */
 int32_t qeng_model_file_config(qeng_ctx* ctx, const char* path, qeng_model_cfg* out, int64_t* n_tensors);

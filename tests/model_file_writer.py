@@ -1,6 +1,7 @@
 """Writes a `.model` container (a `.cyb` file: TOML frontmatter, `~~~name` sections, sized binary)
 from a weight dict of the oracle's layout, with the tensor-index schema the engine reads
-(INTEGRATION.md).  Test infrastructure: the sample files of the loader tests come from here."""
+(sections `config`, `tensors`, `weights`; one [[tensor]] table per tensor with name, dtype, shape,
+offset, size).  Test infrastructure: the sample files of the loader tests come from here."""
 from __future__ import annotations
 
 import numpy as np
