@@ -108,6 +108,8 @@ extern "C" {
     pub fn qeng_weight_unpack_q4(ctx: *mut qeng_ctx, w: *const qeng_weight, q: *mut u8, s: *mut u16) -> i32;
     pub fn qeng_weight_dequant_f32(ctx: *mut qeng_ctx, w: *const qeng_weight, out: *mut f32, stream: *mut c_void) -> i32;
     pub fn qeng_weight_quantize_q4(ctx: *mut qeng_ctx, w_dev: *const c_void, x_dtype: i32, N: i64, K: i64, ld: i64, out: *mut *mut qeng_weight, stream: *mut c_void) -> i32;
+    pub fn qeng_weight_pack_q4k(ctx: *mut qeng_ctx, blocks: *const u8, N: i64, K: i64, out: *mut *mut qeng_weight) -> i32;
+    pub fn qeng_weight_unpack_k4(ctx: *mut qeng_ctx, w: *const qeng_weight, q: *mut u8, scale_min: *mut f32) -> i32;
     pub fn qeng_weight_pack_q8(ctx: *mut qeng_ctx, q: *const i8, s: *const u16, N: i64, K: i64, out: *mut *mut qeng_weight) -> i32;
     pub fn qeng_weight_unpack_q8(ctx: *mut qeng_ctx, w: *const qeng_weight, q: *mut i8, s: *mut u16) -> i32;
     pub fn qeng_weight_quantize_q8(ctx: *mut qeng_ctx, w_dev: *const c_void, x_dtype: i32, N: i64, K: i64, ld: i64, out: *mut *mut qeng_weight, stream: *mut c_void) -> i32;
@@ -138,6 +140,7 @@ extern "C" {
     pub fn qeng_decoder_free(ctx: *mut qeng_ctx, dec: *mut qeng_decoder) -> i32;
     pub fn qeng_decoder_load_matrix(ctx: *mut qeng_ctx, dec: *mut qeng_decoder, layer: i32, which: i32, q: *const u8, s: *const u16, N: i64, K: i64) -> i32;
     pub fn qeng_decoder_load_matrix_q8(ctx: *mut qeng_ctx, dec: *mut qeng_decoder, layer: i32, which: i32, q: *const i8, s: *const u16, N: i64, K: i64) -> i32;
+    pub fn qeng_decoder_load_matrix_q4k(ctx: *mut qeng_ctx, dec: *mut qeng_decoder, layer: i32, which: i32, blocks: *const u8, N: i64, K: i64) -> i32;
     pub fn qeng_decoder_load_norm(ctx: *mut qeng_ctx, dec: *mut qeng_decoder, layer: i32, which: i32, gamma: *const f32) -> i32;
     pub fn qeng_decoder_load_head(ctx: *mut qeng_ctx, dec: *mut qeng_decoder, emb: *const u16, lm_head: *const u16, final_gamma: *const f32) -> i32;
     pub fn qeng_decoder_config(ctx: *mut qeng_ctx, dec: *const qeng_decoder, out: *mut qeng_model_cfg) -> i32;

@@ -23,6 +23,7 @@ constexpr int kPage = 16;
 
 struct HostMat {
   int fmt = QENG_FMT_Q4;
+  int su = 1;  // 16-bit words of scale data per 32-block: 1 (an f16 scale) or 4 (f32 scale and minimum)
   std::vector<uint8_t> q;
   std::vector<uint16_t> s;
   int64_t N = 0, K = 0;
@@ -537,7 +538,14 @@ int32_t plan_step(qeng_ctx* ctx, qeng_decoder* d) {
 // one decode step, all state on the device: x holds the embedding of the token to feed
 int32_t decode_step(qeng_ctx* ctx, qeng_decoder* d, cudaStream_t st) {
   const int B = d->batch;
-  const bool fused = d->cfg.tp_world > 1 && qeng_tp_fuse_ready(ctx, B, d->cfg.d_model);
+  bool fused = d->cfg.tp_world > 1 && qeng_tp_fuse_ready(ctx, B, d->cfg.d_model);
+  // the exchange through the matmul epilogues addresses inbox rows by the row index inside one
+  // pass: every matrix must take the whole batch in one pass
+  for (int l = 0; fused && l < d->cfg.layers; ++l) {
+    const Layer& L = d->layers[l];
+    fused = L.wqkv && L.wo && L.wgu && L.wdown && qeng_gemm_q4_stream_fits(ctx, L.wqkv, B) && qeng_gemm_q4_stream_fits(ctx, L.wo, B) &&
+            qeng_gemm_q4_stream_fits(ctx, L.wgu, B) && qeng_gemm_q4_stream_fits(ctx, L.wdown, B);
+  }
   float* x = d->x;
   for (int l = 0; l < d->cfg.layers; ++l) {
     int32_t rc = run_layer(ctx, d, l, B, d->dec_table, st, fused ? &x : nullptr);
@@ -555,14 +563,14 @@ int32_t decode_step(qeng_ctx* ctx, qeng_decoder* d, cudaStream_t st) {
 }
 
 // shard of a full host matrix: rows [r0,r1) x columns [k0,k1)
-void take_shard(const uint8_t* q, const uint16_t* s, int64_t K, int64_t r0, int64_t r1, int64_t k0, int64_t k1,
+void take_shard(const uint8_t* q, const uint16_t* s, int su, int64_t K, int64_t r0, int64_t r1, int64_t k0, int64_t k1,
                 HostMat& out) {
-  out.N = r1 - r0; out.K = k1 - k0;
+  out.N = r1 - r0; out.K = k1 - k0; out.su = su;
   out.q.resize((size_t)out.N * out.K);
-  out.s.resize((size_t)out.N * out.K / 32);
+  out.s.resize((size_t)out.N * out.K / 32 * su);
   for (int64_t r = r0; r < r1; ++r) {
     memcpy(&out.q[(size_t)(r - r0) * out.K], q + r * K + k0, (size_t)out.K);
-    memcpy(&out.s[(size_t)(r - r0) * (out.K / 32)], s + r * (K / 32) + k0 / 32, (size_t)(out.K / 32) * 2);
+    memcpy(&out.s[(size_t)(r - r0) * (out.K / 32) * su], s + (r * (K / 32) + k0 / 32) * su, (size_t)(out.K / 32) * 2 * su);
   }
 }
 
@@ -692,6 +700,7 @@ static void link_weights(qeng_decoder* d) {
 
 static int32_t pack_fmt(qeng_ctx* ctx, int fmt, const uint8_t* q, const uint16_t* s, int64_t N, int64_t K, qeng_weight** out) {
   if (fmt == QENG_FMT_Q8) return qeng_weight_pack_q8(ctx, reinterpret_cast<const int8_t*>(q), s, N, K, out);
+  if (fmt == QENG_FMT_K4) return qeng_weight_pack_k4(ctx, q, reinterpret_cast<const float*>(s), N, K, out);
   return qeng_weight_pack_q4(ctx, q, s, N, K, out);
 }
 
@@ -725,19 +734,20 @@ static int32_t load_matrix_fmt(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, in
       if (i != which && L.pend[i].N && L.pend[i].fmt != fmt)
         return qeng_fail(ctx, QENG_ERR_ARG, "decoder_load_matrix: layer %d mixes 4-bit and 8-bit blocks inside a fused matrix", layer);
   const bool row_split = which == QENG_W_O || which == QENG_W_DOWN;  // split along K, partial sums
-  if (row_split) take_shard(q, s, K, 0, N, K / t * r, K / t * (r + 1), hm);
-  else take_shard(q, s, K, N / t * r, N / t * (r + 1), 0, K, hm);
+  const int su = fmt == QENG_FMT_K4 ? 4 : 1;
+  if (row_split) take_shard(q, s, su, K, 0, N, K / t * r, K / t * (r + 1), hm);
+  else take_shard(q, s, su, K, N / t * r, N / t * (r + 1), 0, K, hm);
   hm.fmt = fmt;
   if (which <= QENG_W_V) {  // rotary pairs (i, i+64) of every head become MMA rows g / g+8 of one tile
     HostMat pm;
-    pm.N = hm.N; pm.K = hm.K; pm.fmt = fmt;
+    pm.N = hm.N; pm.K = hm.K; pm.fmt = fmt; pm.su = su;
     pm.q.resize(hm.q.size());
     pm.s.resize(hm.s.size());
     for (int64_t row = 0; row < hm.N; ++row) {
       const int64_t head = row / kHD, i = row % kHD;
       const int64_t prow = head * kHD + (((i & 63) >> 3) << 4) + (i & 7) + ((i >> 6) << 3);
       memcpy(&pm.q[(size_t)prow * hm.K], &hm.q[(size_t)row * hm.K], (size_t)hm.K);
-      memcpy(&pm.s[(size_t)prow * (hm.K / 32)], &hm.s[(size_t)row * (hm.K / 32)], (size_t)(hm.K / 32) * 2);
+      memcpy(&pm.s[(size_t)prow * (hm.K / 32) * su], &hm.s[(size_t)row * (hm.K / 32) * su], (size_t)(hm.K / 32) * 2 * su);
     }
     hm = pm;
   }
@@ -750,7 +760,7 @@ static int32_t load_matrix_fmt(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, in
   } else if (which <= QENG_W_V) {
     if (L.pend[QENG_W_Q].N && L.pend[QENG_W_K].N && L.pend[QENG_W_V].N) {
       HostMat f;
-      f.K = dm;
+      f.K = dm; f.su = su; f.fmt = fmt;
       for (int i = QENG_W_Q; i <= QENG_W_V; ++i) {
         f.q.insert(f.q.end(), L.pend[i].q.begin(), L.pend[i].q.end());
         f.s.insert(f.s.end(), L.pend[i].s.begin(), L.pend[i].s.end());
@@ -766,15 +776,15 @@ static int32_t load_matrix_fmt(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, in
       const HostMat& G = L.pend[QENG_W_GATE];
       const HostMat& U = L.pend[QENG_W_UP];
       HostMat f;
-      f.N = 2 * G.N; f.K = dm;
+      f.N = 2 * G.N; f.K = dm; f.su = su; f.fmt = fmt;
       f.q.resize((size_t)f.N * f.K);
-      f.s.resize((size_t)f.N * f.K / 32);
+      f.s.resize((size_t)f.N * f.K / 32 * su);
       for (int64_t i = 0; i < G.N; ++i) {
         const int64_t rg = (i / 8) * 16 + i % 8, ru = rg + 8;
         memcpy(&f.q[(size_t)rg * dm], &G.q[(size_t)i * dm], (size_t)dm);
         memcpy(&f.q[(size_t)ru * dm], &U.q[(size_t)i * dm], (size_t)dm);
-        memcpy(&f.s[(size_t)rg * (dm / 32)], &G.s[(size_t)i * (dm / 32)], (size_t)(dm / 32) * 2);
-        memcpy(&f.s[(size_t)ru * (dm / 32)], &U.s[(size_t)i * (dm / 32)], (size_t)(dm / 32) * 2);
+        memcpy(&f.s[(size_t)rg * (dm / 32) * su], &G.s[(size_t)i * (dm / 32) * su], (size_t)(dm / 32) * 2 * su);
+        memcpy(&f.s[(size_t)ru * (dm / 32) * su], &U.s[(size_t)i * (dm / 32) * su], (size_t)(dm / 32) * 2 * su);
       }
       L.pend[QENG_W_GATE] = HostMat();
       L.pend[QENG_W_UP] = HostMat();
@@ -796,6 +806,16 @@ int32_t qeng_decoder_load_matrix(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, 
 int32_t qeng_decoder_load_matrix_q8(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, int32_t which, const int8_t* q,
                                     const uint16_t* s, int64_t N, int64_t K) {
   return load_matrix_fmt(ctx, d, layer, which, QENG_FMT_Q8, reinterpret_cast<const uint8_t*>(q), s, N, K);
+}
+
+int32_t qeng_decoder_load_matrix_q4k(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, int32_t which, const uint8_t* blocks,
+                                     int64_t N, int64_t K) {
+  if (!ctx || !d || !blocks) return qeng_fail(ctx, QENG_ERR_ARG, "decoder_load_matrix_q4k: null argument");
+  std::vector<uint8_t> q;
+  std::vector<float> dm;
+  int32_t rc = qeng_q4k_expand(ctx, blocks, N, K, &q, &dm);
+  if (rc != QENG_OK) return rc;
+  return load_matrix_fmt(ctx, d, layer, which, QENG_FMT_K4, q.data(), reinterpret_cast<const uint16_t*>(dm.data()), N, K);
 }
 
 int32_t qeng_decoder_load_norm(qeng_ctx* ctx, qeng_decoder* d, int32_t layer, int32_t which, const float* gamma) {

@@ -152,6 +152,38 @@ __device__ __forceinline__ void chunk_mma(int (&d)[4], const WBlocks<Q8>& w, int
 }
 __device__ __forceinline__ float unbias(int d) { return __int_as_float(d) - kBiasF; }
 
+// Scales of one chunk for this lane's rows g / g+8: (even block, odd block).  KQ = false: one f16
+// scale per (row, block), 64 B per chunk and row tile.  KQ = true ("K-quant" 4-bit blocks:
+// w = D * code - M, code 0..15): f32 D and M per (row, block), 256 B per chunk and row tile laid out
+// per lane group g as {De(g), De(g+8), Do(g), Do(g+8), Me(g), Me(g+8), Mo(g), Mo(g+8)}.
+template <bool KQ>
+struct BlkScales {
+  float2 se, so;  // (row g, row g+8) of the even / odd block
+  float2 me, mo;  // minima (KQ only)
+};
+template <bool KQ>
+__device__ __forceinline__ uint32_t scale_chunk_bytes() { return KQ ? 256u : 64u; }
+template <bool KQ>
+__device__ __forceinline__ BlkScales<KQ> load_scales(uint32_t sbase, int ch, int g, bool live = true) {
+  BlkScales<KQ> r;
+  if (KQ) {
+    uint4 a = lds128(sbase + (uint32_t)ch * 256u + (uint32_t)g * 32u);
+    uint4 b = lds128(sbase + (uint32_t)ch * 256u + (uint32_t)g * 32u + 16u);
+    if (!live) a = b = make_uint4(0u, 0u, 0u, 0u);
+    r.se = make_float2(__uint_as_float(a.x), __uint_as_float(a.y));
+    r.so = make_float2(__uint_as_float(a.z), __uint_as_float(a.w));
+    r.me = make_float2(__uint_as_float(b.x), __uint_as_float(b.y));
+    r.mo = make_float2(__uint_as_float(b.z), __uint_as_float(b.w));
+  } else {
+    uint2 s2 = lds64(sbase + (uint32_t)ch * 64u + (uint32_t)g * 8u);
+    if (!live) s2 = make_uint2(0u, 0u);
+    r.se = __half22float2(*reinterpret_cast<const __half2*>(&s2.x));
+    r.so = __half22float2(*reinterpret_cast<const __half2*>(&s2.y));
+    r.me = r.mo = make_float2(0.f, 0.f);
+  }
+  return r;
+}
+
 __device__ __forceinline__ float act_f32(const void* x, int dtype, long long i) {
   if (dtype == QENG_F32) return reinterpret_cast<const float*>(x)[i];
   if (dtype == QENG_F16) return __half2float(reinterpret_cast<const __half*>(x)[i]);
@@ -166,6 +198,8 @@ __device__ __forceinline__ float act_f32(const void* x, int dtype, long long i) 
 //   fex  : [cols][nblk] float   2^e (x 128 for the hi limb), 0 for blocks beyond K
 struct XLayout {
   uint32_t col_stride, xq, zero, zin, fex, bytes;
+  uint32_t fsx;  // [cols][nblk] float: fex * (sum of the column's bytes in the block); 0 = not staged (only
+                 // weight formats with a per-block minimum need the block sums of the activations)
   uint32_t zs;  // bytes per column of zin / fex (padded so that the columns read together fall in different banks)
   int nblk;
 };
@@ -173,7 +207,7 @@ struct XLayout {
 // read zeros); chunks = 64-wide K chunks of the slice.  zero_reserved > 0 puts the zero region
 // first, at a fixed place and size whatever the columns are (a kernel that stages several
 // different operands clears it once); it must be >= x_zero_bytes of every layout used.
-__host__ __device__ inline XLayout x_layout(int cols, int chunks, bool zeroed, uint32_t zero_reserved = 0) {
+__host__ __device__ inline XLayout x_layout(int cols, int chunks, bool zeroed, uint32_t zero_reserved = 0, bool sums = false) {
   XLayout L;
   L.nblk = chunks * 2;
   const uint32_t raw = ((uint32_t)chunks * 64u + 127u) / 128u * 128u;
@@ -196,6 +230,11 @@ __host__ __device__ inline XLayout x_layout(int cols, int chunks, bool zeroed, u
   L.zs = ((uint32_t)L.nblk * 4u + 127u) / 128u * 128u + 16u;
   L.fex = L.zin + (uint32_t)cols * L.zs;
   L.bytes = L.fex + (uint32_t)cols * L.zs;
+  L.fsx = 0;
+  if (sums) {
+    L.fsx = L.bytes;
+    L.bytes += (uint32_t)cols * L.zs;
+  }
   return L;
 }
 // bytes of the zero region (to be cleared once per kernel)
@@ -209,7 +248,8 @@ __host__ __device__ inline uint32_t x_zero_bytes(const XLayout& L) { return L.co
 // from the most significant down; zin0 / fex0 likewise with stride zs.
 template <int LIMBS>
 __device__ __forceinline__ void quantise_group(const float (&v)[8], bool valid, uint32_t xq0, uint32_t col_stride,
-                                               uint32_t zin0, uint32_t fex0, uint32_t zs, int blk_off32, int t) {
+                                               uint32_t zin0, uint32_t fex0, uint32_t zs, int blk_off32, int t,
+                                               uint32_t fsx0 = 0) {
   constexpr int kBits = LIMBS == 3 ? 20 : 13;          // the block's largest magnitude lands in [2^kBits, 2^(kBits+1))
   constexpr int kMaxQ = LIMBS == 3 ? 2097151 : 16383;
   // Every thread of every CTA runs this once per matmul before the first MMA can issue, so the
@@ -270,6 +310,7 @@ __device__ __forceinline__ void quantise_group(const float (&v)[8], bool valid, 
         const float f = step * (float)(1 << (7 * (LIMBS - 1 - l)));
         asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(zin0 + (uint32_t)l * zs + b4), "r"(kBias - 8u * (uint32_t)sum[l]) : "memory");
         asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(fex0 + (uint32_t)l * zs + b4), "f"(f) : "memory");
+        if (fsx0 != 0) asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(fsx0 + (uint32_t)l * zs + b4), "f"(f * (float)sum[l]) : "memory");
       }
     }
   }
@@ -282,7 +323,7 @@ __device__ __forceinline__ void quantise_group(const float (&v)[8], bool valid, 
 // work items wi, wi + NW, ...; an item is max(G/2, 1) chunks.
 
 // G = 4: one activation row.  acc[0] += row g, acc[1] += row g+8 (partial over this lane's columns).
-template <int NW, bool Q8 = false>
+template <int NW, bool Q8 = false, bool KQ = false>
 __device__ __forceinline__ void consume_g4(float (&acc)[2], uint32_t wbase, uint32_t sbase, int nc, int blk0,
                                            const XLayout& L, uint32_t xbase, int wi, int lane) {
   const int g = lane >> 2, t = lane & 3;
@@ -294,6 +335,7 @@ __device__ __forceinline__ void consume_g4(float (&acc)[2], uint32_t wbase, uint
   const uint32_t xa = xbase + L.xq + (uint32_t)(g >> 2) * L.col_stride + (uint32_t)t * 8u + (uint32_t)(blk0 + myblk) * 32u;
   const uint32_t zin = xbase + L.zin + (uint32_t)limb * L.zs + (uint32_t)(blk0 + 2 * (t & 1)) * 4u;
   const uint32_t fex = xbase + L.fex + (uint32_t)limb * L.zs + (uint32_t)(blk0 + 2 * (t & 1)) * 4u;
+  const uint32_t fsx = xbase + L.fsx + (uint32_t)limb * L.zs + (uint32_t)(blk0 + 2 * (t & 1)) * 4u;
   const uint32_t k0 = myblk == 0 ? 0xffffffffu : 0u, k1 = myblk == 1 ? 0xffffffffu : 0u, k2 = myblk == 2 ? 0xffffffffu : 0u,
                  k3 = myblk == 3 ? 0xffffffffu : 0u;
   const int nitems = (nc + 1) >> 1;
@@ -302,32 +344,38 @@ __device__ __forceinline__ void consume_g4(float (&acc)[2], uint32_t wbase, uint
     const WBlocks<Q8> wA = load_chunk<Q8>(wbase + (uint32_t)(2 * it) * chunk_bytes<Q8>(), lane);
     const WBlocks<Q8> wB = load_chunk<Q8>(wbase + (uint32_t)(2 * it + 1) * chunk_bytes<Q8>(), lane);
     const int ch = 2 * it + (t & 1);
-    uint2 s2 = lds64(sbase + (uint32_t)ch * 64u + (uint32_t)g * 8u);
-    if (ch >= nc) s2 = make_uint2(0u, 0u);  // a chunk past the stage's data: whatever the slot holds must not count
+    // a chunk past the stage's data: whatever the slot holds must not count
+    const BlkScales<KQ> S = load_scales<KQ>(sbase, ch, g, ch < nc);
     const uint2 z2 = lds64(zin + (uint32_t)it * 16u);
     const uint2 f2 = lds64(fex + (uint32_t)it * 16u);
     const uint2 b = lds64(xa + (uint32_t)it * 128u);
     int d[4] = {(int)z2.x, (int)z2.y, (int)z2.x, (int)z2.y};
-    if (Q8) d[0] = d[1] = d[2] = d[3] = (int)kBias;  // signed bytes: no zero point
+    if (Q8 || KQ) d[0] = d[1] = d[2] = d[3] = (int)kBias;  // signed bytes / codes with a minimum: no zero point
     chunk_mma<Q8>(d, wA, 0, b.x & k0, b.y & k0);
     chunk_mma<Q8>(d, wA, 1, b.x & k1, b.y & k1);
     chunk_mma<Q8>(d, wB, 0, b.x & k2, b.y & k2);
     chunk_mma<Q8>(d, wB, 1, b.x & k3, b.y & k3);
 
-    const float2 se = __half22float2(*reinterpret_cast<const __half2*>(&s2.x));  // (row g, row g+8) of the even block
-    const float2 so = __half22float2(*reinterpret_cast<const __half2*>(&s2.y));  // ... of the odd block
     const float fe = __uint_as_float(f2.x), fo = __uint_as_float(f2.y);
-    acc[0] = fmaf(se.x * fe, unbias(d[0]), acc[0]);
-    acc[0] = fmaf(so.x * fo, unbias(d[1]), acc[0]);
-    acc[1] = fmaf(se.y * fe, unbias(d[2]), acc[1]);
-    acc[1] = fmaf(so.y * fo, unbias(d[3]), acc[1]);
+    acc[0] = fmaf(S.se.x * fe, unbias(d[0]), acc[0]);
+    acc[0] = fmaf(S.so.x * fo, unbias(d[1]), acc[0]);
+    acc[1] = fmaf(S.se.y * fe, unbias(d[2]), acc[1]);
+    acc[1] = fmaf(S.so.y * fo, unbias(d[3]), acc[1]);
+    if (KQ) {  // - M * (block sum of the activations)
+      const uint2 q2 = lds64(fsx + (uint32_t)it * 16u);
+      const float qe = __uint_as_float(q2.x), qo = __uint_as_float(q2.y);
+      acc[0] = fmaf(-S.me.x, qe, acc[0]);
+      acc[0] = fmaf(-S.mo.x, qo, acc[0]);
+      acc[1] = fmaf(-S.me.y, qe, acc[1]);
+      acc[1] = fmaf(-S.mo.y, qo, acc[1]);
+    }
   }
 }
 
 // One activation row in three limbs (22 bits): the 8 columns hold (limb, block) for the TWO blocks of
 // a chunk (6 used); lane t < 3 owns limb t of both blocks, lane t = 3 idles.  acc[0] += row g,
 // acc[1] += row g+8.
-template <int NW, bool Q8 = false>
+template <int NW, bool Q8 = false, bool KQ = false>
 __device__ __forceinline__ void consume_m1l3(float (&acc)[2], uint32_t wbase, uint32_t sbase, int nc, int blk0,
                                              const XLayout& L, uint32_t xbase, int wi, int lane) {
   const int g = lane >> 2, t = lane & 3;
@@ -339,34 +387,41 @@ __device__ __forceinline__ void consume_m1l3(float (&acc)[2], uint32_t wbase, ui
   for (int j = 0; j < 2; ++j) xa[j] = ((g < 6 && (g & 1) == j) ? xcol : zcol) + (uint32_t)(blk0 + j) * 32u;
   const uint32_t zin = xbase + L.zin + (uint32_t)limb * L.zs + (uint32_t)blk0 * 4u;
   const uint32_t fex = xbase + L.fex + (uint32_t)limb * L.zs + (uint32_t)blk0 * 4u;
+  const uint32_t fsx = xbase + L.fsx + (uint32_t)limb * L.zs + (uint32_t)blk0 * 4u;
   const float live = t < 3 ? 1.f : 0.f;
 #pragma unroll 2
   for (int it = wi; it < nc; it += NW) {
     const WBlocks<Q8> w = load_chunk<Q8>(wbase + (uint32_t)it * chunk_bytes<Q8>(), lane);
-    const uint2 s2 = lds64(sbase + (uint32_t)it * 64u + (uint32_t)g * 8u);
+    const BlkScales<KQ> S = load_scales<KQ>(sbase, it, g);
     const uint2 z2 = lds64(zin + (uint32_t)it * 8u);
     const uint2 f2 = lds64(fex + (uint32_t)it * 8u);
     int d[4] = {(int)z2.x, (int)z2.y, (int)z2.x, (int)z2.y};
-    if (Q8) d[0] = d[1] = d[2] = d[3] = (int)kBias;
+    if (Q8 || KQ) d[0] = d[1] = d[2] = d[3] = (int)kBias;
     const uint32_t xo = (uint32_t)it * 64u;
     uint2 b, b2;
     b = lds64(xa[0] + xo);
     b2 = lds64(xa[1] + xo);
     chunk_mma<Q8>(d, w, 0, b.x, b.y);
     chunk_mma<Q8>(d, w, 1, b2.x, b2.y);
-    const float2 se = __half22float2(*reinterpret_cast<const __half2*>(&s2.x));
-    const float2 so = __half22float2(*reinterpret_cast<const __half2*>(&s2.y));
     const float fe = __uint_as_float(f2.x) * live, fo = __uint_as_float(f2.y) * live;
-    acc[0] = fmaf(se.x * fe, unbias(d[0]), acc[0]);
-    acc[0] = fmaf(so.x * fo, unbias(d[1]), acc[0]);
-    acc[1] = fmaf(se.y * fe, unbias(d[2]), acc[1]);
-    acc[1] = fmaf(so.y * fo, unbias(d[3]), acc[1]);
+    acc[0] = fmaf(S.se.x * fe, unbias(d[0]), acc[0]);
+    acc[0] = fmaf(S.so.x * fo, unbias(d[1]), acc[0]);
+    acc[1] = fmaf(S.se.y * fe, unbias(d[2]), acc[1]);
+    acc[1] = fmaf(S.so.y * fo, unbias(d[3]), acc[1]);
+    if (KQ) {
+      const uint2 q2 = lds64(fsx + (uint32_t)it * 8u);
+      const float qe = __uint_as_float(q2.x) * live, qo = __uint_as_float(q2.y) * live;
+      acc[0] = fmaf(-S.me.x, qe, acc[0]);
+      acc[0] = fmaf(-S.mo.x, qo, acc[0]);
+      acc[1] = fmaf(-S.me.y, qe, acc[1]);
+      acc[1] = fmaf(-S.mo.y, qo, acc[1]);
+    }
   }
 }
 
 // G = 2: two activation rows; columns = (row, limb) x 2 blocks; an item is one chunk.
 // This lane's output columns: column pair t = (row t>>1, limb t&1), blocks 0 and 1 of the chunk.
-template <int NW, bool Q8 = false>
+template <int NW, bool Q8 = false, bool KQ = false>
 __device__ __forceinline__ void consume_g2(float (&acc)[2], uint32_t wbase, uint32_t sbase, int nc, int blk0,
                                            const XLayout& L, uint32_t xbase, int wi, int lane) {
   const int g = lane >> 2, t = lane & 3;
@@ -378,33 +433,40 @@ __device__ __forceinline__ void consume_g2(float (&acc)[2], uint32_t wbase, uint
   for (int j = 0; j < 2; ++j) xa[j] = (myblk == j ? xcol : zcol) + (uint32_t)(blk0 + j) * 32u;
   const uint32_t zin = xbase + L.zin + (uint32_t)t * L.zs + (uint32_t)blk0 * 4u;
   const uint32_t fex = xbase + L.fex + (uint32_t)t * L.zs + (uint32_t)blk0 * 4u;
+  const uint32_t fsx = xbase + L.fsx + (uint32_t)t * L.zs + (uint32_t)blk0 * 4u;
 #pragma unroll 2
   for (int it = wi; it < nc; it += NW) {
     const WBlocks<Q8> w = load_chunk<Q8>(wbase + (uint32_t)it * chunk_bytes<Q8>(), lane);
-    const uint2 s2 = lds64(sbase + (uint32_t)it * 64u + (uint32_t)g * 8u);
+    const BlkScales<KQ> S = load_scales<KQ>(sbase, it, g);
     const uint2 z2 = lds64(zin + (uint32_t)it * 8u);
     const uint2 f2 = lds64(fex + (uint32_t)it * 8u);
     int d[4] = {(int)z2.x, (int)z2.y, (int)z2.x, (int)z2.y};
-    if (Q8) d[0] = d[1] = d[2] = d[3] = (int)kBias;
+    if (Q8 || KQ) d[0] = d[1] = d[2] = d[3] = (int)kBias;
     const uint32_t xo = (uint32_t)it * 64u;
     uint2 b;
     b = lds64(xa[0] + xo);
     chunk_mma<Q8>(d, w, 0, b.x, b.y);
     b = lds64(xa[1] + xo);
     chunk_mma<Q8>(d, w, 1, b.x, b.y);
-    const float2 se = __half22float2(*reinterpret_cast<const __half2*>(&s2.x));
-    const float2 so = __half22float2(*reinterpret_cast<const __half2*>(&s2.y));
     const float fe = __uint_as_float(f2.x), fo = __uint_as_float(f2.y);
-    acc[0] = fmaf(se.x * fe, unbias(d[0]), acc[0]);
-    acc[0] = fmaf(so.x * fo, unbias(d[1]), acc[0]);
-    acc[1] = fmaf(se.y * fe, unbias(d[2]), acc[1]);
-    acc[1] = fmaf(so.y * fo, unbias(d[3]), acc[1]);
+    acc[0] = fmaf(S.se.x * fe, unbias(d[0]), acc[0]);
+    acc[0] = fmaf(S.so.x * fo, unbias(d[1]), acc[0]);
+    acc[1] = fmaf(S.se.y * fe, unbias(d[2]), acc[1]);
+    acc[1] = fmaf(S.so.y * fo, unbias(d[3]), acc[1]);
+    if (KQ) {
+      const uint2 q2 = lds64(fsx + (uint32_t)it * 8u);
+      const float qe = __uint_as_float(q2.x), qo = __uint_as_float(q2.y);
+      acc[0] = fmaf(-S.me.x, qe, acc[0]);
+      acc[0] = fmaf(-S.mo.x, qo, acc[0]);
+      acc[1] = fmaf(-S.me.y, qe, acc[1]);
+      acc[1] = fmaf(-S.mo.y, qo, acc[1]);
+    }
   }
 }
 
 // G = 1: NT tiles of 8 columns = 4 activation rows each; lane t of tile nt owns row 4 nt + t, both
 // limbs.  acc[nt][0] += row g of the weights, acc[nt][1] += row g+8.  An item is one chunk.
-template <int NW, int NT, bool Q8 = false>
+template <int NW, int NT, bool Q8 = false, bool KQ = false>
 __device__ __forceinline__ void consume_g1(float (&acc)[NT][2], uint32_t wbase, uint32_t sbase, int nc, int blk0,
                                            const XLayout& L, uint32_t xbase, int cols, int wi, int lane) {
   const int g = lane >> 2, t = lane & 3;
@@ -417,15 +479,14 @@ __device__ __forceinline__ void consume_g1(float (&acc)[NT][2], uint32_t wbase, 
     const int oc = min(nt * 8 + 2 * t, cols - 2);  // this lane's output columns (hi, lo) of row 4 nt + t
     za[nt] = (uint32_t)oc * L.zs + (uint32_t)blk0 * 4u;
   }
-  const uint32_t zin = xbase + L.zin, fex = xbase + L.fex;
+  const uint32_t zin = xbase + L.zin, fex = xbase + L.fex, fsx = xbase + L.fsx;
   const uint32_t lo_off = L.zs;  // column + 1
 #pragma unroll 2
   for (int it = wi; it < nc; it += NW) {
     const WBlocks<Q8> wq = load_chunk<Q8>(wbase + (uint32_t)it * chunk_bytes<Q8>(), lane);
     const uint4 w = wq.lo;
-    const uint2 s2 = lds64(sbase + (uint32_t)it * 64u + (uint32_t)g * 8u);
-    const float2 se = __half22float2(*reinterpret_cast<const __half2*>(&s2.x));
-    const float2 so = __half22float2(*reinterpret_cast<const __half2*>(&s2.y));
+    const BlkScales<KQ> S = load_scales<KQ>(sbase, it, g);
+    const float2 se = S.se, so = S.so;
     const uint32_t m = 0x0f0f0f0fu;
     // the A registers of the even and of the odd block: unpacked once per chunk, used by every n-tile
     const uint32_t e0 = Q8 ? wq.lo.x : w.x & m, e1 = Q8 ? wq.lo.y : w.y & m, e2 = Q8 ? wq.lo.z : (w.x >> 4) & m,
@@ -445,6 +506,10 @@ __device__ __forceinline__ void consume_g1(float (&acc)[NT][2], uint32_t wbase, 
         de[0] = de[1] = de[2] = de[3] = dd[0] = dd[1] = dd[2] = dd[3] = (int)kBias;
         imma_s8(de, e0, e1, e2, e3, be.x, be.y);
         imma_s8(dd, o0, o1, o2, o3, bo.x, bo.y);
+      } else if (KQ) {
+        de[0] = de[1] = de[2] = de[3] = dd[0] = dd[1] = dd[2] = dd[3] = (int)kBias;
+        imma(de, e0, e1, e2, e3, be.x, be.y);
+        imma(dd, o0, o1, o2, o3, bo.x, bo.y);
       } else {
         imma(de, e0, e1, e2, e3, be.x, be.y);
         imma(dd, o0, o1, o2, o3, bo.x, bo.y);
@@ -457,6 +522,14 @@ __device__ __forceinline__ void consume_g1(float (&acc)[NT][2], uint32_t wbase, 
       acc[nt][0] = fmaf(so.x * fo, vo0, acc[nt][0]);
       acc[nt][1] = fmaf(se.y * fe, ve1, acc[nt][1]);
       acc[nt][1] = fmaf(so.y * fo, vo1, acc[nt][1]);
+      if (KQ) {  // the row's block sums: hi column + lo column
+        const uint2 qh = lds64(fsx + zo), ql = lds64(fsx + zo + lo_off);
+        const float qe = __uint_as_float(qh.x) + __uint_as_float(ql.x), qo = __uint_as_float(qh.y) + __uint_as_float(ql.y);
+        acc[nt][0] = fmaf(-S.me.x, qe, acc[nt][0]);
+        acc[nt][0] = fmaf(-S.mo.x, qo, acc[nt][0]);
+        acc[nt][1] = fmaf(-S.me.y, qe, acc[nt][1]);
+        acc[nt][1] = fmaf(-S.mo.y, qo, acc[nt][1]);
+      }
     }
   }
 }

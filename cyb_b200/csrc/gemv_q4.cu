@@ -306,7 +306,7 @@ int32_t qeng_gemm_q4_decode(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
     if (handled || rc != QENG_OK) return rc;
   }
   if (w->fmt != QENG_FMT_Q4)
-    return qeng_fail(ctx, QENG_ERR_SHAPE, "gemm_q4: this shape (M=%lld, N=%lld, K=%lld) is outside what the streaming kernel takes for 8-bit blocks",
+    return qeng_fail(ctx, QENG_ERR_SHAPE, "gemm_q4: this shape (M=%lld, N=%lld, K=%lld) is outside what the streaming kernel takes for this block format",
                      (long long)M, (long long)w->N, (long long)w->K);
   const int split = (x_dtype == QENG_F32 && split_f32) ? 1 : 0;
   const int max_m = split ? 16 : 32;
@@ -355,7 +355,7 @@ int32_t qeng_gemm_q4(qeng_ctx* ctx, const qeng_weight* w, const void* x, int32_t
   fuse.epilogue = (flags & QENG_GEMM_ACCUMULATE) ? QENG_EPI_ACCUM : QENG_EPI_STORE;
   fuse.two_limbs = (flags & QENG_GEMM_FAST_F16) != 0;
   const bool split = x_dtype == QENG_F32 && !(flags & QENG_GEMM_FAST_F16);
-  const int64_t step = 16;  // rows per pass over the weights
+  const int64_t step = w->fmt == QENG_FMT_K4 ? 4 : 16;  // rows per pass over the weights
   const size_t esz = x_dtype == QENG_F32 ? 4 : 2;
   for (int64_t m0 = 0; m0 < M; m0 += step) {
     int64_t mm = M - m0 < step ? M - m0 : step;

@@ -35,7 +35,7 @@ struct StreamParams {
   // CTA's own loads are all issued
   const uint4* pf_qs;
   const uint2* pf_sc;
-  int pf_ntiles, pf_nchunks, pf_wchunk;
+  int pf_ntiles, pf_nchunks, pf_wchunk, pf_schunk;
   const uint4* qs;
   const uint2* sc;
   int ntiles, nchunks;
@@ -172,9 +172,10 @@ __device__ __forceinline__ void group_sync(int gi) { asm volatile("bar.sync %0, 
 //   kM2L2: two rows in two limbs, two blocks per fragment
 //   kMN  : NT tiles of four rows in two limbs, one block per fragment
 enum { kM1L3 = 0, kM1L2 = 1, kM2L2 = 2, kMN = 3 };
-template <int MODE, int NT, int kTG, bool Q8 = false>
+template <int MODE, int NT, int kTG, bool Q8 = false, bool KQ = false>
 __global__ void __launch_bounds__(kCT + 32 * (kTG == 0 ? 1 : kTG), 1) gemv_q4_stream_kernel(const StreamParams p) {
   constexpr uint32_t kWChunk = Q8 ? 1024u : 512u;  // bytes of the weight plane per 64-wide chunk of a row tile
+  constexpr uint32_t kSChunk = KQ ? 256u : 64u;    // bytes of the scale plane per chunk (f16 scales, or f32 scale + minimum)
   // kTG = 0: all 16 warps work on every tile and the per-tile reduction is deferred: each warp parks its
   // partial sums of a tile in shared memory and moves on; the CTA meets once at the end (or every
   // kDeferTiles tiles), where the warps sum the partials and run the epilogues of the tiles in parallel
@@ -187,9 +188,9 @@ __global__ void __launch_bounds__(kCT + 32 * (kTG == 0 ? 1 : kTG), 1) gemv_q4_st
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int NS = p.nstages;
-  const uint32_t stage_bytes = (uint32_t)p.stage_chunks * (kWChunk + 64u);
+  const uint32_t stage_bytes = (uint32_t)p.stage_chunks * (kWChunk + kSChunk);
   const int sl_alloc = MODE == kM1L2 ? (p.slice_chunks + 1) & ~1 : p.slice_chunks;
-  const XLayout L = x_layout(p.cols, sl_alloc, kZeroed);
+  const XLayout L = x_layout(p.cols, sl_alloc, kZeroed, 0, KQ);
   // carve: ring | activations (128-byte aligned) | reduction buffers | slice accumulators | barriers
   unsigned char* ring = smem;
   unsigned char* xreg = smem + (((size_t)NS * stage_bytes + 127) & ~(size_t)127);
@@ -267,9 +268,10 @@ __global__ void __launch_bounds__(kCT + 32 * (kTG == 0 ? 1 : kTG), 1) gemv_q4_st
             const uint32_t bar = smem_u32(full + s);
             const uint32_t dst = smem_u32(ring) + (uint32_t)s * stage_bytes;
             const size_t chunk = (size_t)tile * p.nchunks + c0;
-            mbar_expect_tx(bar, (uint32_t)nc * (kWChunk + 64u));
+            mbar_expect_tx(bar, (uint32_t)nc * (kWChunk + kSChunk));
             bulk_g2s(dst, reinterpret_cast<const char*>(p.qs) + chunk * kWChunk, (uint32_t)nc * kWChunk, bar);
-            bulk_g2s(dst + (uint32_t)p.stage_chunks * kWChunk, p.sc + chunk * 8, (uint32_t)nc * 64u, bar);
+            bulk_g2s(dst + (uint32_t)p.stage_chunks * kWChunk, reinterpret_cast<const char*>(p.sc) + chunk * kSChunk,
+                     (uint32_t)nc * kSChunk, bar);
           }
         }
       }
@@ -280,7 +282,7 @@ __global__ void __launch_bounds__(kCT + 32 * (kTG == 0 ? 1 : kTG), 1) gemv_q4_st
     // Own loads are all in flight: ask L2 for this CTA's share of the next matrix, so that HBM
     // does not idle while the consumers drain the ring and the next kernel starts up.
     if (pg == 0 && p.pf_qs != nullptr) {
-      const uint32_t qb = (uint32_t)p.pf_nchunks * (uint32_t)p.pf_wchunk, sb = (uint32_t)p.pf_nchunks * 64u;
+      const uint32_t qb = (uint32_t)p.pf_nchunks * (uint32_t)p.pf_wchunk, sb = (uint32_t)p.pf_nchunks * (uint32_t)p.pf_schunk;
       for (int tile = blockIdx.x + gridDim.x * lane; tile < p.pf_ntiles; tile += gridDim.x * 32) {
         const char* q = reinterpret_cast<const char*>(p.pf_qs) + (size_t)tile * qb;
         for (uint32_t o = 0; o < qb; o += 32768u) l2_prefetch(q + o, min(32768u, qb - o));
@@ -348,7 +350,7 @@ __global__ void __launch_bounds__(kCT + 32 * (kTG == 0 ? 1 : kTG), 1) gemv_q4_st
   auto put = [&](int m, int grp, const float (&v)[8], bool valid) {
     const uint32_t c0 = (uint32_t)(kLimbs * m);
     quantise_group<kLimbs>(v, valid, xbase + L.xq + c0 * L.col_stride, L.col_stride, xbase + L.zin + c0 * L.zs,
-                           xbase + L.fex + c0 * L.zs, L.zs, (grp >> 2) * 32, grp & 3);
+                           xbase + L.fex + c0 * L.zs, L.zs, (grp >> 2) * 32, grp & 3, KQ ? xbase + L.fsx + c0 * L.zs : 0u);
   };
   const int ngroups = L.nblk * 4;  // (block, quad lane) groups of the staged slice, padding included
 
@@ -561,9 +563,9 @@ __global__ void __launch_bounds__(kCT + 32 * (kTG == 0 ? 1 : kTG), 1) gemv_q4_st
         // the warp that takes a stage's first item rotates, so that stages whose item count is not a
         // multiple of 16 load the warps evenly over a tile
         const int wr = (warp + kCW - rot) & (kCW - 1);
-        if (MODE == kM1L3) consume_m1l3<kCW, Q8>(acc1, wb, sb, nc, blk0, L, xbase, wr, lane);
-        else if (MODE == kM1L2) consume_g4<kCW, Q8>(acc1, wb, sb, nc, blk0, L, xbase, wr, lane);
-        else consume_g2<kCW, Q8>(acc1, wb, sb, nc, blk0, L, xbase, wr, lane);
+        if (MODE == kM1L3) consume_m1l3<kCW, Q8, KQ>(acc1, wb, sb, nc, blk0, L, xbase, wr, lane);
+        else if (MODE == kM1L2) consume_g4<kCW, Q8, KQ>(acc1, wb, sb, nc, blk0, L, xbase, wr, lane);
+        else consume_g2<kCW, Q8, KQ>(acc1, wb, sb, nc, blk0, L, xbase, wr, lane);
         rot = (rot + (MODE == kM1L2 ? (nc + 1) >> 1 : nc)) & (kCW - 1);
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(empty + s));
@@ -638,10 +640,10 @@ __global__ void __launch_bounds__(kCT + 32 * (kTG == 0 ? 1 : kTG), 1) gemv_q4_st
         const uint32_t wb = smem_u32(ring) + (uint32_t)s * stage_bytes;
         const uint32_t sb = wb + (uint32_t)p.stage_chunks * kWChunk;
         const int blk0 = (c0 - cs0) * 2;
-        if (MODE == kM1L3) consume_m1l3<kGW, Q8>(acc1, wb, sb, nc, blk0, L, xb, wi, lane);
-        else if (MODE == kM1L2) consume_g4<kGW, Q8>(acc1, wb, sb, nc, blk0, L, xb, wi, lane);
-        else if (MODE == kM2L2) consume_g2<kGW, Q8>(acc1, wb, sb, nc, blk0, L, xb, wi, lane);
-        else consume_g1<kGW, NT, Q8>(accn, wb, sb, nc, blk0, L, xb, p.cols, wi, lane);
+        if (MODE == kM1L3) consume_m1l3<kGW, Q8, KQ>(acc1, wb, sb, nc, blk0, L, xb, wi, lane);
+        else if (MODE == kM1L2) consume_g4<kGW, Q8, KQ>(acc1, wb, sb, nc, blk0, L, xb, wi, lane);
+        else if (MODE == kM2L2) consume_g2<kGW, Q8, KQ>(acc1, wb, sb, nc, blk0, L, xb, wi, lane);
+        else consume_g1<kGW, NT, Q8, KQ>(accn, wb, sb, nc, blk0, L, xb, p.cols, wi, lane);
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(empty + s));  // this warp is done with the stage
         QENG_TOCK(tc1, 9, warp == 0);
@@ -697,12 +699,12 @@ __global__ void __launch_bounds__(kCT + 32 * (kTG == 0 ? 1 : kTG), 1) gemv_q4_st
   if (failed && lane == 0) atomicExch(p.status, 4);
 }
 
-template <int MODE, int NT, int kTG, bool Q8 = false>
+template <int MODE, int NT, int kTG, bool Q8 = false, bool KQ = false>
 int32_t launch_stream(qeng_ctx* ctx, const StreamParams& p, size_t smem, cudaStream_t stream) {
   static bool configured_on[64] = {};  // the opt-in shared-memory size is set per device
   bool& configured = configured_on[ctx->device & 63];
   if (!configured) {
-    QENG_CUDA(ctx, cudaFuncSetAttribute(gemv_q4_stream_kernel<MODE, NT, kTG, Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    QENG_CUDA(ctx, cudaFuncSetAttribute(gemv_q4_stream_kernel<MODE, NT, kTG, Q8, KQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     configured = true;
   }
   const int grid = p.ntiles < ctx->sm_count ? p.ntiles : ctx->sm_count;
@@ -718,7 +720,7 @@ int32_t launch_stream(qeng_ctx* ctx, const StreamParams& p, size_t smem, cudaStr
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = ctx->pdl ? 1 : 0;
-  QENG_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4_stream_kernel<MODE, NT, kTG, Q8>, p));
+  QENG_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4_stream_kernel<MODE, NT, kTG, Q8, KQ>, p));
   return QENG_OK;
 }
 
@@ -737,6 +739,8 @@ struct StreamFit {
 StreamFit stream_fit(const qeng_ctx* ctx, const qeng_weight* w, int64_t M, bool two_limbs) {
   StreamFit f = {};
   if (M < 1 || M > 16) return f;
+  const bool kq = w->fmt == QENG_FMT_K4;
+  if (kq && M > 4) return f;  // 4-bit blocks with minima: up to 4 rows per pass (no activation images)
   f.mode = M == 1 ? (two_limbs ? kM1L2 : kM1L3) : (M == 2 ? kM2L2 : kMN);
   f.cols = f.mode == kM1L3 ? 3 : 2 * (int)M;
   f.NT = f.mode == kMN ? (int)((M + 3) / 4) : 1;
@@ -752,8 +756,8 @@ StreamFit stream_fit(const qeng_ctx* ctx, const qeng_weight* w, int64_t M, bool 
     const int nsl = (nch + slice - 1) / slice;
     if (!f.imaged && nsl == 1 && nch * 64 > 8 * kGroups * kCT) return false;  // single-slice staging goes through registers: K <= 12288
     const int alloc = f.mode == kM1L2 ? (slice + 1) & ~1 : slice;
-    const XLayout L = x_layout(f.cols, alloc, f.mode != kMN);
-    f.defer = f.mode != kMN && nsl == 1 && (ctx->stream_groups == 0 || w->fmt == QENG_FMT_Q8);
+    const XLayout L = x_layout(f.cols, alloc, f.mode != kMN, 0, kq);
+    f.defer = f.mode != kMN && nsl == 1 && (ctx->stream_groups == 0 || w->fmt != QENG_FMT_Q4);
     const size_t red = (size_t)(f.defer ? kDeferTiles : 2) * kCW * kMR * 16 * 4;  // grouped: the same for every number of groups
     const size_t accs = nsl > 1 ? (size_t)tiles_per_cta * kMR * 16 * 4 : 0;
     const size_t xarea = f.imaged ? 2 * (((size_t)L.bytes + 127) & ~(size_t)127) : L.bytes;
@@ -761,7 +765,7 @@ StreamFit stream_fit(const qeng_ctx* ctx, const qeng_weight* w, int64_t M, bool 
     f.image_slice_bytes = (L.bytes + 127u) & ~127u;
     const int cap = ctx->stream_stage_chunks > 0 ? ctx->stream_stage_chunks : kStageChunks;
     const int sc = slice < cap ? slice : cap;
-    const size_t slot = (size_t)sc * (w->fmt == QENG_FMT_Q8 ? 1088 : 576);
+    const size_t slot = (size_t)sc * (w->fmt == QENG_FMT_Q8 ? 1088 : (kq ? 768 : 576));
     if (fixed + 2 * slot > budget) return false;
     int ns = (int)((budget - fixed) / slot);
     if (ns > kMaxStages) ns = kMaxStages;
@@ -820,6 +824,7 @@ int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
   p.pf_qs = nx ? nx->qs : nullptr; p.pf_sc = nx ? nx->sc : nullptr;
   p.pf_ntiles = nx ? (int)nx->ntiles : 0; p.pf_nchunks = nx ? (int)nx->nchunks : 0;
   p.pf_wchunk = nx && nx->fmt == QENG_FMT_Q8 ? 1024 : 512;
+  p.pf_schunk = nx && nx->fmt == QENG_FMT_K4 ? 256 : 64;
   p.qkv = qeng_qkv_epi();
   if (fuse.epilogue == QENG_EPI_QKV) {
     if (!fuse.qkv) return qeng_fail(ctx, QENG_ERR_ARG, "gemm_q4: fused q|k|v epilogue without its arguments");
@@ -891,6 +896,17 @@ int32_t qeng_gemm_q4_stream(qeng_ctx* ctx, const qeng_weight* w, const void* x, 
 #define QENG_STREAM_CASE(MODE_, NT_)                                                   \
   (tg == 4 ? launch_stream<MODE_, NT_, 4>(ctx, p, f.smem, stream)                      \
            : (tg == 2 ? launch_stream<MODE_, NT_, 2>(ctx, p, f.smem, stream) : launch_stream<MODE_, NT_, 1>(ctx, p, f.smem, stream)))
+  if (w->fmt == QENG_FMT_K4) {  // 4-bit blocks with per-block scale and minimum: the deferred forms, or one tile group
+    if (f.defer) {
+      if (f.mode == kM1L3) return launch_stream<kM1L3, 1, 0, false, true>(ctx, p, f.smem, stream);
+      if (f.mode == kM1L2) return launch_stream<kM1L2, 1, 0, false, true>(ctx, p, f.smem, stream);
+      return launch_stream<kM2L2, 1, 0, false, true>(ctx, p, f.smem, stream);
+    }
+    if (f.mode == kM1L3) return launch_stream<kM1L3, 1, 1, false, true>(ctx, p, f.smem, stream);
+    if (f.mode == kM1L2) return launch_stream<kM1L2, 1, 1, false, true>(ctx, p, f.smem, stream);
+    if (f.mode == kM2L2) return launch_stream<kM2L2, 1, 1, false, true>(ctx, p, f.smem, stream);
+    return launch_stream<kMN, 1, 1, false, true>(ctx, p, f.smem, stream);  // 3 or 4 rows
+  }
   if (w->fmt == QENG_FMT_Q8) {  // 8-bit blocks: the deferred forms, or one tile group
     if (f.defer) {
       if (f.mode == kM1L3) return launch_stream<kM1L3, 1, 0, true>(ctx, p, f.smem, stream);

@@ -230,7 +230,7 @@ int32_t qeng_weight_pack_q4(qeng_ctx* ctx, const uint8_t* q, const uint16_t* s, 
 
 int32_t qeng_weight_unpack_q4(qeng_ctx* ctx, const qeng_weight* w, uint8_t* q, uint16_t* s) {
   if (!ctx || !w || !q || !s) return qeng_fail(ctx, QENG_ERR_ARG, "weight_unpack_q4: null argument");
-  if (w->fmt != QENG_FMT_Q4) return qeng_fail(ctx, QENG_ERR_ARG, "weight_unpack_q4: the weight holds 8-bit blocks");
+  if (w->fmt != QENG_FMT_Q4) return qeng_fail(ctx, QENG_ERR_ARG, "weight_unpack_q4: the weight holds another block format");
   QENG_CUDA(ctx, cudaSetDevice(ctx->device));
   uint8_t* dq = nullptr;
   uint16_t* ds = nullptr;
@@ -253,6 +253,11 @@ int32_t qeng_weight_unpack_q4(qeng_ctx* ctx, const qeng_weight* w, uint8_t* q, u
 
 int32_t qeng_weight_dequant_f32(qeng_ctx* ctx, const qeng_weight* w, float* out, void* stream) {
   if (!ctx || !w || !out) return qeng_fail(ctx, QENG_ERR_ARG, "weight_dequant_f32: null argument");
+  if (w->fmt == QENG_FMT_K4) {
+    qeng_weight_dequant_k4(w, out, (cudaStream_t)stream);
+    QENG_LAUNCH_CHECK(ctx);
+    return QENG_OK;
+  }
   if (w->fmt == QENG_FMT_Q8) {
     qeng_weight_dequant_q8(w, out, (cudaStream_t)stream);
     QENG_LAUNCH_CHECK(ctx);
@@ -282,7 +287,7 @@ int32_t qeng_weight_free(qeng_ctx* ctx, qeng_weight* w) {
 
 int64_t qeng_weight_rows(const qeng_weight* w) { return w ? w->N : 0; }
 int64_t qeng_weight_cols(const qeng_weight* w) { return w ? w->K : 0; }
-int32_t qeng_weight_format(const qeng_weight* w) { return w && w->fmt == QENG_FMT_Q8 ? 8 : 4; }
+int32_t qeng_weight_format(const qeng_weight* w) { return !w ? 0 : (w->fmt == QENG_FMT_Q8 ? 8 : (w->fmt == QENG_FMT_K4 ? 14 : 4)); }
 int64_t qeng_weight_device_bytes(const qeng_weight* w) { return w ? w->bytes : 0; }
 
 }  // extern "C"

@@ -23,15 +23,16 @@
 //    an m16n8k16 MMA over that chunk;
 //  * scale plane: [tile][chunk][g 0..7] one uint2 = four f16:
 //       (row g, blk 2c), (row g+8, blk 2c), (row g, blk 2c+1), (row g+8, blk 2c+1).
-enum { QENG_FMT_Q4 = 0, QENG_FMT_Q8 = 1 };
+enum { QENG_FMT_Q4 = 0, QENG_FMT_Q8 = 1, QENG_FMT_K4 = 2 };
 
 struct qeng_weight {
-  int fmt = QENG_FMT_Q4;  // Q4: 4-bit codes, w = (c - 8) s; Q8: signed bytes, w = q s (both: one f16 s per 32-block)
+  int fmt = QENG_FMT_Q4;  // Q4: 4-bit codes, w = (c - 8) s; Q8: signed bytes, w = q s (both: one f16 s per 32-block);
+                          // K4: 4-bit codes with f32 scale and minimum per 32-block, w = D c - M (the K-quant super-blocks, expanded)
   int64_t N, K;        // logical shape
   int64_t ntiles;      // N / 16
   int64_t nchunks;     // Kp / 64
   uint4* qs;           // weight plane: Q4 ntiles*nchunks*32 uint4 (nibbles), Q8 ntiles*nchunks*64 uint4 (bytes)
-  uint2* sc;           // scale plane,  ntiles*nchunks*8 uint2
+  uint2* sc;           // scale plane,  ntiles*nchunks*8 uint2 (K4: ntiles*nchunks*256 bytes)
   int64_t bytes;       // device bytes held
   const qeng_weight* next = nullptr;  // matrix the caller multiplies by after this one (L2 prefetch hint)
 };
@@ -225,6 +226,11 @@ int32_t qeng_gemm_q4_prefill(qeng_ctx* ctx, const qeng_weight* w, const void* x,
 constexpr int64_t kPrefillRows = 256;  // from this many rows on, matmuls take the tensor-core path
 
 void qeng_weight_dequant_q8(const qeng_weight* w, float* out, cudaStream_t stream);
+void qeng_weight_dequant_k4(const qeng_weight* w, float* out, cudaStream_t stream);
+// 4-bit codes [N][K] and f32 (scale, minimum) pairs [N][K/32][2] (HOST) -> device weight; and the
+// expansion of Q4_K super-blocks into that form
+int32_t qeng_weight_pack_k4(qeng_ctx* ctx, const uint8_t* q, const float* dm, int64_t N, int64_t K, qeng_weight** out);
+int32_t qeng_q4k_expand(qeng_ctx* ctx, const uint8_t* blocks, int64_t N, int64_t K, std::vector<uint8_t>* q, std::vector<float>* dm);
 
 #if defined(QENG_TRACE) && defined(__CUDACC__)
 // tuning builds only: a launch log behind the status word (status + 256 bytes: a counter, then records

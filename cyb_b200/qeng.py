@@ -88,6 +88,8 @@ _sig("qeng_weight_pack_q4", _i32, _vp, _vp, _vp, _i64, _i64, C.POINTER(_vp))
 _sig("qeng_weight_unpack_q4", _i32, _vp, _vp, _vp, _vp)
 _sig("qeng_weight_dequant_f32", _i32, _vp, _vp, _vp, _vp)
 _sig("qeng_weight_quantize_q4", _i32, _vp, _vp, _i32, _i64, _i64, _i64, C.POINTER(_vp), _vp)
+_sig("qeng_weight_pack_q4k", _i32, _vp, _vp, _i64, _i64, C.POINTER(_vp))
+_sig("qeng_weight_unpack_k4", _i32, _vp, _vp, _vp, _vp)
 _sig("qeng_weight_pack_q8", _i32, _vp, _vp, _vp, _i64, _i64, C.POINTER(_vp))
 _sig("qeng_weight_unpack_q8", _i32, _vp, _vp, _vp, _vp)
 _sig("qeng_weight_quantize_q8", _i32, _vp, _vp, _i32, _i64, _i64, _i64, C.POINTER(_vp), _vp)
@@ -118,6 +120,7 @@ _sig("qeng_decoder_create", _i32, _vp, C.POINTER(ModelCfg), C.POINTER(_vp))
 _sig("qeng_decoder_free", _i32, _vp, _vp)
 _sig("qeng_decoder_load_matrix", _i32, _vp, _vp, _i32, _i32, _vp, _vp, _i64, _i64)
 _sig("qeng_decoder_load_matrix_q8", _i32, _vp, _vp, _i32, _i32, _vp, _vp, _i64, _i64)
+_sig("qeng_decoder_load_matrix_q4k", _i32, _vp, _vp, _i32, _i32, _vp, _i64, _i64)
 _sig("qeng_decoder_load_norm", _i32, _vp, _vp, _i32, _i32, _vp)
 _sig("qeng_decoder_load_head", _i32, _vp, _vp, _vp, _vp, _vp)
 _sig("qeng_decoder_reset", _i32, _vp, _vp, _i32)
@@ -229,6 +232,15 @@ class Context:
             raise QengError(-2, "scale shape %s does not match codes %s" % (s.shape, q.shape))
         h = _vp()
         self.check(_lib.qeng_weight_pack_q4(self.h, _np_ptr(q), _np_ptr(s), n, k, C.byref(h)))
+        return Weight(self, h)
+
+    def pack_q4k(self, blocks, n, k):
+        """blocks: uint8 array of n * k / 256 Q4_K super-blocks of 144 bytes (row-major)."""
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1)
+        if blocks.size != n * (k // 256) * 144:
+            raise QengError(-2, "Q4_K data of %d bytes does not match [%d, %d]" % (blocks.size, n, k))
+        h = _vp()
+        self.check(_lib.qeng_weight_pack_q4k(self.h, _np_ptr(blocks), n, k, C.byref(h)))
         return Weight(self, h)
 
     def pack_q8(self, q, s):
@@ -375,12 +387,18 @@ class Context:
 class Weight:
     def __init__(self, ctx, h, q8=None):
         self.ctx, self.h = ctx, h
-        self.q8 = _lib.qeng_weight_format(h) == 8
+        self.fmt = _lib.qeng_weight_format(h)
+        self.q8 = self.fmt == 8
         self.rows = _lib.qeng_weight_rows(h)
         self.cols = _lib.qeng_weight_cols(h)
         self.device_bytes = _lib.qeng_weight_device_bytes(h)
 
     def unpack(self):
+        if self.fmt == 14:  # K-quant: codes and f32 (scale, minimum) pairs
+            q = np.empty((self.rows, self.cols), np.uint8)
+            dm = np.empty((self.rows, self.cols // 32, 2), np.float32)
+            self.ctx.check(_lib.qeng_weight_unpack_k4(self.ctx.h, self.h, _np_ptr(q), _np_ptr(dm)))
+            return q, dm
         q = np.empty((self.rows, self.cols), np.int8 if self.q8 else np.uint8)
         s = np.empty((self.rows, self.cols // 32), np.float16)
         fn = _lib.qeng_weight_unpack_q8 if self.q8 else _lib.qeng_weight_unpack_q4
@@ -453,6 +471,11 @@ class Decoder:
         self.h = h
         self.batch = 0
 
+    def load_matrix_q4k(self, layer, which, blocks, n, k):
+        """blocks: the matrix as Q4_K super-blocks (uint8, n * k / 256 * 144 bytes)."""
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1)
+        self.ctx.check(_lib.qeng_decoder_load_matrix_q4k(self.ctx.h, self.h, layer, which, _np_ptr(blocks), n, k))
+
     def load_matrix(self, layer, which, q, s):
         """q uint8 codes 0..15 (4-bit blocks) or int8 bytes (8-bit blocks), s float16 scales."""
         q8 = np.asarray(q).dtype == np.int8
@@ -509,7 +532,8 @@ class Decoder:
         w.ctx, w.h = self.ctx, h
         w.rows, w.cols = _lib.qeng_weight_rows(h), _lib.qeng_weight_cols(h)
         w.device_bytes = _lib.qeng_weight_device_bytes(h)
-        w.q8 = _lib.qeng_weight_format(h) == 8
+        w.fmt = _lib.qeng_weight_format(h)
+        w.q8 = w.fmt == 8
         w.free = lambda: None  # borrowed
         return w
 
@@ -557,7 +581,10 @@ def load_decoder_weights(dec, W, cfg):
     names = ["wq", "wk", "wv", "wo", "wgate", "wup", "wdown"]
     for l, lw in enumerate(W["layers"]):
         for i, nm in enumerate(names):
-            dec.load_matrix(l, i, *lw[nm])
+            if nm + "_q4k" in lw:  # the matrix as Q4_K super-blocks (lw[nm] then holds its expansion)
+                dec.load_matrix_q4k(l, i, lw[nm + "_q4k"], *lw[nm][0].shape)
+            else:
+                dec.load_matrix(l, i, *lw[nm])
         dec.load_norm(l, 0, lw["norm1"])
         dec.load_norm(l, 1, lw["norm2"])
         if "qnorm" in lw:  # optional per-head gains of q and k

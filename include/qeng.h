@@ -148,11 +148,23 @@ int32_t qeng_weight_unpack_q8(qeng_ctx* ctx, const qeng_weight* w, int8_t* q, ui
  * q = round-half-away(x * (1/d)).  Asynchronous on `stream`. */
 int32_t qeng_weight_quantize_q8(qeng_ctx* ctx, const void* w_dev, int32_t x_dtype, int64_t N, int64_t K, int64_t ld,
                                 qeng_weight** out, void* stream);
+/* ---- "K-quant" 4-bit weights ("needs fused Q4_K matmul": what kept a catalog model from loading,
+ *      decide/model-lifecycle.md:175).  blocks: HOST, row-major [N][K/256] super-blocks of 144 bytes in
+ * the published Q4_K layout (f16 d, f16 dmin, 12 bytes holding eight 6-bit scales and eight 6-bit
+ * minima, 128 bytes of codes: of every 32 bytes the low nibbles are sub-block 2i, the high nibbles
+ * sub-block 2i+1); w = (d * sc_j) * code - (dmin * m_j).  K % 256 == 0, N % 16 == 0.  The weight is
+ * expanded to per-32-block f32 (scale, minimum) pairs on the device (0.75 B per weight) and taken by
+ * qeng_gemm_q4 / qeng_gemv_q4 (decode kernel, 4 rows per pass), qeng_weight_dequant_f32, the getters. */
+int32_t qeng_weight_pack_q4k(qeng_ctx* ctx, const uint8_t* blocks, int64_t N, int64_t K, qeng_weight** out);
+/* Inverse of the device layout (the bit-exactness check): codes [N][K] (0..15) and f32 pairs
+ * (scale, minimum) [N][K/32][2] to HOST buffers. */
+int32_t qeng_weight_unpack_k4(qeng_ctx* ctx, const qeng_weight* w, uint8_t* q, float* scale_min);
 int32_t qeng_weight_free(qeng_ctx* ctx, qeng_weight* w);
 int64_t qeng_weight_rows(const qeng_weight* w);
 int64_t qeng_weight_cols(const qeng_weight* w);
 int64_t qeng_weight_device_bytes(const qeng_weight* w);
-/* Bits per weight of the block format held: 4 or 8. */
+/* The block format held: 4 (4-bit blocks, f16 scale), 8 (8-bit blocks), 14 (4-bit K-quant blocks with
+ * scale and minimum). */
 int32_t qeng_weight_format(const qeng_weight* w);
 /* Hint: the matmul the caller runs after one over `w` is over `next` (NULL clears the hint).
  * The decode kernel then asks L2 for `next` while it finishes `w`, so that HBM keeps
@@ -274,6 +286,10 @@ int32_t qeng_decoder_load_matrix(qeng_ctx* ctx, qeng_decoder* dec, int32_t layer
  * blocks run through the decode kernels in passes of 16 rows. */
 int32_t qeng_decoder_load_matrix_q8(qeng_ctx* ctx, qeng_decoder* dec, int32_t layer, int32_t which,
                                     const int8_t* q, const uint16_t* s, int64_t N, int64_t K);
+/* The same for Q4_K super-blocks (see qeng_weight_pack_q4k); decode steps of up to 4 sequences take
+ * such layers in one pass, larger batches and prompts in passes of 4 rows. */
+int32_t qeng_decoder_load_matrix_q4k(qeng_ctx* ctx, qeng_decoder* dec, int32_t layer, int32_t which,
+                                     const uint8_t* blocks, int64_t N, int64_t K);
 /* RMSNorm gains of a layer (which = 0: before attention, 1: before FFN), HOST f32[d_model].
  * which = 2 / 3: optional per-head gains of q / k, HOST f32[head_dim] ("QK-norm", named as a
  * blocker for the catalog's Qwen3 models in decide/model-lifecycle.md:173-176): every q and k head

@@ -87,8 +87,77 @@ def centred(q):
 
 
 def dequant(q, s, dtype=np.float64):
-    """w = (q-8)*s for 4-bit codes (uint8), w = q*s for 8-bit blocks (int8); exact in f32 and f64."""
+    """w = (q-8)*s for 4-bit codes (uint8), w = q*s for 8-bit blocks (int8); exact in f32 and f64.
+    K-quant weights come as codes (uint8) with s = f32 pairs [N, K/32, 2] (scale D, minimum M):
+    w = D*q - M (a product and a difference, each rounded when dtype is float32)."""
+    s = np.asarray(s)
+    if s.ndim == 3:
+        D = np.repeat(s[..., 0].astype(dtype), BLOCK, axis=1)
+        M = np.repeat(s[..., 1].astype(dtype), BLOCK, axis=1)
+        return (D * np.asarray(q).astype(dtype)).astype(dtype) - M
     return centred(q).astype(dtype) * np.repeat(s.astype(dtype), BLOCK, axis=1)
+
+
+# ---- "K-quant" 4-bit super-blocks (the published Q4_K layout; "needs fused Q4_K matmul",
+# decide/model-lifecycle.md:175) -------------------------------------------------------------
+Q4K_BYTES = 144  # per 256 weights: f16 d, f16 dmin, 12 bytes of 6-bit scales / minima, 128 bytes of codes
+
+
+def q4k_pack(d, dmin, sc, mn, codes):
+    """Build super-blocks from their fields: d, dmin float16 [N, S]; sc, mn uint8 [N, S, 8] (0..63);
+    codes uint8 [N, S*256] (0..15).  Returns uint8 [N, S, 144]."""
+    n, S = d.shape
+    out = np.zeros((n, S, Q4K_BYTES), np.uint8)
+    out[..., 0:2] = np.ascontiguousarray(d, np.float16).reshape(n, S, 1).view(np.uint8)
+    out[..., 2:4] = np.ascontiguousarray(dmin, np.float16).reshape(n, S, 1).view(np.uint8)
+    sc, mn = sc.astype(np.uint8), mn.astype(np.uint8)
+    p = out[..., 4:16]
+    for j in range(4):
+        p[..., j] = (sc[..., j] & 63) | ((sc[..., j + 4] >> 4) << 6)
+        p[..., j + 4] = (mn[..., j] & 63) | ((mn[..., j + 4] >> 4) << 6)
+        p[..., j + 8] = (sc[..., j + 4] & 15) | ((mn[..., j + 4] & 15) << 4)
+    c = codes.reshape(n, S, 4, 2, 32)  # pairs of sub-blocks share 32 bytes: low nibbles 2i, high nibbles 2i+1
+    out[..., 16:] = (c[:, :, :, 0, :] | (c[:, :, :, 1, :] << 4)).reshape(n, S, 128)
+    return out
+
+
+def q4k_unpack(blocks, n, k):
+    """Super-blocks -> (codes uint8 [n, k], pairs float32 [n, k/32, 2] = (d*sc_j, dmin*m_j))."""
+    b = np.ascontiguousarray(blocks, np.uint8).reshape(n, k // 256, Q4K_BYTES)
+    d = b[..., 0:2].copy().view(np.float16)[..., 0].astype(np.float32)
+    dmin = b[..., 2:4].copy().view(np.float16)[..., 0].astype(np.float32)
+    p = b[..., 4:16]
+    sc = np.empty(b.shape[:2] + (8,), np.uint8)
+    mn = np.empty_like(sc)
+    for j in range(4):
+        sc[..., j] = p[..., j] & 63
+        mn[..., j] = p[..., j + 4] & 63
+        sc[..., j + 4] = (p[..., j + 8] & 15) | ((p[..., j] >> 6) << 4)
+        mn[..., j + 4] = (p[..., j + 8] >> 4) | ((p[..., j + 4] >> 6) << 4)
+    qs = b[..., 16:].reshape(n, k // 256, 4, 32)
+    codes = np.stack([qs & 15, qs >> 4], axis=3).reshape(n, k)
+    dm = np.stack([d[..., None] * sc.astype(np.float32), dmin[..., None] * mn.astype(np.float32)], axis=-1)
+    return codes.astype(np.uint8), dm.reshape(n, k // 32, 2).astype(np.float32)
+
+
+def make_q4k(rng, n, k, wild=False):
+    """Synthetic Q4_K matrix: (codes, pairs, blocks).  Default: magnitudes like make_q4's and minima
+    near 8 scales, i.e. roughly zero-mean weights as a quantiser of real tensors produces; wild = True
+    draws scales and minima independently (weights with large per-block offsets)."""
+    S = k // 256
+    d = (rng.uniform(0.002, 0.02, (n, S)) / 32.0).astype(np.float16)
+    sc = rng.integers(1, 64, (n, S, 8)).astype(np.uint8)
+    if wild:
+        dmin = (rng.uniform(0.002, 0.02, (n, S)) / 4.0).astype(np.float16)
+        mn = rng.integers(0, 64, (n, S, 8)).astype(np.uint8)
+    else:
+        dmin = (d.astype(np.float32) * 8.0).astype(np.float16)
+        mn = np.clip(np.rint(sc * rng.uniform(0.8, 1.2, sc.shape)), 0, 63).astype(np.uint8)
+    codes = rng.integers(0, 16, (n, k), dtype=np.uint8)
+    blocks = q4k_pack(d, dmin, sc, mn, codes)
+    q, dm = q4k_unpack(blocks, n, k)
+    assert np.array_equal(q, codes)
+    return q, dm, blocks
 
 
 def quantize_q8(w):
@@ -145,6 +214,8 @@ def dequant_bf16(q, s):
 
 def gemm_q4(x, q, s):
     """y[m,n] = sum_b s[n,b] * sum_{k in b} x[m,k]*(q[n,k]-8), float64."""
+    if np.asarray(s).ndim == 3:  # K-quant pairs: scale and minimum per block
+        return gemm_q4_fast(x, q, s)
     m, k = x.shape
     n = q.shape[0]
     nb = k // BLOCK
@@ -309,7 +380,12 @@ def make_decoder_weights(cfg, seed=5, fmt="q4"):
     for l in range(cfg.layers):
         lw = {"norm1": np.ones(cfg.d, np.float32), "norm2": np.ones(cfg.d, np.float32)}
         for j, (name, n, k) in enumerate(shapes):
-            lw[name] = (make_q8 if fmt == "q8" else make_q4)(g(2 + 7 * l + j), n, k)
+            if fmt == "q4k":
+                q, dm, blocks = make_q4k(g(2 + 7 * l + j), n, k)
+                lw[name] = (q, dm)
+                lw[name + "_q4k"] = blocks
+            else:
+                lw[name] = (make_q8 if fmt == "q8" else make_q4)(g(2 + 7 * l + j), n, k)
         W["layers"].append(lw)
     return W
 

@@ -65,7 +65,10 @@ def write_model(path, cfg, W, linear_dtype="Q4", tie_head=False, name="sample"):
     for l, lw in enumerate(W["layers"]):
         pre = "model.layers.%d." % l
         for key, hf in HF.items():
-            linear(pre + hf + ".weight", *lw[key])
+            if key + "_q4k" in lw:  # K-quant super-blocks are stored as they are
+                add(pre + hf + ".weight", "Q4_K", list(lw[key][0].shape), np.ascontiguousarray(lw[key + "_q4k"], np.uint8).tobytes())
+            else:
+                linear(pre + hf + ".weight", *lw[key])
         add(pre + "input_layernorm.weight", "F32", [cfg.d], np.asarray(lw["norm1"], np.float32).tobytes())
         add(pre + "post_attention_layernorm.weight", "F16", [cfg.d], np.asarray(lw["norm2"], np.float16).tobytes())
         if "qnorm" in lw:

@@ -51,16 +51,16 @@ def test_malformed_containers_are_rejected(built_lib, tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("linear_dtype,tie", [("Q4", False), ("F32", False), ("F16", True), ("Q8", False)])
+@pytest.mark.parametrize("linear_dtype,tie", [("Q4", False), ("F32", False), ("F16", True), ("Q8", False), ("Q4_K", False)])
 def test_decoder_loaded_from_a_file_equals_one_loaded_from_arrays(ctx, tmp_path, linear_dtype, tie):
     from cyb_b200 import qeng
     cfg = ref.DecoderConfig(**CFG)
-    W = ref.make_decoder_weights(cfg, seed=5, fmt="q8" if linear_dtype == "Q8" else "q4")
+    W = ref.make_decoder_weights(cfg, seed=5, fmt={"Q8": "q8", "Q4_K": "q4k"}.get(linear_dtype, "q4"))
     if tie:
         W["lm_head"] = W["emb"]
     path = os.path.join(tmp_path, "toy.model")
     mfw.write_model(path, cfg, W, linear_dtype=linear_dtype, tie_head=tie)
-    if linear_dtype not in ("Q4", "Q8"):
+    if linear_dtype not in ("Q4", "Q8", "Q4_K"):
         # float weights are quantised at load: what the decoder must then hold is the oracle's
         # quantisation of the stored (rounded) matrix, not the codes the file was made from
         W = dict(W, layers=[dict(lw) for lw in W["layers"]])
@@ -92,7 +92,7 @@ def test_decoder_loaded_from_a_file_equals_one_loaded_from_arrays(ctx, tmp_path,
         for i in range(4):
             qa, sa = a.weight(l, i).unpack()
             qb, sb = b.weight(l, i).unpack()
-            assert np.array_equal(qa, qb) and np.array_equal(sa.view(np.uint16), sb.view(np.uint16))
+            assert np.array_equal(qa, qb) and np.array_equal(sa.view(np.uint8), sb.view(np.uint8))
     # a decoder of another shape refuses the file
     c = ctx.decoder(**{**kw, "ffn": 1024})
     with pytest.raises(qeng.QengError) as e:

@@ -186,3 +186,31 @@ def test_q8_quantizer_known_answers_and_gguf_pin():
     assert np.array_equal(g[..., :2].copy().view(np.uint16)[..., 0], s.view(np.uint16))
     assert np.array_equal(g[..., 2:].copy().view(np.int8).reshape(q.shape), q)
 
+
+def test_q4k_fields_round_trip_and_gguf_pin():
+    """K-quant super-blocks: the 6-bit scale / minimum packing and the nibble order round-trip, and
+    where the third-party `gguf` package is present its Q4_K dequantizer gives the same f32 weights
+    from the same bytes (random field values included)."""
+    rng = ref.rng_of(41)
+    n, k = 48, 768
+    S = k // 256
+    d = rng.uniform(1e-4, 1e-2, (n, S)).astype(np.float16)
+    dmin = rng.uniform(1e-4, 1e-2, (n, S)).astype(np.float16)
+    sc = rng.integers(0, 64, (n, S, 8)).astype(np.uint8)
+    mn = rng.integers(0, 64, (n, S, 8)).astype(np.uint8)
+    codes = rng.integers(0, 16, (n, k), dtype=np.uint8)
+    blocks = ref.q4k_pack(d, dmin, sc, mn, codes)
+    q, dm = ref.q4k_unpack(blocks, n, k)
+    assert np.array_equal(q, codes)
+    assert np.array_equal(dm[..., 0].reshape(n, S, 8), d.astype(np.float32)[..., None] * sc)
+    assert np.array_equal(dm[..., 1].reshape(n, S, 8), dmin.astype(np.float32)[..., None] * mn)
+    w = ref.dequant(q, dm, np.float32)
+    assert np.array_equal(w[0, :32], (dm[0, 0, 0] * codes[0, :32].astype(np.float32)).astype(np.float32) - dm[0, 0, 1])
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    raw = rng.integers(0, 256, blocks.shape, dtype=np.uint8)
+    raw[..., 0:4] = blocks[..., 0:4]  # keep finite f16 d / dmin
+    for b in (blocks, raw):
+        qq, dd = ref.q4k_unpack(b, n, k)
+        assert np.array_equal(quants.dequantize(b.reshape(n, -1), gguf.GGMLQuantizationType.Q4_K), ref.dequant(qq, dd, np.float32))
+
