@@ -18,8 +18,9 @@
 //     the parts in rank order onto the residual stream it keeps in registers, normalises and
 //     quantises.  No barrier, no atomics, and with tensor parallelism the same stores go to every
 //     peer's inbox over NVLink (plain peer stores): the all-reduce costs no launch of its own.
-//   * q|k|v -> attention, attention -> o and gate|up -> down are grid barriers (one atomic
-//     arrival per CTA, bounded wait).
+//   * attention -> o and gate|up -> down hand their rows over the same way (tagged pairs in an
+//     attention box / activation box); q|k|v -> attention is the one grid barrier per layer (one
+//     atomic arrival per CTA, bounded wait): the attention reads the KV pages other CTAs appended.
 // Every wait is bounded (two seconds); on expiry the kernel records a status and runs on to its
 // end without waiting again.
 #include <math.h>

@@ -1,27 +1,30 @@
-// Device-side building blocks of the decode matmul over 4-bit block weights, shared by the
+// Device-side building blocks of the decode matmul over block-quantised weights, shared by the
 // standalone streaming kernel (gemv_q4_stream.cu) and the fused decode-step kernel
 // (decode_step.cu).
 //
-// Arithmetic.  Weights stay 4-bit codes c in 0..15 with one f16 scale s per 32-block:
-// w = (c - 8) s.  Activations are quantised per (row, 32-block) to 15-bit fixed point with a
-// power-of-two step: e = floor(log2(max|x| over the block)) - 13, q = clamp(rint(x 2^-e),
-// -16384, 16383), split into two signed bytes q = 128 hi + lo (hi = q >> 7 in -128..127,
-// lo = q & 127).  The contraction runs on the tensor pipe as integer MMAs
-// (mma.sync.m16n8k32, u8 codes x s8 activation bytes, exact s32 accumulation): the weight
-// words need one AND per four codes, and the block's zero point enters through the
-// accumulator's initial value -8 sum(hi) / -8 sum(lo).  Per block the exact integer result is
-// scaled in f32: y += s 2^e (128 D_hi + D_lo), f32 accumulation over the blocks.
-// Error: the rounding of x to 15 bits relative to its block's largest magnitude (<= 2^-14 of
-// it), ~5e-5 of max|y| for Gaussian activations; everything else is exact up to the f32
-// accumulation.  One-hot or power-of-two activations are exact.
+// Arithmetic.  4-bit blocks: weights stay codes c in 0..15 with one f16 scale s per 32-block,
+// w = (c - 8) s.  Activations are quantised per (row, 32-block) to fixed point with a power-of-two
+// step 2^e: 15 bits in two limbs, q = 128 hi + lo (hi = q >> 7 in -128..127, lo = q & 127), or, for a
+// single activation row, 22 bits in three limbs (q = 16384 h + 128 m + l).  The contraction runs on
+// the tensor pipe as integer MMAs (mma.sync.m16n8k32, u8 codes x s8 limb bytes, exact s32
+// accumulation): a word of 8 codes becomes the operand bytes with two ANDs and a shift, and the
+// block's zero point enters through the accumulator's initial value B - 8 sum(limb), B = 0x4B400000,
+// so that the s32 result read as an f32 is 12582912 + d exactly.  Per block the exact integer result
+// is scaled in f32: y += s 2^e sum_l 128^l D_l, f32 accumulation over the blocks.
+// 8-bit blocks (w = q s, q a signed byte): the bytes are the operand as stored, s8 x s8 MMAs, no
+// zero point.  4-bit K-quant blocks (w = D c - M): no zero point, and a second term
+// - M * 2^e sum_l 128^l S_l with S_l the block sum of the activation limbs.
+// Error: the rounding of x relative to its block's largest magnitude (2^-14 of it with two limbs:
+// ~5e-5 of max|y| for Gaussian activations; 2^-21 with three); everything else is exact up to the
+// f32 accumulation.  One-hot or power-of-two activations are exact.
 //
-// Column use of the 8-wide MMA tile.  An activation row takes two columns (hi, lo).  With one
-// activation row, the 8 columns hold (limb, block) for FOUR consecutive blocks: the MMA of
-// block j gets activation bytes only in the two columns of block j (the other lanes read a
-// zero region), so four blocks share one accumulator fragment and the f32 post-processing (scale
-// conversion, 4 FMAs) is paid once per four blocks instead of once per block.  Two rows: two
-// blocks per fragment.  Three or four rows: one block per fragment, columns = (row, limb).
-// More rows: several such 8-column tiles.
+// Column use of the 8-wide MMA tile.  One activation row in two limbs: the 8 columns hold
+// (limb, block) for FOUR consecutive blocks; the MMA of block j gets activation bytes only in the
+// two columns of block j (the other lanes' bytes are masked to zero), so four blocks share one
+// accumulator fragment and the f32 post-processing is paid once per four blocks.  One row in three
+// limbs, or two rows: two blocks per fragment (the lanes of the other block read a zero region).
+// Three or four rows: one block per fragment, columns = (row, limb).  More rows: several such
+// 8-column tiles.
 #pragma once
 #include "qeng_internal.h"
 

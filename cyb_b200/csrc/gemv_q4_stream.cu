@@ -1,25 +1,27 @@
-// Streaming decode GEMV/GEMM over 4-bit block weights: the bandwidth kernel.
+// Streaming decode GEMV/GEMM over block-quantised weights: the bandwidth kernel.
 //
-// One persistent CTA per SM: 16 consumer warps in up to four tile groups, each
-// group with a producer warp and a ring of shared-memory stages of its own.  A
-// producer walks its group's row tiles (16 rows x K, contiguous in the packed
-// layout) and copies them stage by stage (16 chunks: 8 KB of nibbles + 1 KB of
-// scales) with bulk asynchronous copies (cp.async.bulk, completion counted on
-// an mbarrier), so ~200 KB per SM are in flight without holding registers and
-// independent of what the consumers are doing.  Consumers take the chunks of a stage
-// round-robin, read them with conflict-free 128-bit shared loads, unpack in
-// registers and contract on the tensor pipe with integer MMAs against the
-// activations quantised to two signed bytes per value (gemm_q4_s8.cuh has the
-// arithmetic).  At the end of a row tile the 16 partial accumulators meet in
-// shared memory (one named barrier, double-buffered) and one warp applies the
-// fused epilogue.
+// One persistent CTA per SM: 16 consumer warps and one producer warp per tile group around a ring
+// of shared-memory stages.  A producer walks its row tiles (16 rows x K, contiguous in the packed
+// layout) and copies them stage by stage (up to 64 chunks of 64 k: a whole row tile of K = 4096,
+// 36 KB for 4-bit blocks) with bulk asynchronous copies (cp.async.bulk, completion counted on an
+// mbarrier), so ~200 KB per SM are in flight without holding registers and independent of what the
+// consumers are doing.  Consumers take the chunks of a stage round-robin, read them with
+// conflict-free 128-bit shared loads and contract on the tensor pipe with integer MMAs against the
+// activations quantised to block fixed point (gemm_q4_s8.cuh has the arithmetic).
 //
-// Up to 4 activation rows keep the whole K range staged; more rows (up to 16
-// per launch) are staged in K slices, the weights of a slice streamed for all
-// of the CTA's tiles and the partial sums kept in shared memory between
-// slices, so the weights still cross HBM once per launch.
+// One or two activation rows: all 16 warps work on every tile, park their partial sums of a tile in
+// shared memory and move on; the CTA meets once per 16 tiles, sums the partials and runs the fused
+// epilogues of those tiles in parallel (kTG = 0).  Three to 16 rows: the warps form 1, 2 or 4 tile
+// groups, each with its own ring and producer warp, and reduce per tile over one named barrier.
 //
-// HBM-bound: algorithmic bytes = N*K*0.5625 + activations + outputs.
+// Up to 4 activation rows keep the whole K range staged; more rows (up to 16 per launch) arrive as
+// quantised images per K slice (quantise_rows_kernel), the weights of a slice are streamed for all
+// of the CTA's tiles and the partial sums kept in shared memory between slices, so the weights
+// still cross HBM once per launch.
+//
+// Weight formats: 4-bit blocks (nibbles unpacked in registers, zero point 8), 8-bit blocks (the
+// bytes are the MMA operand as stored), 4-bit K-quant blocks (f32 scale and minimum per block, up to
+// 4 rows).  HBM-bound: algorithmic bytes = N*K*{0.5625, 1.0625, 0.75} + activations + outputs.
 #include <cstdlib>
 #include "gemm_q4_s8.cuh"
 
