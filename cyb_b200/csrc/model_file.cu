@@ -11,11 +11,12 @@
 //   ~~~config    TOML: hidden_size, intermediate_size, num_hidden_layers, num_attention_heads,
 //                num_key_value_heads, head_dim, vocab_size, rms_norm_eps, rope_theta; optional
 //                attn_logit_softcapping, sliding_window, final_logit_softcapping
-//   ~~~tensors   TOML array of tables [[tensor]]: name, dtype ("Q4" | "Q8" | "Q4_K" | "F32" | "F16" | "BF16"),
+//   ~~~tensors   TOML array of tables [[tensor]]: name, dtype ("Q4" | "Q4_0" | "Q8" (= "Q8_0") | "Q4_K" | "F32" | "F16" | "BF16"),
 //                shape = [rows, cols] (or [n]), offset and size in bytes inside `weights`
 //   ~~~weights   binary.  Q4 = row-major 32-blocks of 18 bytes: f16 scale, then 16 bytes holding the
 //                codes of k = 2i (low nibble) and k = 2i + 1 (high nibble); w = (code - 8) * scale.
-//                Q8 = row-major 32-blocks of 34 bytes: f16 scale, then 32 signed bytes; w = q * scale.
+//                Q4_0 = the same block with the nibble order of the published format of that name (byte i:
+//                k = i low, k = i + 16 high).  Q8 = row-major 32-blocks of 34 bytes: f16 scale, then 32 signed bytes; w = q * scale.
 //                Q4_K = row-major super-blocks of 144 bytes per 256 weights (the published layout).
 //
 // The file is mapped read-only (the reference maps its model files, shell/src/lib.rs:31-33); Q4
@@ -264,17 +265,17 @@ bool open_model(const char* path, ModelFile& m) {
     int64_t want = -1;
     if (t.dtype == "F32") want = n * 4;
     else if (t.dtype == "F16" || t.dtype == "BF16") want = n * 2;
-    else if (t.dtype == "Q4") {
+    else if (t.dtype == "Q4" || t.dtype == "Q4_0") {
       if (t.shape.size() != 2 || t.shape[1] % 32 != 0) return fail(m, "tensor `" + t.name + "`: Q4 needs [rows, cols] with cols % 32 == 0");
       want = n / 32 * 18;
-    } else if (t.dtype == "Q8") {
+    } else if (t.dtype == "Q8" || t.dtype == "Q8_0") {
       if (t.shape.size() != 2 || t.shape[1] % 32 != 0) return fail(m, "tensor `" + t.name + "`: Q8 needs [rows, cols] with cols % 32 == 0");
       want = n / 32 * 34;
     } else if (t.dtype == "Q4_K") {
       if (t.shape.size() != 2 || t.shape[1] % 256 != 0) return fail(m, "tensor `" + t.name + "`: Q4_K needs [rows, cols] with cols % 256 == 0");
       want = n / 256 * 144;
     } else {
-      return fail(m, "tensor `" + t.name + "`: dtype `" + t.dtype + "` is not one of Q4, Q8, Q4_K, F32, F16, BF16");
+      return fail(m, "tensor `" + t.name + "`: dtype `" + t.dtype + "` is not one of Q4, Q4_0, Q8, Q8_0, Q4_K, F32, F16, BF16");
     }
     if (t.size != want) return fail(m, "tensor `" + t.name + "`: size " + std::to_string(t.size) + " does not match its shape and dtype (" + std::to_string(want) + ")");
     if (t.offset + t.size > wts->len) return fail(m, "tensor `" + t.name + "`: runs past the end of `weights`");
@@ -394,20 +395,23 @@ int32_t qeng_decoder_load_file(qeng_ctx* ctx, qeng_decoder* dec, const char* pat
     const char* data = wts->data + t->offset;
     q.resize((size_t)N * K);
     s.resize((size_t)N * K / 32);
-    if (t->dtype == "Q4") {
+    if (t->dtype == "Q4" || t->dtype == "Q4_0") {
+      // "Q4": byte i holds k = 2i (low nibble) and k = 2i + 1 (high); "Q4_0" (the order of the
+      // published block of that name): byte i holds k = i (low) and k = i + 16 (high)
+      const bool split = t->dtype == "Q4_0";
       const int64_t nb = N * K / 32;
       for (int64_t b = 0; b < nb; ++b) {
         const uint8_t* blk = reinterpret_cast<const uint8_t*>(data) + b * 18;
         memcpy(&s[(size_t)b], blk, 2);
         uint8_t* dst = &q[(size_t)b * 32];
         for (int i = 0; i < 16; ++i) {
-          dst[2 * i] = blk[2 + i] & 15;
-          dst[2 * i + 1] = blk[2 + i] >> 4;
+          dst[split ? i : 2 * i] = blk[2 + i] & 15;
+          dst[split ? i + 16 : 2 * i + 1] = blk[2 + i] >> 4;
         }
       }
     } else if (t->dtype == "Q4_K") {
       return qeng_decoder_load_matrix_q4k(ctx, dec, layer, which, reinterpret_cast<const uint8_t*>(data), N, K);
-    } else if (t->dtype == "Q8") {
+    } else if (t->dtype == "Q8" || t->dtype == "Q8_0") {
       const int64_t nb = N * K / 32;
       for (int64_t b = 0; b < nb; ++b) {
         const uint8_t* blk = reinterpret_cast<const uint8_t*>(data) + b * 34;
@@ -434,7 +438,7 @@ int32_t qeng_decoder_load_file(qeng_ctx* ctx, qeng_decoder* dec, const char* pat
     if (!t) return required ? qeng_fail(ctx, QENG_ERR_ARG, "model file %s: tensor `%s` is missing", path, name.c_str()) : 1;
     int64_t have = 1;
     for (int64_t d : t->shape) have *= d;
-    if (t->dtype == "Q4" || t->dtype == "Q8" || t->dtype == "Q4_K" || have != n) return qeng_fail(ctx, QENG_ERR_SHAPE, "model file %s: tensor `%s` must hold %lld floats", path, name.c_str(), (long long)n);
+    if (t->dtype[0] == 'Q' || have != n) return qeng_fail(ctx, QENG_ERR_SHAPE, "model file %s: tensor `%s` must hold %lld floats", path, name.c_str(), (long long)n);
     to_f32(*t, wts->data + t->offset, out);
     return QENG_OK;
   };
@@ -471,7 +475,7 @@ int32_t qeng_decoder_load_file(qeng_ctx* ctx, qeng_decoder* dec, const char* pat
   auto table = [&](const std::string& name, std::vector<uint16_t>* out, bool required) -> int32_t {
     const Tensor* t = get(name);
     if (!t) return required ? qeng_fail(ctx, QENG_ERR_ARG, "model file %s: tensor `%s` is missing", path, name.c_str()) : 1;
-    if (t->dtype == "Q4" || t->dtype == "Q8" || t->dtype == "Q4_K" || t->shape.size() != 2 || t->shape[0] != dc.vocab || t->shape[1] != dm)
+    if (t->dtype[0] == 'Q' || t->shape.size() != 2 || t->shape[0] != dc.vocab || t->shape[1] != dm)
       return qeng_fail(ctx, QENG_ERR_SHAPE, "model file %s: tensor `%s` must be a float matrix [%d, %lld]", path, name.c_str(), dc.vocab, (long long)dm);
     const char* data = wts->data + t->offset;
     const size_t n = (size_t)dc.vocab * dm;

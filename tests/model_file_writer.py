@@ -20,6 +20,16 @@ def q4_blocks(q, s):
     return out.tobytes()
 
 
+def q4_0_blocks(q, s):
+    """The same 18-byte block in the nibble order of the published Q4_0: byte i = k = i | (k = i + 16) << 4."""
+    n, k = q.shape
+    out = np.empty((n * k // 32, 18), np.uint8)
+    out[:, :2] = np.ascontiguousarray(s, np.float16).reshape(-1, 1).view(np.uint8)
+    b = q.reshape(-1, 32)
+    out[:, 2:] = (b[:, :16] | (b[:, 16:] << 4)).astype(np.uint8)
+    return out.tobytes()
+
+
 def q8_blocks(q, s):
     """bytes [N,K] int8 + f16 scales [N,K/32] -> row-major 34-byte blocks (scale, then the 32 bytes)."""
     n, k = q.shape
@@ -52,6 +62,8 @@ def write_model(path, cfg, W, linear_dtype="Q4", tie_head=False, name="sample"):
             add(tname, "Q8", list(q.shape), q8_blocks(q, s))
         elif linear_dtype == "Q4":
             add(tname, "Q4", list(q.shape), q4_blocks(q, s))
+        elif linear_dtype == "Q4_0":
+            add(tname, "Q4_0", list(q.shape), q4_0_blocks(q, s))
         else:
             w = ref.dequant(q, s, np.float32)
             if linear_dtype == "F32":

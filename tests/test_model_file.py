@@ -51,7 +51,7 @@ def test_malformed_containers_are_rejected(built_lib, tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("linear_dtype,tie", [("Q4", False), ("F32", False), ("F16", True), ("Q8", False), ("Q4_K", False)])
+@pytest.mark.parametrize("linear_dtype,tie", [("Q4", False), ("F32", False), ("F16", True), ("Q8", False), ("Q4_K", False), ("Q4_0", False)])
 def test_decoder_loaded_from_a_file_equals_one_loaded_from_arrays(ctx, tmp_path, linear_dtype, tie):
     from cyb_b200 import qeng
     cfg = ref.DecoderConfig(**CFG)
@@ -60,7 +60,7 @@ def test_decoder_loaded_from_a_file_equals_one_loaded_from_arrays(ctx, tmp_path,
         W["lm_head"] = W["emb"]
     path = os.path.join(tmp_path, "toy.model")
     mfw.write_model(path, cfg, W, linear_dtype=linear_dtype, tie_head=tie)
-    if linear_dtype not in ("Q4", "Q8", "Q4_K"):
+    if linear_dtype not in ("Q4", "Q8", "Q4_K", "Q4_0"):
         # float weights are quantised at load: what the decoder must then hold is the oracle's
         # quantisation of the stored (rounded) matrix, not the codes the file was made from
         W = dict(W, layers=[dict(lw) for lw in W["layers"]])
@@ -100,3 +100,17 @@ def test_decoder_loaded_from_a_file_equals_one_loaded_from_arrays(ctx, tmp_path,
     assert e.value.code == -2
     for d in (a, b, c):
         d.free()
+
+
+def test_block_byte_orders_match_the_gguf_package():
+    """The "Q4_0" and "Q8" tensor encodings of the container are byte for byte what the third-party
+    `gguf` package writes for its Q4_0 / Q8_0 types (so tensor data of that origin loads as it is)."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    x = ref.rng_of(2).standard_normal((16, 96)).astype(np.float32)
+    q, s = ref.quantize_q4(x)
+    assert np.array_equal(np.frombuffer(mfw.q4_0_blocks(q, s), np.uint8),
+                          quants.quantize(x, gguf.GGMLQuantizationType.Q4_0).reshape(-1))
+    q8, s8 = ref.quantize_q8(x)
+    assert np.array_equal(np.frombuffer(mfw.q8_blocks(q8, s8), np.uint8),
+                          quants.quantize(x, gguf.GGMLQuantizationType.Q8_0).reshape(-1))
