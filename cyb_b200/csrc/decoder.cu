@@ -192,6 +192,7 @@ struct qeng_decoder {
   float *xn = nullptr, *xlast = nullptr, *logits = nullptr;
   int32_t *next = nullptr, *out_tokens = nullptr, *step = nullptr, *dec_table = nullptr;
   int max_steps = 0;
+  int32_t* h_out = nullptr;  // pinned: the tokens of a decode call, then the status word (one synchronisation per call)
   int batch = 0;
   std::vector<int32_t> len;  // host copy of sequence lengths
   bool have_logits = false;
@@ -626,6 +627,7 @@ int32_t qeng_decoder_create(qeng_ctx* ctx, const qeng_model_cfg* cfg, qeng_decod
   }
   if (e == cudaSuccess) e = cudaMalloc(&d->step, 4);
   if (e == cudaSuccess) e = cudaMalloc(&d->out_tokens, (size_t)(d->max_steps + 1) * cfg->max_batch * 4);
+  if (e == cudaSuccess) e = cudaMallocHost(&d->h_out, ((size_t)d->max_steps * cfg->max_batch + 1) * 4);
   if (e == cudaSuccess) e = cudaMalloc(&d->dec_table, (size_t)cfg->max_batch * d->max_pages * 4);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&d->own_stream, cudaStreamNonBlocking);
   d->stream = d->own_stream;
@@ -679,6 +681,7 @@ int32_t qeng_decoder_free(qeng_ctx* ctx, qeng_decoder* d) {
   for (void* p : bufs)
     if (p) cudaFree(p);
   if (d->own_stream) cudaStreamDestroy(d->own_stream);
+  if (d->h_out) cudaFreeHost(d->h_out);
   delete d;
   return QENG_OK;
 }
@@ -978,10 +981,13 @@ int32_t qeng_decoder_decode(qeng_ctx* ctx, qeng_decoder* d, int32_t steps, int32
     }
     for (int s = 0; s < steps; ++s) QENG_CUDA(ctx, cudaGraphLaunch(d->graph, st));
   }
-  QENG_CUDA(ctx, cudaMemcpyAsync(out_tokens, d->out_tokens, (size_t)steps * B * 4, cudaMemcpyDeviceToHost, st));
-  int32_t status = 0;
-  QENG_CUDA(ctx, cudaMemcpyAsync(&status, ctx->status, 4, cudaMemcpyDeviceToHost, st));
+  // tokens and status word through pinned memory: both copies are queued behind the steps and the
+  // call synchronises once
+  const size_t ntok = (size_t)steps * B;
+  QENG_CUDA(ctx, cudaMemcpyAsync(d->h_out, d->out_tokens, ntok * 4, cudaMemcpyDeviceToHost, st));
+  QENG_CUDA(ctx, cudaMemcpyAsync(d->h_out + ntok, ctx->status, 4, cudaMemcpyDeviceToHost, st));
   QENG_CUDA(ctx, cudaStreamSynchronize(st));
+  const int32_t status = d->h_out[ntok];
   for (int b = 0; b < B; ++b) d->len[b] += steps;
   if (d->vsplit) d->logits_partial = true;
   d->next_ready = status == 0;
@@ -990,9 +996,8 @@ int32_t qeng_decoder_decode(qeng_ctx* ctx, qeng_decoder* d, int32_t steps, int32
     return qeng_fail(ctx, QENG_ERR_DEVICE_STATUS, "decoder_decode: a kernel reported status %d (1 = page id outside the pool, 2 = position outside the cache, 3 = token id outside the vocabulary)", status);
   }
   // device order is [step][batch]; the caller gets [batch][steps]
-  std::vector<int32_t> tmp(out_tokens, out_tokens + (size_t)steps * B);
   for (int s = 0; s < steps; ++s)
-    for (int b = 0; b < B; ++b) out_tokens[(size_t)b * steps + s] = tmp[(size_t)s * B + b];
+    for (int b = 0; b < B; ++b) out_tokens[(size_t)b * steps + s] = d->h_out[(size_t)s * B + b];
   return QENG_OK;
 }
 
